@@ -1,0 +1,229 @@
+/*
+ * b200moe — C ABI of the B200 (sm_100a) fused Mixture-of-Experts kernels.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless the
+ * parameter name ends in `_host`; `stream` is a cudaStream_t passed as void*.
+ * No call allocates, synchronises or creates streams (one entry at the end of
+ * this header is the documented exception for allocation-free callers and it
+ * allocates nothing either).  Scratch memory is passed in by the caller; its
+ * size comes from the matching *_workspace_bytes() query.
+ *
+ * Every function returns one of the B200MOE_* status codes below and never
+ * throws or aborts.  Citations name the operator of vllm-xpu-kernels that an
+ * entry point stands in for (path inside that project).
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_OK 0
+#define B200MOE_INVALID_ARG (-1)
+#define B200MOE_UNSUPPORTED (-2)
+#define B200MOE_WORKSPACE_TOO_SMALL (-3)
+#define B200MOE_CUDA_ERROR (-4)
+#define B200MOE_TIMEOUT (-5)
+
+/* element types */
+#define B200MOE_F32 0
+#define B200MOE_F16 1
+#define B200MOE_BF16 2
+#define B200MOE_E4M3 3
+#define B200MOE_I32 4
+#define B200MOE_I64 5
+#define B200MOE_U32 6
+#define B200MOE_U8 7
+#define B200MOE_E2M1X2 8 /* two e2m1 per byte, low nibble = even element */
+
+/* weight recipes of the grouped GEMM */
+#define B200MOE_RECIPE_BF16 0     /* B [E,K,N] bf16/f16, no scales                     */
+#define B200MOE_RECIPE_FP8_BLOCK 1 /* B [E,K,N] e4m3, scales f32 [E,K/128,N/128]        */
+#define B200MOE_RECIPE_MXFP4 2    /* B [E,N,K/2] e2m1x2, scales e8m0 u8 [E,N,K/32]     */
+
+#define B200MOE_B_LAYOUT_KN 0
+#define B200MOE_B_LAYOUT_NK 1
+
+/* epilogues of the grouped GEMM */
+#define B200MOE_EPI_STORE 0        /* D = acc (+bias), dtype of D                       */
+#define B200MOE_EPI_SILU_MUL 1     /* D[:, j] = silu(acc[:, j]) * acc[:, N/2 + j]       */
+#define B200MOE_EPI_SWIGLU_OAI 2   /* D[:, j] from acc[:, 2j] (gate), acc[:, 2j+1] (up) */
+
+const char* b200moe_version(void);
+/* Text for a status code. */
+const char* b200moe_status_string(int status);
+/* Last CUDA error text seen by this library on the calling thread. */
+const char* b200moe_last_error(void);
+
+/* ---- routing ---------------------------------------------------------- */
+
+/* topk_softmax (csrc/moe/torch_bindings.cpp:62-66, csrc/moe/topk.cpp:889-941).
+ * logits [T,E] of `in_dtype` (F32/F16/BF16); bias f32 [E] or NULL; is_padding
+ * u8 [T] or NULL.  Outputs: weights f32 [T,k]; ids [T,k] of `ids_dtype`
+ * (I32/U32/I64); src_rows i32 [T,k] (= j*T + t) or NULL. */
+int b200moe_topk_softmax(const void* logits, int in_dtype, int T, int E, int k,
+                         int renormalize, const float* bias,
+                         const uint8_t* is_padding, float* weights, void* ids,
+                         int ids_dtype, int32_t* src_rows, void* stream);
+
+/* topk_sigmoid (csrc/moe/torch_bindings.cpp:68-72, csrc/moe/topk.cpp:943-997). */
+int b200moe_topk_sigmoid(const void* logits, int in_dtype, int T, int E, int k,
+                         int renormalize, const float* bias,
+                         float routed_scaling_factor, const uint8_t* is_padding,
+                         float* weights, void* ids, int ids_dtype,
+                         int32_t* src_rows, void* stream);
+
+/* grouped_topk (csrc/moe/torch_bindings.cpp:56-60, csrc/moe/grouped_topk.cpp:825-942).
+ * scores [T,E] of `in_dtype`; bias [E] of `bias_dtype` (F32/F16/BF16);
+ * scoring_func 0 = scores are already activated, 1 = sigmoid here.
+ * Outputs: values f32 [T,k], ids i32 [T,k]. */
+int b200moe_grouped_topk(const void* scores, int in_dtype, const void* bias,
+                         int bias_dtype, int T, int E, int n_group,
+                         int topk_group, int k, int renormalize,
+                         float routed_scaling_factor, int scoring_func,
+                         float* values, int32_t* ids, void* stream);
+
+/* ---- permutation ------------------------------------------------------ */
+
+/* moe_align_block_size (csrc/moe/torch_bindings.cpp:14-20,
+ * csrc/moe/moe_align_sum_kernels.cpp:1034-1181).  topk_ids: `numel` entries of
+ * `ids_dtype`; expert_map i32 [num_experts] or NULL.  sorted_token_ids has
+ * `sorted_capacity` entries, expert_ids `blocks_capacity`.  Order inside an
+ * expert is ascending flat index (stable), so the result is reproducible. */
+size_t b200moe_moe_align_block_size_workspace_bytes(int64_t numel, int num_experts);
+int b200moe_moe_align_block_size(const void* topk_ids, int ids_dtype,
+                                 int64_t numel, int num_experts, int block_size,
+                                 const int32_t* expert_map,
+                                 int32_t* sorted_token_ids, int64_t sorted_capacity,
+                                 int32_t* expert_ids, int64_t blocks_capacity,
+                                 int32_t* num_tokens_post_pad, void* workspace,
+                                 size_t workspace_bytes, void* stream);
+
+/* init_expert_map (csrc/moe/torch_bindings.cpp:86-91, csrc/moe/init_expert_map.cpp:78-95). */
+int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,
+                            int ep_rank, int ep_size, void* stream);
+
+/* remap_hidden_states (csrc/moe/torch_bindings.cpp:92-101,
+ * csrc/moe/remap_hidden_states.cpp:415-568).  Copies row t of `hidden`
+ * (row_bytes bytes, a multiple of 16) and of `scales` (scale_row_bytes, may be
+ * 0/NULL) to the permuted row of every local (t, j); rows_per_expert i32
+ * [local_experts] is ADDED to (the caller zeroes it, as the reference's caller
+ * does); row_map i32 [T,k] gets the permuted row or -1.  Stable. */
+size_t b200moe_remap_hidden_states_workspace_bytes(int T, int k, int local_experts);
+int b200moe_remap_hidden_states(const void* hidden, const void* scales,
+                                void* remapped, void* remapped_scales,
+                                int64_t row_bytes, int64_t scale_row_bytes,
+                                const void* topk_ids, int ids_dtype,
+                                const int32_t* expert_map, int T, int k,
+                                int total_experts, int local_experts,
+                                int32_t* rows_per_expert, int32_t* row_map,
+                                void* workspace, size_t workspace_bytes,
+                                void* stream);
+
+/* moe_gather (csrc/moe/torch_bindings.cpp:81-85, csrc/moe/moe_gather.cpp:162-205).
+ * out[t,:] = sum_j w[t,j] * y[row_map[t,j],:] (fp32 accumulate, -1 skipped). */
+int b200moe_moe_gather(void* out, const void* y, int dtype, const float* weights,
+                       const int32_t* row_map, int T, int k, int H, void* stream);
+
+/* moe_sum (csrc/moe/torch_bindings.cpp:7-10, csrc/moe/moe_align_sum_kernels.cpp:1224-1372).
+ * out[t,:] = sum_j in[t,j,:]; with topk_ids, slots with id < 0 or
+ * expert_map[id] < 0 are skipped. */
+int b200moe_moe_sum(const void* in, void* out, int dtype, int T, int k, int H,
+                    const void* topk_ids, int ids_dtype,
+                    const int32_t* expert_map, void* stream);
+
+/* ---- gated activations and activation quantisation --------------------- */
+
+/* silu_and_mul (csrc/torch_bindings.cpp:80-81, csrc/activation.cpp:546-553). in [R,2d] -> out [R,d]. */
+int b200moe_silu_and_mul(void* out, const void* in, int dtype, int64_t R, int d,
+                         void* stream);
+/* swigluoai_and_mul (csrc/torch_bindings.cpp:192-196, csrc/activation.cpp:737-743). */
+int b200moe_swigluoai_and_mul(void* out, const void* in, int dtype, int64_t R,
+                              int d, float alpha, float limit, void* stream);
+
+/* per_token_group_fp8_quant (csrc/torch_bindings.cpp:175-182,
+ * csrc/quantization/fp8/fp8_quant.cpp:724-849).  scales f32, element (r, g) at
+ * r*scale_stride_row + g*scale_stride_group. */
+int b200moe_per_token_group_fp8_quant(const void* in, int dtype, void* out_q,
+                                      float* out_s, int64_t R, int N,
+                                      int group_size, float eps, float fp8_min,
+                                      float fp8_max, int scale_ue8m0,
+                                      int64_t scale_stride_row,
+                                      int64_t scale_stride_group, void* stream);
+
+/* per_token_group_quant_mxfp4 (csrc/torch_bindings.cpp:185-189,
+ * csrc/quantization/fp4/mxfp4_quant.cpp:24-126).  group_size must be 32. */
+int b200moe_per_token_group_quant_mxfp4(const void* in, int dtype, uint8_t* out_q,
+                                        float* out_s, int64_t R, int N,
+                                        int group_size, float eps,
+                                        int64_t scale_stride_row,
+                                        int64_t scale_stride_group, void* stream);
+
+/* silu_and_mul_per_block_quant (csrc/torch_bindings.cpp:89-101,
+ * csrc/quantization/fused_kernels/fused_silu_mul_block_quant.cpp). in [R,2d]. */
+int b200moe_silu_mul_block_quant(const void* in, int dtype, void* out_q,
+                                 float* out_s, int64_t R, int d, int group_size,
+                                 const float* scale_ub, int scale_ue8m0,
+                                 int64_t scale_stride_row,
+                                 int64_t scale_stride_group, void* stream);
+
+/* silu_and_mul_mxfp4_quant (csrc/torch_bindings.cpp:103-107,
+ * csrc/quantization/fused_kernels/fused_silu_mul_mxfp4_quant.cpp). */
+int b200moe_silu_mul_mxfp4_quant(const void* in, int dtype, uint8_t* out_q,
+                                 float* out_s, int64_t R, int d, int group_size,
+                                 float eps, void* stream);
+
+/* ---- grouped GEMM ------------------------------------------------------ */
+
+typedef struct b200moe_gemm_args {
+  int recipe;        /* B200MOE_RECIPE_*                                        */
+  int epilogue;      /* B200MOE_EPI_*                                           */
+  int a_dtype;       /* BF16/F16 (any recipe) or E4M3 (FP8_BLOCK with a_scale)  */
+  int d_dtype;       /* BF16/F16, or E4M3 with d_scale (fused group-128 quant)  */
+  const void* A;     /* [R,K] rows grouped by expert, back to back              */
+  const float* a_scale; /* [R,K/128] f32 when a_dtype == E4M3, else NULL        */
+  const void* B;     /* per recipe                                              */
+  int b_layout;      /* BF16 recipe only: B200MOE_B_LAYOUT_KN [E,K,N] (the operator's
+                        layout) or B200MOE_B_LAYOUT_NK [E,N,K]                    */
+  const void* b_scale;
+  const void* bias;  /* [E,N] of bias_dtype or NULL                             */
+  int bias_dtype;
+  void* D;           /* [R,N] or [R,N/2] for the gated epilogues                */
+  float* d_scale;    /* [R,(N/2)/128] f32 when d_dtype == E4M3                  */
+  const int32_t* rows_per_expert; /* i32 [E], device                           */
+  int64_t R;         /* rows of A (upper bound on sum(rows_per_expert))         */
+  int N, K, E;
+  float alpha, limit; /* SWIGLU_OAI parameters                                  */
+} b200moe_gemm_args;
+
+/* cutlass_grouped_gemm_interface (csrc/xpu/torch_bindings.cpp:58-67,
+ * csrc/xpu/grouped_gemm/grouped_gemm_interface.cpp:12-64): for expert e with
+ * rows [off_e, off_e + rows_e): D = A * B_e (+ bias_e), fp32 accumulate. */
+size_t b200moe_grouped_gemm_workspace_bytes(const b200moe_gemm_args* args);
+int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Expands quantised expert weights to bf16 once, so that later grouped-GEMM
+ * calls can take the 16-bit path without a per-call workspace: FP8_BLOCK
+ * [E,K,N] -> bf16 [E,K,N]; MXFP4 [E,N,K/2] -> bf16 [E,N,K] (exact).
+ * Stands in for the in-register up-conversion of
+ * csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:399-483. */
+int b200moe_dequant_weights(int recipe, const void* B, const void* b_scale,
+                            void* out_bf16, int E, int N, int K, void* stream);
+
+/* Plain CUDA-core evaluation of the same contract, one thread per output
+ * element, for checking the tensor-core path on sizes a CPU cannot reach. */
+int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* stream);
+
+/* Reads (and clears) the sticky device status word that bounded waits inside
+ * the tensor-core kernels set when they give up; 0 = none.  Synchronises. */
+int b200moe_device_status(void* stream, int* status_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

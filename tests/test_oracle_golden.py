@@ -1,0 +1,144 @@
+"""The CPU oracle against outputs of the reference project's own torch oracles
+(tests/golden/*.npz, written by tests/golden/make_golden.py) and against the
+known answers the reference documents."""
+import glob
+import os
+
+import pytest
+import torch
+
+from conftest import GOLDEN, as_bf16, load_golden
+from oracle import moe_oracle as O
+
+
+def _names(prefix):
+    return sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, prefix + "*.npz")))
+
+
+@pytest.mark.parametrize("name", _names("topk_"))
+def test_topk_matches_reference(name):
+    g = load_golden(name)
+    k = g["k"]
+    if name == "topk_ties":
+        w, i = O.topk_softmax(g["logits"], k, True)
+        assert torch.equal(i, g["i"]) and torch.equal(w, g["w"])
+        return
+    renorm = bool(g["renorm"])
+    w, i = O.topk_softmax(g["logits"], k, renorm)
+    assert torch.equal(i, g["i"]) and torch.equal(w, g["w"])
+    w, i = O.topk_softmax(g["logits"], k, renorm, bias=g["bias"], is_padding=g["pad"])
+    assert torch.equal(i, g["ib"]) and torch.equal(w, g["wb"])
+    w, i = O.topk_sigmoid(g["logits"], k, renorm, bias=g["bias"], routed_scaling_factor=2.5)
+    assert torch.equal(i, g["is_"]) and torch.equal(w, g["ws"])
+
+
+@pytest.mark.parametrize("name", _names("grouped_"))
+def test_grouped_topk_matches_reference(name):
+    g = load_golden(name)
+    logits = as_bf16(g["logits"]) if name == "grouped_bf16" else g["logits"]
+    renorm = bool(g.get("renorm", True))
+    w, i = O.grouped_topk(logits, g["k"], renorm, g["ng"], g["tg"], "sigmoid", 2.5, g["bias"])
+    assert torch.equal(i, g["i"]) and torch.equal(w, g["w"])
+    if "i_softmax" in g:
+        w, i = O.grouped_topk(logits, g["k"], renorm, g["ng"], g["tg"], "softmax", 1.0, g["bias"])
+        assert torch.equal(i, g["i_softmax"]) and torch.equal(w, g["w_softmax"])
+
+
+@pytest.mark.parametrize("name", _names("align_"))
+def test_align_matches_reference(name):
+    g = load_golden(name)
+    s, e, n = O.moe_align_block_size(g["ids"], g["bs"], g["E"])
+    assert torch.equal(s, g["sorted"]) and torch.equal(e, g["experts"]) and torch.equal(n, g["total"])
+    s, e, n = O.moe_align_block_size(g["ids"], g["bs"], g["E"], expert_map=g["emap"])
+    assert torch.equal(s, g["sorted_m"]) and torch.equal(e, g["experts_m"]) and torch.equal(n, g["total_m"])
+
+
+def test_align_documented_example():
+    # tests/ops/moe_align_block_size_ops.py:56-69 of the reference, shifted to
+    # zero-based expert ids (its 1..4 are experts 0..3 of 4 here).
+    ids = torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]], dtype=torch.int32) - 1
+    s, e, n = O.moe_align_block_size(ids, 4, 4)
+    assert s[:16].tolist() == [3, 6, 9, 12, 0, 4, 10, 12, 1, 7, 11, 12, 2, 5, 8, 12]
+    assert e[:4].tolist() == [0, 1, 2, 3] and n.item() == 16
+
+
+@pytest.mark.parametrize("name", _names("remap_"))
+def test_remap_and_gather_match_reference(name):
+    g = load_golden(name)
+    hs = as_bf16(g["hs"])
+    emap = g.get("emap")
+    out, _, rows, rmap = O.remap_hidden_states(hs, None, g["ids"], emap, g["E_loc"])
+    n = int(rows.sum())
+    assert torch.equal(rows, g["rows"]) and torch.equal(rmap, g["rmap"])
+    assert torch.equal(out[:n].view(torch.int16), g["out"][:n])
+    gout = O.moe_gather(as_bf16(g["y"]), g["w"], g["rmap"])
+    assert torch.equal(gout.view(torch.int16), g["gout"])
+
+
+def test_activations_match_reference():
+    g = load_golden("act")
+    x = as_bf16(g["x"])
+    assert torch.equal(O.silu_and_mul(x).view(torch.int16), g["silu"])
+    assert torch.equal(O.swigluoai_and_mul(x).view(torch.int16), g["oai"])
+
+
+def test_fp8_group_quant_matches_reference():
+    g = load_golden("fp8_group")
+    # the reference test oracle divides by the scale and has no lower clamp on
+    # the scale beyond eps; same formula otherwise
+    q, s = O.per_token_group_fp8_quant(g["x"], 128, divide=True)
+    assert torch.allclose(s, g["s"], rtol=0, atol=0)
+    assert torch.equal(q.view(torch.uint8), g["q"])
+    # the operator multiplies by the reciprocal: same scales, values within one code
+    q2, s2 = O.per_token_group_fp8_quant(g["x"], 128)
+    assert torch.equal(s2, s)
+    assert (q2.float() - q.float()).abs().max() <= 32.0
+    assert (q2.view(torch.uint8) != g["q"]).float().mean() < 0.01
+
+
+def test_mxfp4_matches_reference():
+    g = load_golden("mxfp4_ref")
+    x = as_bf16(g["x"])
+    packed, s = O.per_token_group_quant_mxfp4(x)
+    # scales: the reference's e8m0 byte b means 2^(b-127)
+    assert torch.equal(s, torch.exp2(g["s"].float() - 127.0))
+    # codes differ from round-to-nearest-even only at exact midpoints
+    deq = O.unpack_e2m1(packed).view(16, -1, 32) * s.unsqueeze(-1)
+    assert (deq.view(16, -1) - g["deq"]).abs().max() <= 0.5 * s.max()
+    assert (packed != g["q"]).float().mean() < 0.05
+    # the weight quantiser used for synthetic data is round-to-nearest-even like the reference
+    wq, ws = O.quant_mxfp4_weight(x.float())
+    assert torch.equal(ws, g["s"]) and torch.equal(wq, g["q"])
+    assert torch.equal(O.dequant_mxfp4(wq, ws), g["deq"])
+
+
+def test_e2m1_code_points():
+    # tests/test_mxfp4_quant.py:113-142 of the reference: every representable value maps to itself
+    vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    assert O.e2m1_code(vals).tolist() == list(range(8))
+    assert O.e2m1_code(-vals[1:]).tolist() == [c + 8 for c in range(1, 8)]
+    assert torch.equal(O.unpack_e2m1(torch.tensor([[0x21]], dtype=torch.uint8)), torch.tensor([[0.5, 1.0]]))
+
+
+def test_fp8_block_weight_dequant_matches_reference():
+    g = load_golden("fp8_block_w")
+    w = g["w"].view(torch.float8_e4m3fn)
+    assert torch.equal(O.dequant_fp8_block(w, g["s"]), g["deq"])
+
+
+def test_layer_matches_reference():
+    g = load_golden("layer_bf16")
+    x, w13, w2 = as_bf16(g["x"]), as_bf16(g["w13"]), as_bf16(g["w2"])
+    out = O.fused_moe("bf16", x, w13.transpose(1, 2).contiguous(), None, None,
+                      w2.transpose(1, 2).contiguous(), None, None, g["tw"], g["ti"], "silu")
+    ref = as_bf16(g["out"]).float()
+    # the reference rounds each expert's output and the weights to bf16 before summing
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def test_token_expert_indices():
+    assert O.token_expert_indices(3, 2).tolist() == [[0, 3], [1, 4], [2, 5]]
+
+
+def test_init_expert_map():
+    assert O.init_expert_map(2, 1, 3).tolist() == [-1, -1, 0, 1, -1, -1]

@@ -1,0 +1,837 @@
+// Grouped GEMM of the fused-MoE layer on the Blackwell tensor cores.
+//
+//   D[rows of expert e, :] = A[rows of expert e, :] * B_e (+ bias_e)
+//
+// One persistent, warp-specialised CTA per SM:
+//   warp 0      TMA producer: 128-byte-swizzled tiles of A and B into a ring of
+//               shared-memory stages, one mbarrier pair per stage;
+//   warp 1      owns tensor memory and issues tcgen05.mma (one elected lane);
+//   warps 2..   read accumulators out of tensor memory (tcgen05.ld), apply
+//               scales / bias / the gated activation and store rows.
+// Every role walks the same static tile sequence (tile = blockIdx.x + i*grid),
+// so no tile index is passed between warps.  Expert row ranges come from
+// rows_per_expert on the device: each CTA prefix-sums it into shared memory and
+// finds a tile's expert by binary search, so there is no host sync, no helper
+// launch and no per-call workspace.  M tiles start at the expert's first row;
+// rows past the expert's end are loaded (they belong to the next expert or are
+// zero-filled by TMA) but never stored.
+//
+// FP8 with 128x128 fp32 weight scales and per-row-per-128 activation scales
+// cannot be folded into the MMA, so for that recipe the MMA warp writes one
+// partial accumulator per 128 of K into a ring of tensor-memory buffers and the
+// reader warps add scale * partial into fp32 registers while the next partial
+// is being computed.
+//
+// All waits are bounded: a wait that runs out of budget raises a CTA-wide abort
+// flag, records B200MOE_TIMEOUT in a device status word and the CTA tears down
+// (frees tensor memory) instead of hanging.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace b200moe {
+
+__device__ int g_device_status = 0;
+
+namespace {
+
+using namespace sm100;
+
+constexpr int BM = 128;
+constexpr int kStageRowBytes = 128;  // one swizzle row: 64 bf16 or 128 fp8 along the box's inner dim
+constexpr int kMaxExpertsSmem = 1024;
+constexpr int kSwizzleGroupM = 8;
+
+enum : int { KIND_F16 = 0, KIND_F8 = 1 };
+
+struct GemmParams {
+  const float* a_scale;
+  const float* b_scale;
+  const void* bias;
+  int bias_dtype;
+  void* D;
+  float* d_scale;
+  int d_dtype;
+  const int32_t* rows_per_expert;
+  int64_t R;
+  int N, K, E;
+  int ldd;     // row stride of D in elements
+  int ab_fmt;  // operand format code of the instruction descriptor
+  float alpha, limit;
+};
+
+struct TileCoord {
+  int expert;
+  int row_start;   // first row of A / D
+  int rows_valid;  // rows of this tile that belong to the expert
+  int n_tile;
+};
+
+struct Schedule {
+  int tile_prefix[kMaxExpertsSmem + 1];
+  int row_prefix[kMaxExpertsSmem + 1];
+  int num_experts;
+  int n_tiles;
+};
+
+// Prefix sums of rows and of M tiles per expert, by warp 0 of the CTA.
+__device__ __forceinline__ void build_schedule(Schedule& s, const int32_t* rows_per_expert, int E,
+                                               int64_t R, int n_tiles) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int tile_run = 0;
+    long long row_run = 0;
+    for (int base = 0; base < E; base += 32) {
+      const int e = base + lane;
+      long long rows = e < E ? rows_per_expert[e] : 0;
+      if (rows < 0) rows = 0;
+      long long incl_rows = rows;
+      int tiles = static_cast<int>((rows + BM - 1) / BM);
+      int incl_tiles = tiles;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const long long r = __shfl_up_sync(0xffffffffu, incl_rows, off);
+        const int t = __shfl_up_sync(0xffffffffu, incl_tiles, off);
+        if (lane >= off) {
+          incl_rows += r;
+          incl_tiles += t;
+        }
+      }
+      if (e < E) {
+        long long rs = row_run + incl_rows - rows;
+        s.row_prefix[e] = static_cast<int>(rs < R ? rs : R);
+        s.tile_prefix[e] = tile_run + incl_tiles - tiles;
+      }
+      row_run += __shfl_sync(0xffffffffu, incl_rows, 31);
+      tile_run += __shfl_sync(0xffffffffu, incl_tiles, 31);
+    }
+    if (lane == 0) {
+      s.row_prefix[E] = static_cast<int>(row_run < R ? row_run : R);
+      s.tile_prefix[E] = tile_run;
+      s.num_experts = E;
+      s.n_tiles = n_tiles;
+    }
+  }
+}
+
+__device__ __forceinline__ int total_tiles(const Schedule& s) {
+  return s.tile_prefix[s.num_experts] * s.n_tiles;
+}
+
+// Tile t -> coordinates.  M tiles are visited in groups of kSwizzleGroupM with
+// the M index fastest, so a weight tile is reused by neighbouring CTAs while it
+// is still in L2.
+__device__ __forceinline__ TileCoord decode_tile(const Schedule& s, int t) {
+  const int mt = s.tile_prefix[s.num_experts];
+  const int per_group = kSwizzleGroupM * s.n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * kSwizzleGroupM;
+  const int gsize = (mt - first_m) < kSwizzleGroupM ? (mt - first_m) : kSwizzleGroupM;
+  const int within = t - g * per_group;
+  const int m = first_m + within % gsize;
+  TileCoord c;
+  c.n_tile = within / gsize;
+  int lo = 0, hi = s.num_experts;  // largest e with tile_prefix[e] <= m
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (s.tile_prefix[mid] <= m) lo = mid; else hi = mid;
+  }
+  c.expert = lo;
+  const int local = m - s.tile_prefix[lo];
+  const int rows_e = s.row_prefix[lo + 1] - s.row_prefix[lo];
+  c.row_start = s.row_prefix[lo] + local * BM;
+  const int left = rows_e - local * BM;
+  c.rows_valid = left < BM ? (left < 0 ? 0 : left) : BM;
+  return c;
+}
+
+__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+
+__device__ __forceinline__ float swiglu_oai_f32(float g, float u, float alpha, float limit) {
+  g = fminf(g, limit);
+  u = fmaxf(fminf(u, limit), -limit);
+  return (u + 1.0f) * (g * (1.0f / (1.0f + expf(-g * alpha))));
+}
+
+__device__ __forceinline__ float load_bias(const void* bias, int dtype, int64_t i) {
+  if (dtype == B200MOE_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[i]);
+  if (dtype == B200MOE_F16) return __half2float(reinterpret_cast<const __half*>(bias)[i]);
+  return reinterpret_cast<const float*>(bias)[i];
+}
+
+// Stores `n` (multiple of 8) fp32 values as 16-bit elements with 16-byte stores.
+template <int NV>
+__device__ __forceinline__ void store_row16(void* D, int d_dtype, int64_t elem_off,
+                                            const float (&v)[NV], int n_valid) {
+  if (d_dtype == B200MOE_BF16) {
+    __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(D) + elem_off;
+#pragma unroll
+    for (int i = 0; i < NV; i += 8) {
+      if (i + 8 <= n_valid) {
+        Vec<__nv_bfloat16, 8> o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16_rn(v[i + j]);
+        *reinterpret_cast<Vec<__nv_bfloat16, 8>*>(p + i) = o;
+      } else {
+        for (int j = 0; j < 8; ++j)
+          if (i + j < n_valid) p[i + j] = __float2bfloat16_rn(v[i + j]);
+      }
+    }
+  } else {
+    __half* p = reinterpret_cast<__half*>(D) + elem_off;
+#pragma unroll
+    for (int i = 0; i < NV; i += 8) {
+      if (i + 8 <= n_valid) {
+        Vec<__half, 8> o;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o.v[j] = __float2half_rn(v[i + j]);
+        *reinterpret_cast<Vec<__half, 8>*>(p + i) = o;
+      } else {
+        for (int j = 0; j < 8; ++j)
+          if (i + j < n_valid) p[i + j] = __float2half_rn(v[i + j]);
+      }
+    }
+  }
+}
+
+template <int KIND_, bool B_MN_MAJOR_, bool PROMOTE_, int BN_, int EPI_, int STAGES_>
+struct Config {
+  static constexpr int KIND = KIND_;
+  static constexpr bool B_MN_MAJOR = B_MN_MAJOR_;
+  static constexpr bool PROMOTE = PROMOTE_;
+  static constexpr int BN = BN_;
+  static constexpr int EPI = EPI_;
+  static constexpr int STAGES = STAGES_;
+  static constexpr int ELT = KIND == KIND_F16 ? 2 : 1;
+  static constexpr int BK = kStageRowBytes / ELT;       // elements of K per stage
+  static constexpr int UMMA_K = 32 / ELT;                // K per MMA instruction
+  static constexpr int A_BYTES = BM * kStageRowBytes;
+  static constexpr int B_BYTES = BN * kStageRowBytes;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int CHUNK_COLS = kStageRowBytes / ELT;  // N columns per MN-major TMA box
+  static constexpr int N_CHUNKS = BN / CHUNK_COLS;
+  static constexpr int ACC_BUFS = PROMOTE ? (512 / BN) : 2;
+  static constexpr int TMEM_COLS = ACC_BUFS * BN;        // 256 or 512
+  static constexpr int EPI_WARPS = BN / 32 >= 8 ? 8 : 4;
+  static constexpr int THREADS = 64 + EPI_WARPS * 32;
+  static constexpr int COLS_PER_THREAD = BN / (EPI_WARPS / 4);
+  static constexpr bool GATED_SPLIT = EPI == B200MOE_EPI_SILU_MUL;  // tile = [gate half | up half]
+  static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES;
+  static_assert(!(GATED_SPLIT && EPI_WARPS == 8), "split gated tiles are laid out for 4 reader warps");
+  static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && N_CHUNKS < 2), "a split gated tile needs two weight boxes");
+  static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed by the tensor-memory allocation");
+};
+
+struct alignas(8) Barriers {
+  uint64_t full[8];
+  uint64_t empty[8];
+  uint64_t tfull[4];
+  uint64_t tempty[4];
+};
+
+template <typename C>
+__global__ void __launch_bounds__(C::THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ Schedule sched;
+  __shared__ Barriers bars;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = C::GATED_SPLIT ? (p.N / 2 + C::BN / 2 - 1) / (C::BN / 2)
+                                     : (p.N + C::BN - 1) / C::BN;
+  const int num_kb = (p.K + C::BK - 1) / C::BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&bars.full[s], 1);
+      mbar_init(&bars.empty[s], 1);
+    }
+    for (int b = 0; b < C::ACC_BUFS; ++b) {
+      mbar_init(&bars.tfull[b], 1);
+      mbar_init(&bars.tempty[b], C::EPI_WARPS);
+    }
+    mbar_fence_init();
+    prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  build_schedule(sched, p.rows_per_expert, p.E, p.R, n_tiles);
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+  const int num_tiles = total_tiles(sched);
+  volatile int* abort_p = &abort_flag;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = decode_tile(sched, t);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(&bars.empty[stage], phase ^ 1u, abort_p);
+          if (!ok) break;
+          uint8_t* a_dst = tiles + stage * C::STAGE_BYTES;
+          uint8_t* b_dst = a_dst + C::A_BYTES;
+          mbar_arrive_expect_tx(&bars.full[stage], C::STAGE_BYTES);
+          tma_load_2d(a_dst, &map_a, &bars.full[stage], kb * C::BK, tc.row_start);
+          if constexpr (C::B_MN_MAJOR) {
+#pragma unroll
+            for (int c = 0; c < C::N_CHUNKS; ++c) {
+              int col;
+              if constexpr (C::GATED_SPLIT) {
+                const int half = C::N_CHUNKS / 2;
+                col = (c < half ? 0 : p.N / 2) + tc.n_tile * (C::BN / 2) + (c % half) * C::CHUNK_COLS;
+              } else {
+                col = tc.n_tile * C::BN + c * C::CHUNK_COLS;
+              }
+              tma_load_3d(b_dst + c * (C::BK * kStageRowBytes), &map_b, &bars.full[stage], col,
+                          kb * C::BK, tc.expert);
+            }
+          } else {
+            if (C::GATED_SPLIT) {
+              tma_load_3d(b_dst, &map_b, &bars.full[stage], kb * C::BK, tc.n_tile * (C::BN / 2),
+                          tc.expert);
+              tma_load_3d(b_dst + (C::BN / 2) * kStageRowBytes, &map_b, &bars.full[stage],
+                          kb * C::BK, p.N / 2 + tc.n_tile * (C::BN / 2), tc.expert);
+            } else {
+              tma_load_3d(b_dst, &map_b, &bars.full[stage], kb * C::BK, tc.n_tile * C::BN,
+                          tc.expert);
+            }
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(p.ab_fmt, p.ab_fmt, 0u, C::B_MN_MAJOR ? 1u : 0u, BM, C::BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t buf_phase = 0;
+      bool ok = true;
+      const int phases_per_tile = C::PROMOTE ? num_kb : 1;
+      const int kb_per_phase = C::PROMOTE ? 1 : num_kb;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
+          ok = mbar_wait(&bars.tempty[buf], buf_phase ^ 1u, abort_p);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + buf * C::BN;
+          for (int kb = 0; kb < kb_per_phase && ok; ++kb) {
+            ok = mbar_wait(&bars.full[stage], phase, abort_p);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+            const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < C::BK / C::UMMA_K; ++kk) {
+              const uint64_t a_desc = make_sdesc_sw128(a_addr + kk * 32, 16, 1024);
+              const uint64_t b_desc =
+                  C::B_MN_MAJOR
+                      ? make_sdesc_sw128(b_addr + kk * C::UMMA_K * kStageRowBytes,
+                                         C::BK * kStageRowBytes, 1024)
+                      : make_sdesc_sw128(b_addr + kk * 32, 16, 1024);
+              const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
+              if (C::KIND == KIND_F16) mma_f16(d_tmem, a_desc, b_desc, idesc, acc);
+              else mma_f8(d_tmem, a_desc, b_desc, idesc, acc);
+            }
+            mma_commit(&bars.empty[stage]);
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) mma_commit(&bars.tfull[buf]);
+          if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ---------------- accumulator readers / epilogue ----------------
+    const int ew = warp - 2;
+    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int col_group = C::EPI_WARPS == 8 ? (ew >> 2) : 0;
+    const int row_in_tile = quad * 32 + lane;
+    constexpr int CPT = C::COLS_PER_THREAD;
+    constexpr int NCH = CPT / 32;
+    int buf = 0;
+    uint32_t buf_phase = 0;
+    bool ok = true;
+    const int phases_per_tile = C::PROMOTE ? num_kb : 1;
+    const int nb_count = p.N / 128;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const TileCoord tc = decode_tile(sched, t);
+      const bool row_ok = row_in_tile < tc.rows_valid;
+      const int64_t grow = static_cast<int64_t>(tc.row_start) + row_in_tile;
+      // Column of the full-N problem that TMEM column (col_group*CPT + j) holds.
+      // For the split gated tile the first BN/2 TMEM columns are gate columns
+      // and the second half the matching up columns.
+      float acc[C::PROMOTE ? CPT : 1];
+      if constexpr (C::PROMOTE) {
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+      }
+      const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+
+      for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
+        ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t_addr = tmem_base + lane_addr + buf * C::BN + col_group * CPT;
+        if constexpr (C::PROMOTE) {
+          const float sa = row_ok ? p.a_scale[grow * num_kb + ph] : 0.f;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            // 128-column weight-scale block of this chunk
+            int gcol;
+            const int tcol = col_group * CPT + c * 32;
+            if (C::GATED_SPLIT)
+              gcol = (tcol < C::BN / 2 ? 0 : p.N / 2 - C::BN / 2) + tc.n_tile * (C::BN / 2) + tcol;
+            else
+              gcol = tc.n_tile * C::BN + tcol;
+            const int nb = gcol / 128 < nb_count ? gcol / 128 : nb_count - 1;
+            const float sb =
+                p.b_scale[(static_cast<int64_t>(tc.expert) * num_kb + ph) * nb_count + nb];
+            const float s = sa * sb;
+            float v[32];
+            tmem_ld_32x32(t_addr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, v[j], acc[c * 32 + j]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.tempty[buf]);
+        }
+        if (!C::PROMOTE || ph == phases_per_tile - 1) {
+          // ---- final epilogue of the tile ----
+          auto get_chunk = [&](int c, float (&v)[32]) {
+            if constexpr (C::PROMOTE) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
+            } else {
+              tmem_ld_32x32(t_addr + c * 32, v);
+              tmem_ld_wait();
+            }
+          };
+          if constexpr (C::EPI == B200MOE_EPI_STORE) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              float v[32];
+              get_chunk(c, v);
+              const int col0 = tc.n_tile * C::BN + col_group * CPT + c * 32;
+              if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N)
+                    v[j] += load_bias(p.bias, p.bias_dtype,
+                                      static_cast<int64_t>(tc.expert) * p.N + col0 + j);
+              }
+              if (row_ok && col0 < p.N)
+                store_row16<32>(p.D, p.d_dtype, grow * p.ldd + col0, v, p.N - col0);
+            }
+          } else if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
+            // this thread: gate columns [0, CPT/2) and up columns [CPT/2, CPT) of its group
+            constexpr int HALF_CH = NCH / 2;
+            const int half_n = p.N / 2;
+#pragma unroll
+            for (int c = 0; c < HALF_CH; ++c) {
+              float g[32], u[32];
+              get_chunk(c, g);
+              get_chunk(c + HALF_CH, u);
+              const int col0 = tc.n_tile * (C::BN / 2) + c * 32;
+              if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < half_n) {
+                    g[j] += load_bias(p.bias, p.bias_dtype,
+                                      static_cast<int64_t>(tc.expert) * p.N + col0 + j);
+                    u[j] += load_bias(p.bias, p.bias_dtype,
+                                      static_cast<int64_t>(tc.expert) * p.N + half_n + col0 + j);
+                  }
+              }
+#pragma unroll
+              for (int j = 0; j < 32; ++j) g[j] = silu_f32(g[j]) * u[j];
+              if (row_ok && col0 < half_n)
+                store_row16<32>(p.D, p.d_dtype, grow * p.ldd + col0, g, half_n - col0);
+            }
+          } else {  // SWIGLU_OAI: (gate, up) pairs are adjacent columns
+#pragma unroll
+            for (int c = 0; c < NCH; ++c) {
+              float v[32];
+              get_chunk(c, v);
+              const int col0 = tc.n_tile * C::BN + col_group * CPT + c * 32;
+              if (p.bias) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N)
+                    v[j] += load_bias(p.bias, p.bias_dtype,
+                                      static_cast<int64_t>(tc.expert) * p.N + col0 + j);
+              }
+              float o[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                o[j] = swiglu_oai_f32(v[2 * j], v[2 * j + 1], p.alpha, p.limit);
+              if (row_ok && col0 < p.N)
+                store_row16<16>(p.D, p.d_dtype, grow * p.ldd + col0 / 2, o, (p.N - col0) / 2);
+            }
+          }
+          if (!C::PROMOTE) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars.tempty[buf]);
+          }
+        }
+        if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    if (threadIdx.x == 0) atomicExch(&g_device_status, B200MOE_TIMEOUT);
+    // Let copies that are still in flight land before shared memory is released.
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+CUtensorMapDataType tm_dtype(int dtype) {
+  switch (dtype) {
+    case B200MOE_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    case B200MOE_F16: return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    default: return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  }
+}
+
+// Row-major [rows, cols] (2-D) or [batch, rows, cols] (3-D) tensor, box of
+// `box_cols` x `box_rows` elements, 128-byte swizzle, zero fill out of bounds.
+int make_map(CUtensorMap* map, int dtype, const void* base, uint64_t cols, uint64_t rows,
+             uint64_t batch, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return B200MOE_CUDA_ERROR;
+  const uint64_t elt = dtype_size(dtype);
+  cuuint64_t dims[3] = {cols, rows, batch ? batch : 1};
+  cuuint64_t strides[2] = {cols * elt, cols * rows * elt};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint32_t rank = batch ? 3 : 2;
+  CUresult r = fn(map, tm_dtype(dtype), rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled", cudaErrorInvalidValue);
+    return B200MOE_CUDA_ERROR;
+  }
+  return B200MOE_OK;
+}
+
+template <typename C>
+int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaStream_t st) {
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, a.a_dtype, a.A, a.K, a.R, 0, C::BK, BM);
+  if (rc != B200MOE_OK) return rc;
+  if (C::B_MN_MAJOR)
+    rc = make_map(&map_b, b_dtype, B, a.N, a.K, a.E, C::CHUNK_COLS, C::BK);
+  else
+    rc = make_map(&map_b, b_dtype, B, a.K, a.N, a.E, C::BK, C::GATED_SPLIT ? C::BN / 2 : C::BN);
+  if (rc != B200MOE_OK) return rc;
+
+  GemmParams p;
+  p.a_scale = a.a_scale;
+  p.b_scale = reinterpret_cast<const float*>(a.b_scale);
+  p.bias = a.bias;
+  p.bias_dtype = a.bias_dtype;
+  p.D = a.D;
+  p.d_scale = a.d_scale;
+  p.d_dtype = a.d_dtype;
+  p.rows_per_expert = a.rows_per_expert;
+  p.R = a.R;
+  p.N = a.N;
+  p.K = a.K;
+  p.E = a.E;
+  p.ldd = a.epilogue == B200MOE_EPI_STORE ? a.N : a.N / 2;
+  p.alpha = a.alpha;
+  p.limit = a.limit;
+  p.ab_fmt = a.a_dtype == B200MOE_BF16 ? 1 : 0;  // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
+
+  static bool attr_set = false;  // per template instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<C>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(C::SMEM_BYTES));
+    if (e != cudaSuccess) {
+      set_last_error("cudaFuncSetAttribute", e);
+      return B200MOE_CUDA_ERROR;
+    }
+    attr_set = true;
+  }
+  const int n_tiles = C::GATED_SPLIT ? (a.N / 2 + C::BN / 2 - 1) / (C::BN / 2)
+                                     : (a.N + C::BN - 1) / C::BN;
+  const int64_t max_m_tiles = (a.R + BM - 1) / BM + a.E;
+  int64_t grid = max_m_tiles * n_tiles;
+  if (grid > kNumSMs) grid = kNumSMs;
+  if (grid < 1) grid = 1;
+  grouped_gemm_kernel<C><<<static_cast<int>(grid), C::THREADS, C::SMEM_BYTES, st>>>(map_a, map_b, p);
+  return launch_status("grouped_gemm_kernel");
+}
+
+// ---- CUDA-core evaluation of the same contract (checking aid) --------------------------
+
+__global__ void gemm_check_kernel(b200moe_gemm_args a, int b_layout_nk) {
+  // one thread per (row, col); expert of the row by linear scan
+  const int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (idx >= a.R * a.N) return;
+  const int64_t row = idx / a.N;
+  const int col = static_cast<int>(idx % a.N);
+  int e = -1;
+  int64_t off = 0;
+  for (int i = 0; i < a.E; ++i) {
+    const int64_t n = a.rows_per_expert[i];
+    if (row < off + n) { e = i; break; }
+    off += n;
+  }
+  if (e < 0) return;
+  float acc = 0.f;
+  const int nkb = a.K / 128;
+  for (int k = 0; k < a.K; ++k) {
+    float av;
+    if (a.a_dtype == B200MOE_E4M3) {
+      av = e4m3_to_f32(reinterpret_cast<const uint8_t*>(a.A)[row * a.K + k]);
+      if (a.a_scale) av *= a.a_scale[row * nkb + k / 128];
+    } else if (a.a_dtype == B200MOE_BF16) {
+      av = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.A)[row * a.K + k]);
+    } else {
+      av = __half2float(reinterpret_cast<const __half*>(a.A)[row * a.K + k]);
+    }
+    float bv;
+    if (a.recipe == B200MOE_RECIPE_BF16) {
+      const int64_t at = b_layout_nk ? (static_cast<int64_t>(e) * a.N + col) * a.K + k
+                                     : (static_cast<int64_t>(e) * a.K + k) * a.N + col;
+      bv = a.a_dtype == B200MOE_F16 ? __half2float(reinterpret_cast<const __half*>(a.B)[at])
+                                    : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(a.B)[at]);
+    } else if (a.recipe == B200MOE_RECIPE_FP8_BLOCK) {
+      bv = e4m3_to_f32(reinterpret_cast<const uint8_t*>(a.B)[(static_cast<int64_t>(e) * a.K + k) * a.N + col]);
+      bv *= reinterpret_cast<const float*>(a.b_scale)[(static_cast<int64_t>(e) * nkb + k / 128) * (a.N / 128) + col / 128];
+    } else {
+      const uint8_t byte = reinterpret_cast<const uint8_t*>(a.B)[(static_cast<int64_t>(e) * a.N + col) * (a.K / 2) + k / 2];
+      const int code = (k & 1) ? (byte >> 4) : (byte & 0xF);
+      const float mag[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+      bv = (code & 8) ? -mag[code & 7] : mag[code & 7];
+      const uint8_t sc = reinterpret_cast<const uint8_t*>(a.b_scale)[(static_cast<int64_t>(e) * a.N + col) * (a.K / 32) + k / 32];
+      bv *= exp2f(static_cast<float>(sc) - 127.f);
+    }
+    acc = fmaf(av, bv, acc);
+  }
+  if (a.bias) acc += load_bias(a.bias, a.bias_dtype, static_cast<int64_t>(e) * a.N + col);
+  if (a.d_dtype == B200MOE_F32) reinterpret_cast<float*>(a.D)[idx] = acc;
+  else if (a.d_dtype == B200MOE_BF16) reinterpret_cast<__nv_bfloat16*>(a.D)[idx] = __float2bfloat16_rn(acc);
+  else reinterpret_cast<__half*>(a.D)[idx] = __float2half_rn(acc);
+}
+
+// ---- weight dequantisation to 16-bit (compatibility paths) ------------------------------
+
+__global__ void dequant_fp8_block_kernel(const uint8_t* __restrict__ w, const float* __restrict__ s,
+                                         __nv_bfloat16* __restrict__ out, int64_t E, int K, int N) {
+  const int64_t total = E * K * static_cast<int64_t>(N) / 8;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t at = i * 8;
+    const int col = static_cast<int>(at % N);
+    const int64_t ek = at / N;
+    const int k = static_cast<int>(ek % K);
+    const int64_t e = ek / K;
+    const float sc = s[(e * (K / 128) + k / 128) * (N / 128) + col / 128];
+    const uint2 raw = *reinterpret_cast<const uint2*>(w + at);
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+    Vec<__nv_bfloat16, 8> o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o.v[j] = __float2bfloat16_rn(e4m3_to_f32(b[j]) * sc);
+    *reinterpret_cast<Vec<__nv_bfloat16, 8>*>(out + at) = o;
+  }
+}
+
+// [E,N,K/2] e2m1 pairs + [E,N,K/32] e8m0 -> [E,N,K] bf16 (exact: every product
+// of an e2m1 value and a power of two is a bf16 number).
+__global__ void dequant_mxfp4_kernel(const uint8_t* __restrict__ w, const uint8_t* __restrict__ s,
+                                     __nv_bfloat16* __restrict__ out, int64_t rows, int K) {
+  const int64_t total = rows * (K / 8);
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t row = i / (K / 8);
+    const int k0 = static_cast<int>(i % (K / 8)) * 8;
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(w + row * (K / 2) + k0 / 2);
+    const float sc = exp2f(static_cast<float>(s[row * (K / 32) + k0 / 32]) - 127.f);
+    Vec<__nv_bfloat16, 8> o;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int code = (raw >> (4 * j)) & 0xF;
+      const int m = code & 7;
+      float mag = m < 4 ? 0.5f * m : (m == 4 ? 2.f : (m == 5 ? 3.f : (m == 6 ? 4.f : 6.f)));
+      o.v[j] = __float2bfloat16_rn((code & 8) ? -mag * sc : mag * sc);
+    }
+    *reinterpret_cast<Vec<__nv_bfloat16, 8>*>(out + row * K + k0) = o;
+  }
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+static int validate(const b200moe_gemm_args* a) {
+  if (!a) return B200MOE_INVALID_ARG;
+  if (a->R < 0 || a->N <= 0 || a->K <= 0 || a->E <= 0 || a->E > kMaxExpertsSmem) return B200MOE_INVALID_ARG;
+  if (a->N % 8 != 0) return B200MOE_INVALID_ARG;
+  if (a->R == 0) return B200MOE_OK;
+  if (!a->A || !a->B || !a->D || !a->rows_per_expert) return B200MOE_INVALID_ARG;
+  if (a->R >= (1ll << 31)) return B200MOE_UNSUPPORTED;
+  return B200MOE_OK;
+}
+
+extern "C" size_t b200moe_grouped_gemm_workspace_bytes(const b200moe_gemm_args* a) {
+  if (!a) return 0;
+  const size_t full = static_cast<size_t>(a->E) * a->N * a->K * 2;
+  if (a->recipe == B200MOE_RECIPE_MXFP4) return full;
+  if (a->recipe == B200MOE_RECIPE_FP8_BLOCK && a->a_dtype != B200MOE_E4M3) return full;
+  return 0;
+}
+
+extern "C" int b200moe_dequant_weights(int recipe, const void* B, const void* b_scale, void* out,
+                                       int E, int N, int K, void* stream) {
+  if (!B || !b_scale || !out || E <= 0 || N <= 0 || K <= 0) return B200MOE_INVALID_ARG;
+  cudaStream_t st = as_stream(stream);
+  const int grid = kNumSMs * 8;
+  if (recipe == B200MOE_RECIPE_FP8_BLOCK) {
+    if (K % 128 || N % 128) return B200MOE_INVALID_ARG;
+    dequant_fp8_block_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint8_t*>(B),
+                                                   reinterpret_cast<const float*>(b_scale),
+                                                   reinterpret_cast<__nv_bfloat16*>(out), E, K, N);
+  } else if (recipe == B200MOE_RECIPE_MXFP4) {
+    if (K % 32) return B200MOE_INVALID_ARG;
+    dequant_mxfp4_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint8_t*>(B),
+                                               reinterpret_cast<const uint8_t*>(b_scale),
+                                               reinterpret_cast<__nv_bfloat16*>(out),
+                                               static_cast<int64_t>(E) * N, K);
+  } else {
+    return B200MOE_UNSUPPORTED;
+  }
+  return launch_status("dequant_weights");
+}
+
+template <int KIND, bool MN, bool PROMOTE, int BN, int STAGES>
+static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaStream_t st) {
+  switch (a.epilogue) {
+    case B200MOE_EPI_STORE:
+      return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, STAGES>>(a, B, b_dtype, st);
+    case B200MOE_EPI_SILU_MUL:
+      if constexpr (MN && BN * (KIND == KIND_F16 ? 2 : 1) < 256) return B200MOE_UNSUPPORTED;
+      else return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SILU_MUL, STAGES>>(a, B, b_dtype, st);
+    case B200MOE_EPI_SWIGLU_OAI:
+      return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SWIGLU_OAI, STAGES>>(a, B, b_dtype, st);
+    default:
+      return B200MOE_INVALID_ARG;
+  }
+}
+
+extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspace,
+                                    size_t workspace_bytes, void* stream) {
+  int rc = validate(args);
+  if (rc != B200MOE_OK || args->R == 0) return rc;
+  b200moe_gemm_args a = *args;
+  cudaStream_t st = as_stream(stream);
+  if (a.d_dtype != B200MOE_BF16 && a.d_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
+  if (a.epilogue != B200MOE_EPI_STORE && (a.N % 2 != 0)) return B200MOE_INVALID_ARG;
+
+  if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3) {
+    if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
+    if (a.epilogue == B200MOE_EPI_SILU_MUL) return B200MOE_UNSUPPORTED;
+    return launch_epi<KIND_F8, true, true, 128, 6>(a, a.B, B200MOE_E4M3, st);
+  }
+
+  // 16-bit activations: weights must be 16-bit too; quantised weights are
+  // expanded into the workspace first (slow path kept for API compatibility).
+  if (a.a_dtype != B200MOE_BF16 && a.a_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
+  const void* B = a.B;
+  bool b_nk = a.recipe == B200MOE_RECIPE_BF16 && a.b_layout == B200MOE_B_LAYOUT_NK;
+  if (a.recipe != B200MOE_RECIPE_BF16) {
+    if (a.a_dtype != B200MOE_BF16) return B200MOE_UNSUPPORTED;
+    const size_t need = b200moe_grouped_gemm_workspace_bytes(&a);
+    if (!workspace || workspace_bytes < need) return B200MOE_WORKSPACE_TOO_SMALL;
+    rc = b200moe_dequant_weights(a.recipe, a.B, a.b_scale, workspace, a.E, a.N, a.K, stream);
+    if (rc != B200MOE_OK) return rc;
+    B = workspace;
+    b_nk = a.recipe == B200MOE_RECIPE_MXFP4;
+  }
+  if (a.K % 8 != 0) return B200MOE_INVALID_ARG;
+  if (b_nk) return launch_epi<KIND_F16, false, false, 128, 6>(a, B, a.a_dtype, st);
+  return launch_epi<KIND_F16, true, false, 128, 6>(a, B, a.a_dtype, st);
+}
+
+extern "C" int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* stream) {
+  int rc = validate(args);
+  if (rc != B200MOE_OK || args->R == 0) return rc;
+  const int64_t total = args->R * args->N;
+  const bool b_nk = args->recipe == B200MOE_RECIPE_BF16 && args->b_layout == B200MOE_B_LAYOUT_NK;
+  gemm_check_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, as_stream(stream)>>>(*args, b_nk ? 1 : 0);
+  return launch_status("gemm_check_kernel");
+}
+
+extern "C" int b200moe_device_status(void* stream, int* status_host) {
+  if (!status_host) return B200MOE_INVALID_ARG;
+  cudaStream_t st = as_stream(stream);
+  int zero = 0;
+  cudaError_t e = cudaMemcpyFromSymbolAsync(status_host, g_device_status, sizeof(int), 0,
+                                            cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e == cudaSuccess && *status_host != 0)
+    e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+  if (e != cudaSuccess) {
+    set_last_error("device_status", e);
+    return B200MOE_CUDA_ERROR;
+  }
+  return B200MOE_OK;
+}

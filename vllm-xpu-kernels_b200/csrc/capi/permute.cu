@@ -1,0 +1,420 @@
+// Token permutation: moe_align_block_size, remap_hidden_states, init_expert_map.
+//
+// Both permutations are one stable counting sort of the flat (token, slot)
+// indices by expert, done with integers only so the result is reproducible and
+// equal to what a stable sort gives:
+//   1. count   — each CTA histograms a contiguous chunk of flat indices into
+//                 shared memory and writes its row of per-CTA counts;
+//   2. scan    — one CTA turns the [n_cta, E] counts into, for every
+//                 (cta, expert), the output position of that CTA's first
+//                 element of that expert (expert starts padded to the block
+//                 size for align), and writes the per-expert results;
+//   3. place   — each CTA walks its chunk again in index order; an element's
+//                 rank among equal experts comes from a warp match plus
+//                 per-warp running offsets, never from atomics.
+// Inputs that fit one chunk take a single fused launch.
+#include "common.cuh"
+
+namespace b200moe {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kChunk = 2048;  // flat indices per CTA: 8 warps x 8 steps x 32 lanes
+constexpr int kMaxExperts = 1024;
+
+struct GroupParams {
+  const void* ids;
+  int ids_dtype;
+  int64_t numel;
+  int num_keys;        // number of output groups' key space (experts before mapping for align)
+  int id_limit;        // ids >= id_limit are ignored
+  const int32_t* map;  // optional id -> key (remap) or id -> keep? (align)
+  int map_is_filter;   // 1: map only decides validity (align); 0: map gives the key (remap)
+  int block_size;      // padding unit of each group's run (1 = none)
+};
+
+__device__ __forceinline__ int key_of(const GroupParams& p, int64_t i) {
+  const int64_t id = load_index(p.ids, p.ids_dtype, i);
+  if (id < 0 || id >= p.id_limit) return -1;
+  if (p.map) {
+    const int m = p.map[id];
+    if (m < 0) return -1;
+    return p.map_is_filter ? static_cast<int>(id) : m;
+  }
+  return static_cast<int>(id);
+}
+
+// Histogram of this CTA's chunk into smem hist[num_keys].
+__device__ __forceinline__ void chunk_histogram(const GroupParams& p, int64_t base, int* hist) {
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads) hist[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < kChunk; i += kThreads) {
+    const int64_t idx = base + i;
+    if (idx < p.numel) {
+      const int key = key_of(p, idx);
+      if (key >= 0) atomicAdd(&hist[key], 1);  // integer counts: order does not matter
+    }
+  }
+  __syncthreads();
+}
+
+// Walks the chunk in index order.  warp w owns indices [w*256, w*256+256) of
+// the chunk; per-warp counts are prefix-summed across warps so that positions
+// follow ascending flat index.  `emit(idx, key, pos)` is called once per valid
+// element with pos = cta_base[key] + rank inside the CTA.
+template <typename Emit>
+__device__ __forceinline__ void chunk_place(const GroupParams& p, int64_t base,
+                                            const int* cta_base, int* warp_off, Emit emit) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kPerWarp = kChunk / kWarps;
+  for (int e = threadIdx.x; e < p.num_keys * kWarps; e += kThreads) warp_off[e] = 0;
+  __syncthreads();
+  int keys[kPerWarp / 32];
+#pragma unroll
+  for (int s = 0; s < kPerWarp / 32; ++s) {
+    const int64_t idx = base + warp * kPerWarp + s * 32 + lane;
+    keys[s] = idx < p.numel ? key_of(p, idx) : -1;
+    if (keys[s] >= 0) atomicAdd(&warp_off[warp * p.num_keys + keys[s]], 1);
+  }
+  __syncthreads();
+  // exclusive prefix over warps, per key
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads) {
+    int run = cta_base[e];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = warp_off[w * p.num_keys + e];
+      warp_off[w * p.num_keys + e] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  int* mine = warp_off + warp * p.num_keys;
+#pragma unroll
+  for (int s = 0; s < kPerWarp / 32; ++s) {
+    const int key = keys[s];
+    const unsigned peers = __match_any_sync(0xffffffffu, key);
+    if (key >= 0) {
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      const int pos = mine[key] + rank;
+      emit(base + warp * kPerWarp + s * 32 + lane, key, pos);
+    }
+    __syncwarp();
+    if (key >= 0 && lane == (31 - __clz(peers))) mine[key] += __popc(peers);
+    __syncwarp();
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) count_kernel(GroupParams p, int* __restrict__ counts) {
+  extern __shared__ int smem[];
+  chunk_histogram(p, static_cast<int64_t>(blockIdx.x) * kChunk, smem);
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads)
+    counts[static_cast<int64_t>(blockIdx.x) * p.num_keys + e] = smem[e];
+}
+
+// Per-key totals -> padded starts (exclusive scan over keys, any num_keys <=
+// 1024 by a block-wide scan of 1024 slots).  Returns this thread's key start
+// in `start` for key = threadIdx.x + 256*j via smem arrays.
+__device__ __forceinline__ void scan_keys(int num_keys, int block_size, const int* total,
+                                          int* start, int* grand_total) {
+  // total/start are smem arrays of kMaxExperts ints.  Sequential-in-warp scan:
+  // thread t handles 4 consecutive keys.
+  __shared__ int warp_sums[kWarps];
+  const int t = threadIdx.x;
+  int v[4], pad[4];
+  int local = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = t * 4 + j;
+    v[j] = e < num_keys ? total[e] : 0;
+    pad[j] = (v[j] + block_size - 1) / block_size * block_size;
+    local += pad[j];
+  }
+  int incl = local;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, off);
+    if ((t & 31) >= off) incl += o;
+  }
+  if ((t & 31) == 31) warp_sums[t >> 5] = incl;
+  __syncthreads();
+  int warp_base = 0;
+  for (int w = 0; w < (t >> 5); ++w) warp_base += warp_sums[w];
+  int run = warp_base + incl - local;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int e = t * 4 + j;
+    if (e < num_keys) start[e] = run;
+    run += pad[j];
+  }
+  if (t == kThreads - 1) *grand_total = run;
+  __syncthreads();
+}
+
+struct AlignOut {
+  int32_t* sorted_ids;
+  int64_t sorted_capacity;
+  int32_t* expert_ids;
+  int64_t blocks_capacity;
+  int32_t* total;
+  const int32_t* expert_map;
+};
+
+__device__ __forceinline__ void write_align_meta(const AlignOut& o, int num_keys, int block_size,
+                                                 const int* total, const int* start,
+                                                 int grand_total) {
+  for (int e = threadIdx.x; e < num_keys; e += kThreads) {
+    const int nb = (total[e] + block_size - 1) / block_size;
+    const int b0 = start[e] / block_size;
+    const int label = o.expert_map ? o.expert_map[e] : e;
+    for (int b = 0; b < nb; ++b)
+      if (b0 + b < o.blocks_capacity) o.expert_ids[b0 + b] = label;
+  }
+  for (int64_t b = grand_total / block_size + threadIdx.x; b < o.blocks_capacity; b += kThreads)
+    o.expert_ids[b] = 0;
+  if (threadIdx.x == 0) o.total[0] = grand_total;
+}
+
+// counts [n_cta, E] -> in place: position of each CTA's first element per key.
+__global__ void __launch_bounds__(kThreads) scan_kernel(GroupParams p, int n_cta,
+                                                        int* __restrict__ counts, AlignOut ao,
+                                                        int32_t* __restrict__ rows_per_key) {
+  __shared__ int total[kMaxExperts];
+  __shared__ int start[kMaxExperts];
+  __shared__ int grand;
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads) {
+    int run = 0;
+    for (int c = 0; c < n_cta; ++c) run += counts[static_cast<int64_t>(c) * p.num_keys + e];
+    total[e] = run;
+  }
+  __syncthreads();
+  scan_keys(p.num_keys, p.block_size, total, start, &grand);
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads) {
+    int run = start[e];
+    for (int c = 0; c < n_cta; ++c) {
+      const int64_t at = static_cast<int64_t>(c) * p.num_keys + e;
+      const int cnt = counts[at];
+      counts[at] = run;
+      run += cnt;
+    }
+    if (rows_per_key) rows_per_key[e] += total[e];
+  }
+  if (ao.sorted_ids) write_align_meta(ao, p.num_keys, p.block_size, total, start, grand);
+}
+
+__global__ void fill_kernel(int32_t* __restrict__ dst, int64_t n, int32_t value) {
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    dst[i] = value;
+}
+
+__global__ void __launch_bounds__(kThreads) place_align_kernel(GroupParams p,
+                                                               const int* __restrict__ bases,
+                                                               AlignOut ao) {
+  extern __shared__ int smem[];
+  int* cta_base = smem;
+  int* warp_off = smem + p.num_keys;
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads)
+    cta_base[e] = bases[static_cast<int64_t>(blockIdx.x) * p.num_keys + e];
+  __syncthreads();
+  chunk_place(p, static_cast<int64_t>(blockIdx.x) * kChunk, cta_base, warp_off,
+              [&](int64_t idx, int, int pos) {
+                if (pos < ao.sorted_capacity) ao.sorted_ids[pos] = static_cast<int32_t>(idx);
+              });
+}
+
+__global__ void __launch_bounds__(kThreads) place_remap_kernel(GroupParams p,
+                                                               const int* __restrict__ bases,
+                                                               int32_t* __restrict__ row_map) {
+  extern __shared__ int smem[];
+  int* cta_base = smem;
+  int* warp_off = smem + p.num_keys;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kChunk;
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads)
+    cta_base[e] = bases[static_cast<int64_t>(blockIdx.x) * p.num_keys + e];
+  for (int i = threadIdx.x; i < kChunk; i += kThreads)
+    if (base + i < p.numel) row_map[base + i] = -1;
+  __syncthreads();
+  chunk_place(p, base, cta_base, warp_off,
+              [&](int64_t idx, int, int pos) { row_map[idx] = pos; });
+}
+
+// Whole permutation in one CTA when numel <= kChunk.
+__global__ void __launch_bounds__(kThreads) fused_small_kernel(GroupParams p, AlignOut ao,
+                                                               int32_t* __restrict__ rows_per_key,
+                                                               int32_t* __restrict__ row_map) {
+  extern __shared__ int smem[];
+  __shared__ int total[kMaxExperts];
+  __shared__ int start[kMaxExperts];
+  __shared__ int grand;
+  int* warp_off = smem;
+  chunk_histogram(p, 0, total);
+  scan_keys(p.num_keys, p.block_size, total, start, &grand);
+  if (ao.sorted_ids) {
+    write_align_meta(ao, p.num_keys, p.block_size, total, start, grand);
+    for (int64_t i = threadIdx.x; i < ao.sorted_capacity; i += kThreads)
+      ao.sorted_ids[i] = static_cast<int32_t>(p.numel);
+  }
+  if (rows_per_key)
+    for (int e = threadIdx.x; e < p.num_keys; e += kThreads) rows_per_key[e] += total[e];
+  if (row_map)
+    for (int i = threadIdx.x; i < p.numel; i += kThreads) row_map[i] = -1;
+  __syncthreads();
+  chunk_place(p, 0, start, warp_off, [&](int64_t idx, int, int pos) {
+    if (ao.sorted_ids) {
+      if (pos < ao.sorted_capacity) ao.sorted_ids[pos] = static_cast<int32_t>(idx);
+    } else {
+      row_map[idx] = pos;
+    }
+  });
+}
+
+int run_grouping(const GroupParams& p, const AlignOut& ao, int32_t* rows_per_key,
+                 int32_t* row_map, void* ws, size_t ws_bytes, cudaStream_t st) {
+  if (p.num_keys > kMaxExperts) return B200MOE_UNSUPPORTED;
+  const int64_t n_cta64 = (p.numel + kChunk - 1) / kChunk;
+  const size_t place_smem = static_cast<size_t>(p.num_keys) * (1 + kWarps) * sizeof(int);
+  if (n_cta64 <= 1) {
+    fused_small_kernel<<<1, kThreads, p.num_keys * kWarps * sizeof(int), st>>>(p, ao, rows_per_key,
+                                                                              row_map);
+    return launch_status("fused_small_kernel");
+  }
+  const int n_cta = static_cast<int>(n_cta64);
+  const size_t need = static_cast<size_t>(n_cta) * p.num_keys * sizeof(int);
+  if (!ws || ws_bytes < need) return B200MOE_WORKSPACE_TOO_SMALL;
+  int* counts = reinterpret_cast<int*>(ws);
+  if (ao.sorted_ids) {
+    const int blocks = static_cast<int>((ao.sorted_capacity + 4095) / 4096);
+    fill_kernel<<<blocks < 592 ? blocks : 592, 256, 0, st>>>(ao.sorted_ids, ao.sorted_capacity,
+                                                             static_cast<int32_t>(p.numel));
+  }
+  count_kernel<<<n_cta, kThreads, p.num_keys * sizeof(int), st>>>(p, counts);
+  scan_kernel<<<1, kThreads, 0, st>>>(p, n_cta, counts, ao, rows_per_key);
+  if (ao.sorted_ids)
+    place_align_kernel<<<n_cta, kThreads, place_smem, st>>>(p, counts, ao);
+  else
+    place_remap_kernel<<<n_cta, kThreads, place_smem, st>>>(p, counts, row_map);
+  return launch_status("stable grouping");
+}
+
+// ---- row copy of remap_hidden_states ------------------------------------------
+
+// One CTA per token: the row is read once and written to each of its k
+// permuted positions in 16-byte pieces.
+__global__ void __launch_bounds__(256) copy_rows_kernel(
+    const uint4* __restrict__ src, const uint8_t* __restrict__ src_scale,
+    uint4* __restrict__ dst, uint8_t* __restrict__ dst_scale, int64_t row_vecs,
+    int64_t scale_row_bytes, const int32_t* __restrict__ row_map, int k) {
+  const int64_t t = blockIdx.x;
+  __shared__ int rows[64];
+  for (int j = threadIdx.x; j < k; j += blockDim.x) rows[j] = row_map[t * k + j];
+  __syncthreads();
+  const uint4* s = src + t * row_vecs;
+  for (int64_t v = threadIdx.x; v < row_vecs; v += blockDim.x) {
+    const uint4 val = s[v];
+    for (int j = 0; j < k; ++j) {
+      const int r = rows[j];
+      if (r >= 0) dst[static_cast<int64_t>(r) * row_vecs + v] = val;
+    }
+  }
+  if (src_scale) {
+    const uint8_t* ss = src_scale + t * scale_row_bytes;
+    if ((scale_row_bytes & 3) == 0) {
+      for (int64_t v = threadIdx.x; v < scale_row_bytes / 4; v += blockDim.x) {
+        const uint32_t val = reinterpret_cast<const uint32_t*>(ss)[v];
+        for (int j = 0; j < k; ++j)
+          if (rows[j] >= 0)
+            reinterpret_cast<uint32_t*>(dst_scale + static_cast<int64_t>(rows[j]) * scale_row_bytes)[v] = val;
+      }
+    } else {
+      for (int64_t v = threadIdx.x; v < scale_row_bytes; v += blockDim.x) {
+        const uint8_t val = ss[v];
+        for (int j = 0; j < k; ++j)
+          if (rows[j] >= 0) dst_scale[static_cast<int64_t>(rows[j]) * scale_row_bytes + v] = val;
+      }
+    }
+  }
+}
+
+__global__ void init_expert_map_kernel(int32_t* map, int num_local, int ep_rank, int total) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const int lo = ep_rank * num_local;
+  map[i] = (i >= lo && i < lo + num_local) ? i - lo : -1;
+}
+
+}  // namespace
+}  // namespace b200moe
+
+using namespace b200moe;
+
+static size_t grouping_workspace(int64_t numel, int num_keys) {
+  const int64_t n_cta = (numel + kChunk - 1) / kChunk;
+  return n_cta <= 1 ? 0 : static_cast<size_t>(n_cta) * num_keys * sizeof(int);
+}
+
+extern "C" size_t b200moe_moe_align_block_size_workspace_bytes(int64_t numel, int num_experts) {
+  return grouping_workspace(numel, num_experts);
+}
+
+extern "C" int b200moe_moe_align_block_size(const void* topk_ids, int ids_dtype, int64_t numel,
+                                            int num_experts, int block_size,
+                                            const int32_t* expert_map, int32_t* sorted_token_ids,
+                                            int64_t sorted_capacity, int32_t* expert_ids,
+                                            int64_t blocks_capacity, int32_t* num_tokens_post_pad,
+                                            void* workspace, size_t workspace_bytes,
+                                            void* stream) {
+  if (numel < 0 || num_experts <= 0 || block_size <= 0 || !is_index_dtype(ids_dtype) ||
+      !sorted_token_ids || !expert_ids || !num_tokens_post_pad || (numel > 0 && !topk_ids))
+    return B200MOE_INVALID_ARG;
+  if (numel >= (1ll << 31)) return B200MOE_UNSUPPORTED;
+  GroupParams p{topk_ids, ids_dtype, numel, num_experts, num_experts, expert_map, 1, block_size};
+  AlignOut ao{sorted_token_ids, sorted_capacity, expert_ids, blocks_capacity, num_tokens_post_pad,
+              expert_map};
+  return run_grouping(p, ao, nullptr, nullptr, workspace, workspace_bytes, as_stream(stream));
+}
+
+extern "C" int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts, int ep_rank,
+                                       int ep_size, void* stream) {
+  if (!expert_map || num_local_experts <= 0 || ep_size <= 0 || ep_rank < 0 || ep_rank >= ep_size)
+    return B200MOE_INVALID_ARG;
+  const int total = num_local_experts * ep_size;
+  init_expert_map_kernel<<<(total + 255) / 256, 256, 0, as_stream(stream)>>>(
+      expert_map, num_local_experts, ep_rank, total);
+  return launch_status("init_expert_map_kernel");
+}
+
+extern "C" size_t b200moe_remap_hidden_states_workspace_bytes(int T, int k, int local_experts) {
+  return grouping_workspace(static_cast<int64_t>(T) * k, local_experts);
+}
+
+extern "C" int b200moe_remap_hidden_states(const void* hidden, const void* scales, void* remapped,
+                                           void* remapped_scales, int64_t row_bytes,
+                                           int64_t scale_row_bytes, const void* topk_ids,
+                                           int ids_dtype, const int32_t* expert_map, int T, int k,
+                                           int total_experts, int local_experts,
+                                           int32_t* rows_per_expert, int32_t* row_map,
+                                           void* workspace, size_t workspace_bytes,
+                                           void* stream) {
+  if (T < 0 || k <= 0 || k > 64 || local_experts <= 0 || total_experts <= 0 ||
+      !is_index_dtype(ids_dtype) || !rows_per_expert || !row_map)
+    return B200MOE_INVALID_ARG;
+  if (row_bytes % 16 != 0) return B200MOE_INVALID_ARG;
+  if (T == 0) return B200MOE_OK;
+  if (!topk_ids || (hidden && !remapped) || (scales && !remapped_scales)) return B200MOE_INVALID_ARG;
+  cudaStream_t st = as_stream(stream);
+  GroupParams p{topk_ids, ids_dtype, static_cast<int64_t>(T) * k, local_experts,
+                expert_map ? total_experts : local_experts, expert_map, 0, 1};
+  AlignOut none{nullptr, 0, nullptr, 0, nullptr, nullptr};
+  int rc = run_grouping(p, none, rows_per_expert, row_map, workspace, workspace_bytes, st);
+  if (rc != B200MOE_OK) return rc;
+  if (hidden) {
+    copy_rows_kernel<<<T, 256, 0, st>>>(reinterpret_cast<const uint4*>(hidden),
+                                        reinterpret_cast<const uint8_t*>(scales),
+                                        reinterpret_cast<uint4*>(remapped),
+                                        reinterpret_cast<uint8_t*>(remapped_scales),
+                                        row_bytes / 16, scale_row_bytes, row_map, k);
+    rc = launch_status("copy_rows_kernel");
+  }
+  return rc;
+}

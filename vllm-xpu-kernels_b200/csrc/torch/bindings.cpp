@@ -1,0 +1,620 @@
+// Torch operator registry of the fused-MoE path.
+//
+// Registers, on the CUDA dispatch key, the operator schemas that
+// vllm-xpu-kernels registers on XPU for this path (csrc/moe/torch_bindings.cpp,
+// csrc/torch_bindings.cpp, csrc/xpu/torch_bindings.cpp) in the same three
+// library namespaces.  Each implementation validates its tensors, allocates
+// scratch through torch's caching allocator and calls the C ABI of
+// libb200moe.so on the current CUDA stream.  There is no other code path: if a
+// tensor is not on a CUDA device the dispatcher has no kernel to run.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <ATen/ATen.h>
+#include <torch/library.h>
+
+#include <optional>
+#include <string>
+#include <tuple>
+
+#include "b200moe.h"
+
+#ifndef B200MOE_NS_C
+#define B200MOE_NS_C _C
+#endif
+#ifndef B200MOE_NS_MOE_C
+#define B200MOE_NS_MOE_C _moe_C
+#endif
+#ifndef B200MOE_NS_XPU_C
+#define B200MOE_NS_XPU_C _xpu_C
+#endif
+
+namespace {
+
+using at::Tensor;
+using OptTensor = std::optional<Tensor>;
+
+void* cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void check(int status, const char* op) {
+  TORCH_CHECK(status == B200MOE_OK, op, ": ", b200moe_status_string(status), " (",
+              b200moe_last_error(), ")");
+}
+
+int float_code(const Tensor& t, const char* what) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return B200MOE_F32;
+    case at::kHalf: return B200MOE_F16;
+    case at::kBFloat16: return B200MOE_BF16;
+    default: TORCH_CHECK(false, what, ": unsupported dtype ", t.scalar_type());
+  }
+  return -1;
+}
+
+int index_code(const Tensor& t, const char* what) {
+  switch (t.scalar_type()) {
+    case at::kInt: return B200MOE_I32;
+    case at::kLong: return B200MOE_I64;
+    case at::kUInt32: return B200MOE_U32;
+    default: TORCH_CHECK(false, what, ": index tensor must be int32, uint32 or int64");
+  }
+  return -1;
+}
+
+const void* opt_ptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+Tensor workspace(size_t bytes, const Tensor& like) {
+  return at::empty({static_cast<int64_t>(bytes ? bytes : 1)}, like.options().dtype(at::kByte));
+}
+
+// ---- routing ------------------------------------------------------------------
+
+void topk_common(bool sigmoid, Tensor& topk_weights, Tensor& topk_indices,
+                 Tensor& token_expert_indices, const Tensor& gating_output, bool renormalize,
+                 const OptTensor& bias, double scale, const OptTensor& is_padding) {
+  const char* op = sigmoid ? "topk_sigmoid" : "topk_softmax";
+  TORCH_CHECK(gating_output.dim() >= 1 && gating_output.is_contiguous(), op,
+              ": gating_output must be contiguous");
+  const int64_t E = gating_output.size(-1);
+  const int64_t T = gating_output.numel() / E;
+  const int64_t k = topk_weights.size(-1);
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, op, ": topk_weights must be float32");
+  TORCH_CHECK(topk_weights.is_contiguous() && topk_indices.is_contiguous() &&
+                  token_expert_indices.is_contiguous(),
+              op, ": outputs must be contiguous");
+  TORCH_CHECK(topk_indices.numel() == T * k && topk_weights.numel() == T * k, op,
+              ": output shape mismatch");
+  TORCH_CHECK(token_expert_indices.scalar_type() == at::kInt, op,
+              ": token_expert_indices must be int32");
+  Tensor bias_f;
+  const float* bias_p = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->numel() == E, op, ": bias must have num_experts entries");
+    bias_f = bias->to(at::kFloat).contiguous();
+    bias_p = bias_f.data_ptr<float>();
+  }
+  Tensor pad_u8;
+  const uint8_t* pad_p = nullptr;
+  if (is_padding.has_value()) {
+    TORCH_CHECK(is_padding->numel() == T, op, ": is_padding must have one entry per row");
+    pad_u8 = is_padding->to(at::kBool).contiguous();
+    pad_p = reinterpret_cast<const uint8_t*>(pad_u8.data_ptr());
+  }
+  c10::cuda::CUDAGuard guard(gating_output.device());
+  const int in = float_code(gating_output, op);
+  const int idt = index_code(topk_indices, op);
+  int rc;
+  if (sigmoid)
+    rc = b200moe_topk_sigmoid(gating_output.data_ptr(), in, T, E, k, renormalize, bias_p,
+                              static_cast<float>(scale), pad_p, topk_weights.data_ptr<float>(),
+                              topk_indices.data_ptr(), idt, token_expert_indices.data_ptr<int>(),
+                              cur_stream());
+  else
+    rc = b200moe_topk_softmax(gating_output.data_ptr(), in, T, E, k, renormalize, bias_p, pad_p,
+                              topk_weights.data_ptr<float>(), topk_indices.data_ptr(), idt,
+                              token_expert_indices.data_ptr<int>(), cur_stream());
+  check(rc, op);
+}
+
+void topk_softmax(Tensor& w, Tensor& ids, Tensor& src, const Tensor& gating, bool renorm,
+                  const OptTensor& bias, const OptTensor& is_padding) {
+  topk_common(false, w, ids, src, gating, renorm, bias, 1.0, is_padding);
+}
+
+void topk_sigmoid(Tensor& w, Tensor& ids, Tensor& src, const Tensor& gating, bool renorm,
+                  const OptTensor& bias, double scale, const OptTensor& is_padding) {
+  topk_common(true, w, ids, src, gating, renorm, bias, scale, is_padding);
+}
+
+std::tuple<Tensor, Tensor> grouped_topk(const Tensor& scores, int64_t n_group, int64_t topk_group,
+                                        int64_t topk, bool renormalize, double scale,
+                                        const Tensor& bias, int64_t scoring_func) {
+  TORCH_CHECK(scores.dim() == 2 && scores.is_contiguous(), "grouped_topk: scores must be [T, E] contiguous");
+  const int64_t T = scores.size(0), E = scores.size(1);
+  TORCH_CHECK(bias.numel() == E && bias.is_contiguous(), "grouped_topk: bias must have num_experts entries");
+  TORCH_CHECK(n_group > 0 && n_group <= 32, "grouped_topk: n_group must be in [1, 32]");
+  TORCH_CHECK(topk > 0 && topk <= 32, "grouped_topk: topk must be in [1, 32]");
+  TORCH_CHECK(E % n_group == 0, "grouped_topk: num_experts must be divisible by n_group");
+  c10::cuda::CUDAGuard guard(scores.device());
+  Tensor values = at::empty({T, topk}, scores.options().dtype(at::kFloat));
+  Tensor ids = at::empty({T, topk}, scores.options().dtype(at::kInt));
+  check(b200moe_grouped_topk(scores.data_ptr(), float_code(scores, "grouped_topk"), bias.data_ptr(),
+                             float_code(bias, "grouped_topk"), T, E, n_group, topk_group, topk,
+                             renormalize, static_cast<float>(scale), scoring_func,
+                             values.data_ptr<float>(), ids.data_ptr<int>(), cur_stream()),
+        "grouped_topk");
+  return {values, ids};
+}
+
+// ---- permutation -----------------------------------------------------------------
+
+void moe_align_block_size(const Tensor& topk_ids, int64_t num_experts, int64_t block_size,
+                          Tensor& sorted_token_ids, Tensor& experts_ids,
+                          Tensor& num_tokens_post_pad, const OptTensor& maybe_expert_map) {
+  TORCH_CHECK(topk_ids.is_contiguous(), "moe_align_block_size: topk_ids must be contiguous");
+  TORCH_CHECK(sorted_token_ids.scalar_type() == at::kInt && experts_ids.scalar_type() == at::kInt &&
+                  num_tokens_post_pad.scalar_type() == at::kInt,
+              "moe_align_block_size: outputs must be int32");
+  TORCH_CHECK(num_experts <= 1024, "moe_align_block_size: at most 1024 experts");
+  if (maybe_expert_map.has_value())
+    TORCH_CHECK(maybe_expert_map->scalar_type() == at::kInt && maybe_expert_map->is_contiguous(),
+                "moe_align_block_size: expert_map must be contiguous int32");
+  c10::cuda::CUDAGuard guard(topk_ids.device());
+  const size_t ws = b200moe_moe_align_block_size_workspace_bytes(topk_ids.numel(), num_experts);
+  Tensor w = workspace(ws, topk_ids);
+  check(b200moe_moe_align_block_size(
+            topk_ids.data_ptr(), index_code(topk_ids, "moe_align_block_size"), topk_ids.numel(),
+            num_experts, block_size,
+            reinterpret_cast<const int32_t*>(opt_ptr(maybe_expert_map)),
+            sorted_token_ids.data_ptr<int>(), sorted_token_ids.numel(), experts_ids.data_ptr<int>(),
+            experts_ids.numel(), num_tokens_post_pad.data_ptr<int>(), w.data_ptr(), ws,
+            cur_stream()),
+        "moe_align_block_size");
+}
+
+void init_expert_map(Tensor expert_map, int64_t num_experts, int64_t ep_rank, int64_t ep_size) {
+  TORCH_CHECK(expert_map.scalar_type() == at::kInt && expert_map.is_contiguous(),
+              "init_expert_map: expert_map must be contiguous int32");
+  TORCH_CHECK(expert_map.numel() == num_experts * ep_size, "init_expert_map: size mismatch");
+  c10::cuda::CUDAGuard guard(expert_map.device());
+  check(b200moe_init_expert_map(expert_map.data_ptr<int>(), num_experts, ep_rank, ep_size,
+                                cur_stream()),
+        "init_expert_map");
+}
+
+void remap_hidden_states(const Tensor& hidden_states, const OptTensor& hidden_states_scales,
+                         Tensor remapped_hidden_states, const OptTensor& remapped_scales,
+                         const OptTensor& expert_map, Tensor rows_per_expert,
+                         Tensor unpermuted_row_to_permuted_row, const Tensor& topk_ids,
+                         int64_t total_experts_num, int64_t local_experts_num) {
+  TORCH_CHECK(hidden_states.dim() == 2 && hidden_states.is_contiguous() &&
+                  remapped_hidden_states.is_contiguous(),
+              "remap_hidden_states: hidden states must be contiguous 2-D");
+  TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous(), "remap_hidden_states: topk_ids must be [T, k]");
+  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt &&
+                  unpermuted_row_to_permuted_row.scalar_type() == at::kInt,
+              "remap_hidden_states: rows_per_expert and the row map must be int32");
+  TORCH_CHECK(local_experts_num <= 1024, "remap_hidden_states: at most 1024 local experts");
+  const int64_t T = hidden_states.size(0), k = topk_ids.size(1);
+  const int64_t row_bytes = hidden_states.size(1) * hidden_states.element_size();
+  TORCH_CHECK(row_bytes % 16 == 0, "remap_hidden_states: a row must be a multiple of 16 bytes");
+  TORCH_CHECK(remapped_hidden_states.numel() * remapped_hidden_states.element_size() >= T * k * row_bytes,
+              "remap_hidden_states: remapped buffer too small");
+  int64_t scale_row_bytes = 0;
+  if (hidden_states_scales.has_value()) {
+    TORCH_CHECK(remapped_scales.has_value(), "remap_hidden_states: remapped scales missing");
+    TORCH_CHECK(hidden_states_scales->is_contiguous() && remapped_scales->is_contiguous(),
+                "remap_hidden_states: scales must be contiguous");
+    scale_row_bytes = hidden_states_scales->size(1) * hidden_states_scales->element_size();
+  }
+  Tensor map32;
+  const int32_t* map_p = nullptr;
+  if (expert_map.has_value()) {
+    map32 = expert_map->scalar_type() == at::kInt ? expert_map->contiguous()
+                                                  : expert_map->to(at::kInt).contiguous();
+    map_p = map32.data_ptr<int>();
+  }
+  c10::cuda::CUDAGuard guard(hidden_states.device());
+  const size_t ws = b200moe_remap_hidden_states_workspace_bytes(T, k, local_experts_num);
+  Tensor w = workspace(ws, topk_ids);
+  check(b200moe_remap_hidden_states(
+            hidden_states.data_ptr(), opt_ptr(hidden_states_scales),
+            remapped_hidden_states.data_ptr(),
+            remapped_scales.has_value() ? remapped_scales->data_ptr() : nullptr, row_bytes,
+            scale_row_bytes, topk_ids.data_ptr(), index_code(topk_ids, "remap_hidden_states"),
+            map_p, T, k, total_experts_num, local_experts_num, rows_per_expert.data_ptr<int>(),
+            unpermuted_row_to_permuted_row.data_ptr<int>(), w.data_ptr(), ws, cur_stream()),
+        "remap_hidden_states");
+}
+
+void moe_gather(Tensor& output, const Tensor& moe_output, const Tensor& topk_weights,
+                const Tensor& unpermuted_row_to_permuted_row, int64_t /*num_experts*/) {
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "moe_gather: topk_weights must be float32");
+  TORCH_CHECK(output.scalar_type() == moe_output.scalar_type(), "moe_gather: dtype mismatch");
+  TORCH_CHECK(output.is_contiguous() && moe_output.is_contiguous() && topk_weights.is_contiguous() &&
+                  unpermuted_row_to_permuted_row.is_contiguous(),
+              "moe_gather: tensors must be contiguous");
+  TORCH_CHECK(unpermuted_row_to_permuted_row.scalar_type() == at::kInt, "moe_gather: row map must be int32");
+  const int64_t T = output.size(0), H = output.size(1), k = topk_weights.size(1);
+  c10::cuda::CUDAGuard guard(output.device());
+  check(b200moe_moe_gather(output.data_ptr(), moe_output.data_ptr(), float_code(output, "moe_gather"),
+                           topk_weights.data_ptr<float>(),
+                           unpermuted_row_to_permuted_row.data_ptr<int>(), T, k, H, cur_stream()),
+        "moe_gather");
+}
+
+void moe_sum(const Tensor& input, Tensor& output, const OptTensor& topk_ids,
+             const OptTensor& expert_map) {
+  TORCH_CHECK(input.dim() == 3, "moe_sum: input must be [num_tokens, topk, hidden]");
+  const int64_t num_tokens = input.size(0), topk = input.size(1), hidden = input.size(2);
+  TORCH_CHECK(input.scalar_type() == output.scalar_type(),
+              "moe_sum: input and output must have the same dtype");
+  TORCH_CHECK(input.device() == output.device(), "moe_sum: input and output must be on the same device");
+  TORCH_CHECK(input.is_contiguous() && output.is_contiguous(),
+              "moe_sum expects contiguous input and output");
+  TORCH_CHECK(input.numel() == output.numel() * topk,
+              "moe_sum: input shape must be [num_tokens, topk, hidden] matching output "
+              "[num_tokens, hidden]");
+  TORCH_CHECK(!(expert_map.has_value() && !topk_ids.has_value()),
+              "moe_sum: expert_map requires topk_ids to be provided");
+  int idt = B200MOE_I32;
+  if (topk_ids.has_value()) {
+    const Tensor& tk = *topk_ids;
+    TORCH_CHECK(tk.is_contiguous(), "moe_sum: topk_ids must be contiguous");
+    TORCH_CHECK(tk.device() == input.device(), "moe_sum: topk_ids must be on the same device as input");
+    TORCH_CHECK(tk.dim() == 2 && tk.size(0) == num_tokens && tk.size(1) == topk,
+                "moe_sum: topk_ids must have shape [num_tokens, topk]");
+    idt = index_code(tk, "moe_sum");
+    if (expert_map.has_value()) {
+      TORCH_CHECK(expert_map->scalar_type() == at::kInt, "moe_sum: expert_map must be int32");
+      TORCH_CHECK(expert_map->is_contiguous(), "moe_sum: expert_map must be contiguous");
+      TORCH_CHECK(expert_map->device() == input.device(),
+                  "moe_sum: expert_map must be on the same device as input");
+    }
+  }
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_moe_sum(input.data_ptr(), output.data_ptr(), float_code(input, "moe_sum"),
+                        num_tokens, topk, hidden, opt_ptr(topk_ids), idt,
+                        reinterpret_cast<const int32_t*>(opt_ptr(expert_map)), cur_stream()),
+        "moe_sum");
+}
+
+// ---- activations / quantisation -----------------------------------------------------
+
+void silu_and_mul(Tensor& result, const Tensor& input) {
+  TORCH_CHECK(input.is_contiguous() && result.is_contiguous(), "silu_and_mul: tensors must be contiguous");
+  TORCH_CHECK(input.scalar_type() == result.scalar_type(), "silu_and_mul: dtype mismatch");
+  const int64_t d = input.size(-1) / 2;
+  TORCH_CHECK(result.size(-1) == d, "silu_and_mul: output must have half the input's last dim");
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_silu_and_mul(result.data_ptr(), input.data_ptr(), float_code(input, "silu_and_mul"),
+                             input.numel() / (2 * d), d, cur_stream()),
+        "silu_and_mul");
+}
+
+void swigluoai_and_mul(Tensor& out, const Tensor& input, double alpha, double limit) {
+  TORCH_CHECK(input.is_contiguous() && out.is_contiguous(), "swigluoai_and_mul: tensors must be contiguous");
+  TORCH_CHECK(input.scalar_type() == out.scalar_type(), "swigluoai_and_mul: dtype mismatch");
+  const int64_t d = input.size(-1) / 2;
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_swigluoai_and_mul(out.data_ptr(), input.data_ptr(),
+                                  float_code(input, "swigluoai_and_mul"), input.numel() / (2 * d), d,
+                                  static_cast<float>(alpha), static_cast<float>(limit), cur_stream()),
+        "swigluoai_and_mul");
+}
+
+void scale_strides(const Tensor& s, int64_t rows, int64_t groups, int64_t* sr, int64_t* sg) {
+  TORCH_CHECK(s.scalar_type() == at::kFloat, "group quant: scales must be float32");
+  TORCH_CHECK(s.numel() == rows * groups, "group quant: scales must have one entry per group");
+  if (s.dim() >= 2) {
+    *sr = s.stride(-2);
+    *sg = s.stride(-1);
+  } else {
+    *sr = groups;
+    *sg = 1;
+  }
+}
+
+void per_token_group_fp8_quant(const Tensor& input, Tensor& output_q, Tensor& output_s,
+                               int64_t group_size, double eps, double fp8_min, double fp8_max,
+                               bool scale_ue8m0, bool, bool) {
+  TORCH_CHECK(input.is_contiguous() && output_q.is_contiguous(), "per_token_group_fp8_quant: contiguous tensors expected");
+  TORCH_CHECK(output_q.scalar_type() == at::kFloat8_e4m3fn, "per_token_group_fp8_quant: output must be float8_e4m3fn");
+  const int64_t N = input.size(-1);
+  TORCH_CHECK(N % group_size == 0, "per_token_group_fp8_quant: hidden size must be divisible by group_size");
+  const int64_t R = input.numel() / N;
+  int64_t sr, sg;
+  scale_strides(output_s, R, N / group_size, &sr, &sg);
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_per_token_group_fp8_quant(
+            input.data_ptr(), float_code(input, "per_token_group_fp8_quant"), output_q.data_ptr(),
+            output_s.data_ptr<float>(), R, N, group_size, static_cast<float>(eps),
+            static_cast<float>(fp8_min), static_cast<float>(fp8_max), scale_ue8m0, sr, sg,
+            cur_stream()),
+        "per_token_group_fp8_quant");
+}
+
+void per_token_group_quant_mxfp4(const Tensor& input, Tensor& output_q, Tensor& output_s,
+                                 int64_t group_size, double eps) {
+  TORCH_CHECK(input.is_contiguous() && output_q.is_contiguous(), "per_token_group_quant_mxfp4: contiguous tensors expected");
+  TORCH_CHECK(group_size == 32, "per_token_group_quant_mxfp4: group_size must be 32");
+  const int64_t N = input.size(-1);
+  const int64_t R = input.numel() / N;
+  TORCH_CHECK(output_q.numel() * output_q.element_size() == R * N / 2,
+              "per_token_group_quant_mxfp4: output must hold two values per byte");
+  int64_t sr, sg;
+  scale_strides(output_s, R, N / 32, &sr, &sg);
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_per_token_group_quant_mxfp4(
+            input.data_ptr(), float_code(input, "per_token_group_quant_mxfp4"),
+            reinterpret_cast<uint8_t*>(output_q.data_ptr()), output_s.data_ptr<float>(), R, N,
+            group_size, static_cast<float>(eps), sr, sg, cur_stream()),
+        "per_token_group_quant_mxfp4");
+}
+
+void silu_and_mul_per_block_quant(Tensor& out, const Tensor& input, Tensor& scales,
+                                  int64_t group_size, const OptTensor& scale_ub,
+                                  bool is_scale_transposed, bool scale_ue8m0) {
+  TORCH_CHECK(input.is_contiguous() && out.is_contiguous(), "silu_and_mul_per_block_quant: contiguous tensors expected");
+  TORCH_CHECK(out.scalar_type() == at::kFloat8_e4m3fn, "silu_and_mul_per_block_quant: output must be float8_e4m3fn");
+  const int64_t d = input.size(-1) / 2;
+  const int64_t R = input.numel() / (2 * d);
+  TORCH_CHECK(d % group_size == 0, "silu_and_mul_per_block_quant: hidden size must be divisible by group_size");
+  int64_t sr, sg;
+  scale_strides(scales, R, d / group_size, &sr, &sg);
+  if (is_scale_transposed && scales.dim() >= 2 && scales.size(0) != R) { sr = scales.stride(-1); sg = scales.stride(-2); }
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_silu_mul_block_quant(
+            input.data_ptr(), float_code(input, "silu_and_mul_per_block_quant"), out.data_ptr(),
+            scales.data_ptr<float>(), R, d, group_size,
+            scale_ub.has_value() ? scale_ub->data_ptr<float>() : nullptr, scale_ue8m0, sr, sg,
+            cur_stream()),
+        "silu_and_mul_per_block_quant");
+}
+
+void silu_and_mul_mxfp4_quant(Tensor& out, const Tensor& input, Tensor& scales, int64_t group_size,
+                              double eps) {
+  TORCH_CHECK(input.is_contiguous() && out.is_contiguous() && scales.is_contiguous(),
+              "silu_and_mul_mxfp4_quant: contiguous tensors expected");
+  TORCH_CHECK(scales.scalar_type() == at::kFloat, "silu_and_mul_mxfp4_quant: scales must be float32");
+  const int64_t d = input.size(-1) / 2;
+  const int64_t R = input.numel() / (2 * d);
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_silu_mul_mxfp4_quant(input.data_ptr(), float_code(input, "silu_and_mul_mxfp4_quant"),
+                                     reinterpret_cast<uint8_t*>(out.data_ptr()),
+                                     scales.data_ptr<float>(), R, d, group_size,
+                                     static_cast<float>(eps), cur_stream()),
+        "silu_and_mul_mxfp4_quant");
+}
+
+// ---- grouped GEMM -----------------------------------------------------------------
+
+int act_code(const Tensor& t, const char* op) {
+  if (t.scalar_type() == at::kFloat8_e4m3fn) return B200MOE_E4M3;
+  return float_code(t, op);
+}
+
+// Shared by the reference-named entry and the extended one.
+Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
+                         const OptTensor& B_scale, const OptTensor& bias, Tensor D,
+                         const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
+                         int64_t epilogue, int64_t b_layout, double alpha, double limit) {
+  const char* op = "cutlass_grouped_gemm_interface";
+  TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && D.is_contiguous(), op, ": A, B and D must be contiguous");
+  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
+                  rows_per_expert.numel() >= num_experts,
+              op, ": rows_per_expert must be int32 [num_experts]");
+  TORCH_CHECK(N % 8 == 0, op, ": N must be a multiple of 8");
+  b200moe_gemm_args a{};
+  a.epilogue = static_cast<int>(epilogue);
+  a.a_dtype = act_code(A, op);
+  a.d_dtype = act_code(D, op);
+  a.A = A.data_ptr();
+  a.B = B.data_ptr();
+  a.b_layout = static_cast<int>(b_layout);
+  a.D = D.data_ptr();
+  a.rows_per_expert = rows_per_expert.data_ptr<int>();
+  a.R = A.numel() / K;
+  a.N = N;
+  a.K = K;
+  a.E = num_experts;
+  a.alpha = static_cast<float>(alpha);
+  a.limit = static_cast<float>(limit);
+  const auto bt = B.scalar_type();
+  if (bt == at::kFloat8_e4m3fn) {
+    TORCH_CHECK(B_scale.has_value() && B_scale->scalar_type() == at::kFloat && B_scale->dim() == 3,
+                op, ": float8 weights need float32 block scales [E, K/128, N/128]");
+    TORCH_CHECK(B_scale->is_contiguous(), op, ": weight scales must be contiguous");
+    TORCH_CHECK(K % 128 == 0 && N % 128 == 0, op, ": block-FP8 needs K and N to be multiples of 128");
+    a.recipe = B200MOE_RECIPE_FP8_BLOCK;
+    a.b_scale = B_scale->data_ptr();
+    if (a.a_dtype == B200MOE_E4M3) {
+      TORCH_CHECK(A_scale.has_value() && A_scale->scalar_type() == at::kFloat && A_scale->is_contiguous(),
+                  op, ": float8 activations need float32 per-token-group-128 scales");
+      a.a_scale = A_scale->data_ptr<float>();
+    }
+  } else if (bt == at::kFloat4_e2m1fn_x2 || (bt == at::kByte && B_scale.has_value())) {
+    TORCH_CHECK(B_scale.has_value() && B_scale->element_size() == 1 && B_scale->is_contiguous(), op,
+                ": MXFP4 weights need e8m0 scales [E, N, K/32]");
+    TORCH_CHECK(K % 32 == 0, op, ": MXFP4 needs K to be a multiple of 32");
+    a.recipe = B200MOE_RECIPE_MXFP4;
+    a.b_scale = B_scale->data_ptr();
+  } else {
+    TORCH_CHECK(bt == A.scalar_type(), op, ": 16-bit weights must have the activations' dtype");
+    TORCH_CHECK(!B_scale.has_value(), op, ": 16-bit weights take no scales");
+    a.recipe = B200MOE_RECIPE_BF16;
+  }
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->is_contiguous() && bias->numel() == num_experts * N, op, ": bias must be [E, N]");
+    a.bias = bias->data_ptr();
+    a.bias_dtype = float_code(*bias, op);
+  }
+  c10::cuda::CUDAGuard guard(A.device());
+  const size_t ws = b200moe_grouped_gemm_workspace_bytes(&a);
+  Tensor w = workspace(ws, rows_per_expert);
+  check(b200moe_grouped_gemm(&a, w.data_ptr(), ws, cur_stream()), op);
+  return D;
+}
+
+Tensor cutlass_grouped_gemm_interface(const Tensor& ptr_A, const OptTensor& ptr_A_scale,
+                                      const Tensor& ptr_B, const OptTensor& ptr_B_scale,
+                                      const OptTensor& ptr_bias, Tensor ptr_D,
+                                      const Tensor& rows_per_expert, int64_t N, int64_t K,
+                                      int64_t num_experts) {
+  return grouped_gemm_impl(ptr_A, ptr_A_scale, ptr_B, ptr_B_scale, ptr_bias, ptr_D, rows_per_expert,
+                           N, K, num_experts, B200MOE_EPI_STORE, B200MOE_B_LAYOUT_KN, 1.702, 7.0);
+}
+
+Tensor b200_grouped_gemm(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
+                         const OptTensor& B_scale, const OptTensor& bias, Tensor D,
+                         const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
+                         int64_t epilogue, int64_t b_layout, double alpha, double limit) {
+  return grouped_gemm_impl(A, A_scale, B, B_scale, bias, D, rows_per_expert, N, K, num_experts,
+                           epilogue, b_layout, alpha, limit);
+}
+
+Tensor b200_grouped_gemm_check(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
+                               const OptTensor& B_scale, const OptTensor& bias, Tensor D,
+                               const Tensor& rows_per_expert, int64_t N, int64_t K,
+                               int64_t num_experts, int64_t b_layout) {
+  b200moe_gemm_args a{};
+  a.a_dtype = act_code(A, "b200_grouped_gemm_check");
+  a.d_dtype = float_code(D, "b200_grouped_gemm_check");
+  a.A = A.data_ptr();
+  a.a_scale = A_scale.has_value() ? A_scale->data_ptr<float>() : nullptr;
+  a.B = B.data_ptr();
+  a.b_scale = B_scale.has_value() ? B_scale->data_ptr() : nullptr;
+  a.b_layout = static_cast<int>(b_layout);
+  a.bias = bias.has_value() ? bias->data_ptr() : nullptr;
+  a.bias_dtype = bias.has_value() ? float_code(*bias, "b200_grouped_gemm_check") : 0;
+  a.D = D.data_ptr();
+  a.rows_per_expert = rows_per_expert.data_ptr<int>();
+  a.R = D.numel() / N;
+  a.N = N;
+  a.K = K;
+  a.E = num_experts;
+  a.recipe = B.scalar_type() == at::kFloat8_e4m3fn ? B200MOE_RECIPE_FP8_BLOCK
+             : (B.element_size() == 1 ? B200MOE_RECIPE_MXFP4 : B200MOE_RECIPE_BF16);
+  c10::cuda::CUDAGuard guard(A.device());
+  check(b200moe_grouped_gemm_check(&a, cur_stream()), "b200_grouped_gemm_check");
+  return D;
+}
+
+Tensor b200_dequant_weights(const Tensor& B, const Tensor& B_scale) {
+  TORCH_CHECK(B.dim() == 3 && B.is_contiguous() && B_scale.is_contiguous(), "b200_dequant_weights: contiguous [E, ., .] weights expected");
+  c10::cuda::CUDAGuard guard(B.device());
+  Tensor out;
+  int rc;
+  if (B.scalar_type() == at::kFloat8_e4m3fn) {
+    out = at::empty(B.sizes(), B.options().dtype(at::kBFloat16));
+    rc = b200moe_dequant_weights(B200MOE_RECIPE_FP8_BLOCK, B.data_ptr(), B_scale.data_ptr(),
+                                 out.data_ptr(), B.size(0), B.size(2), B.size(1), cur_stream());
+  } else {
+    out = at::empty({B.size(0), B.size(1), B.size(2) * 2}, B.options().dtype(at::kBFloat16));
+    rc = b200moe_dequant_weights(B200MOE_RECIPE_MXFP4, B.data_ptr(), B_scale.data_ptr(),
+                                 out.data_ptr(), B.size(0), B.size(1), B.size(2) * 2, cur_stream());
+  }
+  check(rc, "b200_dequant_weights");
+  return out;
+}
+
+int64_t b200_device_status() {
+  int st = 0;
+  check(b200moe_device_status(cur_stream(), &st), "b200_device_status");
+  return st;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(B200MOE_NS_MOE_C, m) {
+  m.def("moe_sum(Tensor input, Tensor! output, Tensor? topk_ids, Tensor? expert_map) -> ()");
+  m.def(
+      "moe_align_block_size(Tensor topk_ids, int num_experts, int block_size, Tensor! "
+      "sorted_token_ids, Tensor! experts_ids, Tensor! num_tokens_post_pad, Tensor? "
+      "maybe_expert_map) -> ()");
+  m.def(
+      "grouped_topk(Tensor scores, int n_group, int topk_group, int topk, bool renormalize, float "
+      "routed_scaling_factor, Tensor bias, int scoring_func) -> (Tensor, Tensor)");
+  m.def(
+      "topk_softmax(Tensor! topk_weights, Tensor! topk_indices, Tensor! token_expert_indices, "
+      "Tensor gating_output, bool renormalize, Tensor? bias, Tensor? is_padding) -> ()");
+  m.def(
+      "topk_sigmoid(Tensor! topk_weights, Tensor! topk_indices, Tensor! token_expert_indices, "
+      "Tensor gating_output, bool renormalize, Tensor? bias, float routed_scaling_factor, Tensor? "
+      "is_padding) -> ()");
+  m.def(
+      "moe_gather(Tensor! output, Tensor moe_output, Tensor topk_weights, Tensor "
+      "unpermuted_row_to_permuted_row, int num_experts) -> ()");
+  m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
+  m.def(
+      "remap_hidden_states(Tensor hidden_states, Tensor? hidden_states_scales, Tensor "
+      "remapped_hidden_states, Tensor? remapped_hidden_states_scales, Tensor? expert_map, Tensor "
+      "rows_per_expert, Tensor unpermuted_row_to_permuted_row, Tensor topk_ids, int "
+      "total_experts_num, int local_experts_num) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(B200MOE_NS_MOE_C, CUDA, m) {
+  m.impl("moe_sum", &moe_sum);
+  m.impl("moe_align_block_size", &moe_align_block_size);
+  m.impl("grouped_topk", &grouped_topk);
+  m.impl("topk_softmax", &topk_softmax);
+  m.impl("topk_sigmoid", &topk_sigmoid);
+  m.impl("moe_gather", &moe_gather);
+  m.impl("init_expert_map", &init_expert_map);
+  m.impl("remap_hidden_states", &remap_hidden_states);
+}
+
+TORCH_LIBRARY(B200MOE_NS_C, m) {
+  m.def("silu_and_mul(Tensor! result, Tensor input) -> ()");
+  m.def("swigluoai_and_mul(Tensor! out, Tensor input, float alpha=1.702, float limit=7.0) -> ()");
+  m.def(
+      "per_token_group_fp8_quant(Tensor input, Tensor! output_q, Tensor! output_s, int group_size, "
+      "float eps, float fp8_min, float fp8_max, bool scale_ue8m0, bool dummy_is_scale_transposed, "
+      "bool dummy_is_tma_aligned) -> ()");
+  m.def(
+      "per_token_group_quant_mxfp4(Tensor input, Tensor! output_q, Tensor! output_s, int "
+      "group_size, float eps) -> ()");
+  m.def(
+      "silu_and_mul_per_block_quant(Tensor! out, Tensor input, Tensor! scales, int group_size, "
+      "Tensor? scale_ub=None, bool is_scale_transposed=False, bool scale_ue8m0=False) -> ()");
+  m.def(
+      "silu_and_mul_mxfp4_quant(Tensor! out, Tensor input, Tensor! scales, int group_size, float "
+      "eps=1e-10) -> ()");
+}
+
+TORCH_LIBRARY_IMPL(B200MOE_NS_C, CUDA, m) {
+  m.impl("silu_and_mul", &silu_and_mul);
+  m.impl("swigluoai_and_mul", &swigluoai_and_mul);
+  m.impl("per_token_group_fp8_quant", &per_token_group_fp8_quant);
+  m.impl("per_token_group_quant_mxfp4", &per_token_group_quant_mxfp4);
+  m.impl("silu_and_mul_per_block_quant", &silu_and_mul_per_block_quant);
+  m.impl("silu_and_mul_mxfp4_quant", &silu_and_mul_mxfp4_quant);
+}
+
+TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
+  m.def(
+      "cutlass_grouped_gemm_interface(Tensor ptr_A, Tensor? ptr_A_scale, Tensor ptr_B, Tensor? "
+      "ptr_B_scale, Tensor? ptr_bias, Tensor ptr_D, Tensor rows_per_expert, int N, int K, int "
+      "num_experts) -> Tensor");
+  // Extensions used by the fused layer: epilogue selection and a second weight layout.
+  m.def(
+      "b200_grouped_gemm(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? bias, "
+      "Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, int "
+      "b_layout, float alpha=1.702, float limit=7.0) -> Tensor");
+  m.def(
+      "b200_grouped_gemm_check(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? "
+      "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "
+      "Tensor");
+  m.def("b200_dequant_weights(Tensor B, Tensor B_scale) -> Tensor");
+  m.def("b200_device_status() -> int");
+}
+
+TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CUDA, m) {
+  m.impl("cutlass_grouped_gemm_interface", &cutlass_grouped_gemm_interface);
+  m.impl("b200_grouped_gemm", &b200_grouped_gemm);
+  m.impl("b200_grouped_gemm_check", &b200_grouped_gemm_check);
+  m.impl("b200_dequant_weights", &b200_dequant_weights);
+}
+
+TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CompositeExplicitAutograd, m) {
+  m.impl("b200_device_status", &b200_device_status);
+}

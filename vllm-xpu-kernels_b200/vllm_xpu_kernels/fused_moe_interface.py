@@ -1,0 +1,228 @@
+"""Fused Mixture-of-Experts layer for B200.
+
+``XpuFusedMoe`` keeps the constructor and ``apply`` signature of
+vllm_xpu_kernels/fused_moe_interface.py:186-330 of the reference project, so
+vLLM code that drives that class runs unchanged; underneath, every step is a
+hand-written sm_100a kernel:
+
+    remap_hidden_states  ->  grouped GEMM w13 (+ gated activation in the
+    epilogue where the recipe allows)  ->  [activation quant]  ->  grouped GEMM
+    w2  ->  moe_gather
+
+Recipes, detected from the weight dtypes as the reference does
+(fused_moe_interface.py:70-83):
+
+* bf16 / fp16 weights ``[E, K, N]``: tcgen05 kind::f16, activation fused into
+  the first GEMM's epilogue.
+* block-FP8 weights ``[E, K, N]`` + f32 scales ``[E, K/128, N/128]``:
+  activations are FP8 with one f32 scale per token per 128 columns (passed in
+  as ``a1q_scale`` or quantised here), tcgen05 kind::f8f6f4 with the scales
+  applied per 128 of K; SiLU*mul and the re-quantisation for the second GEMM are
+  one fused kernel.
+* MXFP4 weights ``[E, N, K/2]`` + e8m0 scales ``[E, N, K/32]``: expanded once,
+  exactly, to bf16 ``[E, N, K]`` at construction (every e2m1 x 2^e product is a
+  bf16 number) and run on the 16-bit path with bf16 activations, which is the
+  W4A16 arithmetic of the reference kernel.
+"""
+from typing import Optional
+
+import torch
+
+try:
+    from . import _C  # noqa: F401
+    from . import _moe_C  # noqa: F401
+    from . import _xpu_C  # noqa: F401
+    FUSEDMOE_UNAVAILABLE_REASON = None
+    FUSEDMOE_AVAILABLE = True
+except ImportError as e:  # the class below then raises on construction
+    FUSEDMOE_UNAVAILABLE_REASON = str(e)
+    FUSEDMOE_AVAILABLE = False
+
+EPI_STORE, EPI_SILU_MUL, EPI_SWIGLU_OAI = 0, 1, 2
+B_LAYOUT_KN, B_LAYOUT_NK = 0, 1
+
+
+def _get_weights_dtype(weight, scales):
+    dt = weight.dtype
+    is_fp8 = dt in (torch.float8_e4m3fn, torch.float8_e5m2)
+    is_int4 = dt == torch.uint8
+    is_mxfp4 = dt == torch.float4_e2m1fn_x2
+    is_mxfp8 = is_fp8 and scales is not None and scales.dtype in (torch.uint8, torch.float8_e8m0fnu)
+    is_block_fp8 = (is_fp8 and scales is not None and scales.dtype == torch.float32
+                    and scales.ndim == 3)
+    is_fp8 = is_fp8 and not is_mxfp8 and not is_block_fp8
+    return is_fp8, is_int4, is_mxfp4, is_mxfp8, is_block_fp8
+
+
+def _get_recipe(is_fp8, is_mxfp8, is_mxfp4, is_int4, is_block_fp8):
+    if is_mxfp8:
+        return "mxfp8"
+    if is_block_fp8:
+        return "fp8block"
+    if is_mxfp4:
+        return "mxfp4"
+    if is_int4:
+        return "int4"
+    if is_fp8:
+        return "fp8"
+    return "bf16"
+
+
+def _is_swigluoai(activation) -> bool:
+    return activation == "swigluoai" or "SWIGLUOAI" in str(activation)
+
+
+class XpuFusedMoe:
+
+    def __init__(
+        self,
+        w13,
+        w13_scales,
+        w13_bias,
+        w2,
+        w2_scales,
+        w2_bias,
+        n_experts_per_token,
+        activation,
+        num_experts,
+        ep_rank=0,
+        ep_size=1,
+        expert_map=None,
+        gemm1_clamp_limit: Optional[float] = None,
+        activation_situ_beta: Optional[float] = None,
+        activation_situ_linear_beta: Optional[float] = None,
+    ):
+        if not FUSEDMOE_AVAILABLE:
+            raise ImportError(FUSEDMOE_UNAVAILABLE_REASON)
+        assert w13.is_contiguous() and w2.is_contiguous()
+        assert w13.is_cuda, "XpuFusedMoe (B200) needs its weights on a CUDA device"
+        flags = _get_weights_dtype(w13, w13_scales)
+        self.is_fp8, self.is_int4, self.is_mxfp4, self.is_mxfp8, self.is_block_fp8 = flags
+        self.recipe = _get_recipe(self.is_fp8, self.is_mxfp8, self.is_mxfp4, self.is_int4,
+                                  self.is_block_fp8)
+        if self.recipe in ("int4", "mxfp8", "fp8"):
+            raise NotImplementedError(
+                f"recipe {self.recipe} is not part of the B200 fused-MoE path "
+                "(supported: bf16/fp16, block-FP8, MXFP4)")
+        if activation != "silu" and not _is_swigluoai(activation):
+            raise ValueError(f"Unsupported FusedMoe activation: {activation}.")
+
+        # 4-bit weights are [E, N, K/2]; everything else is [E, K, N].
+        self.inter_size = (w13.shape[-2] if self.is_mxfp4 else w13.shape[-1]) // 2
+        self.w13, self.w2 = w13, w2
+        self.gemm1_wei_scales = w13_scales if self.recipe != "bf16" else None
+        self.gemm2_wei_scales = w2_scales if self.recipe != "bf16" else None
+        self.w13_bias, self.w2_bias = w13_bias, w2_bias
+        self.n_experts_per_token = n_experts_per_token
+        self.activation = activation
+        self.num_experts = num_experts
+        self.ep_rank, self.ep_size = ep_rank, ep_size
+        self.gemm1_clamp_limit = gemm1_clamp_limit
+
+        if self.is_mxfp4:
+            # One-time exact expansion; tagged on the object so it happens once.
+            self._w13_16 = torch.ops._xpu_C.b200_dequant_weights(
+                w13.view(torch.uint8), w13_scales.view(torch.uint8))
+            self._w2_16 = torch.ops._xpu_C.b200_dequant_weights(
+                w2.view(torch.uint8), w2_scales.view(torch.uint8))
+
+        self.expert_map = expert_map
+        if self.expert_map is None and self.ep_size > 1:
+            self.expert_map = torch.empty((self.num_experts * self.ep_size), dtype=torch.int32,
+                                          device=w13.device)
+            torch.ops._moe_C.init_expert_map(self.expert_map, self.num_experts, self.ep_rank,
+                                             self.ep_size)
+        if self.expert_map is not None:
+            self.total_experts_num = self.expert_map.shape[0]
+        else:
+            self.total_experts_num = self.num_experts * self.ep_size
+        self.local_experts_num = self.num_experts
+
+    # ------------------------------------------------------------------
+    def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
+              a1q_scale=None):
+        """output[T, H] = sum_j w[t, j] * Expert_{ids[t, j]}(hidden_states[t]).
+
+        ``hidden_states`` is bf16/fp16 ``[T, H]``, or already quantised
+        (e4m3 ``[T, H]`` with ``a1q_scale`` f32 ``[T, H/128]``) for block-FP8
+        weights.  ``topk_weights`` is f32 ``[T, k]``; ``topk_ids`` int32/int64
+        global expert ids; ``expert_map`` int32 global -> local id or -1."""
+        num_rows, hidden_size = hidden_states.shape
+        k = self.n_experts_per_token
+        R = num_rows * k
+        dev = hidden_states.device
+        if expert_map is None and self.ep_size > 1:
+            expert_map = self.expert_map
+        if num_rows == 0:
+            return
+
+        if self.is_block_fp8 and a1q_scale is None:
+            # dynamic per-token-group-128 quantisation, once per token (not per routed row)
+            from .moe_utils import quant_fp8_block_act
+            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states)
+        act_quant = a1q_scale is not None
+        if act_quant and not self.is_block_fp8:
+            raise NotImplementedError("quantised activations are only taken with block-FP8 weights")
+
+        remapped = torch.empty((R, hidden_size), dtype=hidden_states.dtype, device=dev)
+        remapped_scales = (torch.empty((R, a1q_scale.shape[1]), dtype=a1q_scale.dtype, device=dev)
+                           if act_quant else None)
+        rows_per_expert = torch.zeros((self.num_experts,), dtype=torch.int32, device=dev)
+        row_map = torch.empty((num_rows, k), dtype=torch.int32, device=dev)
+        torch.ops._moe_C.remap_hidden_states(hidden_states, a1q_scale, remapped, remapped_scales,
+                                             expert_map, rows_per_expert, row_map, topk_ids,
+                                             self.total_experts_num, self.local_experts_num)
+
+        I, E = self.inter_size, self.num_experts
+        oai = _is_swigluoai(self.activation)
+        gemm = torch.ops._xpu_C.b200_grouped_gemm
+        if self.is_block_fp8:
+            gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
+            gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
+                 gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
+            self._clamp(gemm1_out)
+            if oai:
+                act = torch.empty((R, I), dtype=output.dtype, device=dev)
+                torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
+                from .moe_utils import quant_fp8_block_act
+                act_q, act_s = quant_fp8_block_act(act)
+            else:
+                act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
+                act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
+                torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
+            gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
+            gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
+                 rows_per_expert, hidden_size, I, E, EPI_STORE, B_LAYOUT_KN)
+        else:
+            if self.is_mxfp4:
+                w13, w2, layout = self._w13_16, self._w2_16, B_LAYOUT_NK
+            else:
+                w13, w2, layout = self.w13, self.w2, B_LAYOUT_KN
+            act = torch.empty((R, I), dtype=output.dtype, device=dev)
+            if self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0:
+                gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
+                gemm(remapped, None, w13, None, self.w13_bias, gemm1_out, rows_per_expert, 2 * I,
+                     hidden_size, E, EPI_STORE, layout)
+                self._clamp(gemm1_out)
+                if oai:
+                    torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
+                else:
+                    torch.ops._C.silu_and_mul(act, gemm1_out)
+            else:
+                gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
+                     hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702, 7.0)
+            gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
+            gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, I, E,
+                 EPI_STORE, layout)
+
+        torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
+
+    def _clamp(self, gemm1_out):
+        lim = self.gemm1_clamp_limit
+        if lim is not None and lim > 0:
+            if _is_swigluoai(self.activation):
+                gemm1_out[:, 0::2].clamp_(max=lim)
+                gemm1_out[:, 1::2].clamp_(min=-lim, max=lim)
+            else:
+                gemm1_out[:, :self.inter_size].clamp_(max=lim)
+                gemm1_out[:, self.inter_size:].clamp_(min=-lim, max=lim)

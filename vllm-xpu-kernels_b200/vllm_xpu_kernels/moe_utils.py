@@ -1,0 +1,107 @@
+"""Quantisation helpers of the fused-MoE path.
+
+Same names and argument meaning as vllm_xpu_kernels/moe_utils.py of the
+reference project; the quantising functions call the CUDA operators, the
+de-quantising ones are plain tensor arithmetic on whatever device the input
+lives on.
+"""
+import torch
+
+from . import _C  # noqa: F401
+from . import _moe_C  # noqa: F401
+from . import _xpu_C  # noqa: F401
+
+finfo = torch.finfo(torch.float8_e4m3fn)
+FP8_E4M3_MIN = finfo.min
+FP8_E4M3_MAX = finfo.max
+
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
+
+
+def _as_e8m0(s):
+    return s.view(torch.float8_e8m0fnu) if s.dtype == torch.uint8 else s
+
+
+def dequant_mxfp4(x_lp, x_scale):
+    """[..., n] packed e2m1 pairs with one scale per 32 values -> fp32 [..., 2n]."""
+    u8 = x_lp.view(torch.uint8)
+    lut = torch.tensor(_E2M1, dtype=torch.float32, device=u8.device)
+    vals = torch.stack((lut[(u8 & 0xF).long()], lut[(u8 >> 4).long()]), dim=-1).flatten(-2)
+    out = vals.reshape(-1, 32) * x_scale.reshape(-1, 1).to(torch.float32)
+    return out.reshape(u8.shape[:-1] + (u8.shape[-1] * 2,))
+
+
+def dequant_mxfp8(x_lp, x_scale):
+    out = x_lp.to(torch.float32).reshape(-1, 32) * x_scale.reshape(-1, 1).to(torch.float32)
+    return out.reshape(x_lp.shape)
+
+
+def dequant_fp8_block_wei(x_lp, x_scale):
+    K, N = x_lp.shape
+    x = x_lp.to(torch.float32).view(K // 128, 128, N // 128, 128)
+    return (x * x_scale.unsqueeze(1).unsqueeze(-1)).reshape(K, N)
+
+
+def dequant_fp8_block_act(x_lp, x_scale):
+    shape = x_lp.shape
+    x = x_lp.reshape(shape[0], shape[-1] // 128, 128).to(torch.float32)
+    return (x * x_scale.unsqueeze(-1)).reshape(shape)
+
+
+def quant_fp8_block_act(x: torch.Tensor):
+    """Per-token-group-128 FP8 quantisation -> (e4m3 [M, K], f32 [M, K/128])."""
+    x_q = torch.empty(x.shape, device=x.device, dtype=torch.float8_e4m3fn)
+    x_s = torch.empty(x.shape[:-1] + (x.shape[-1] // 128,), device=x.device, dtype=torch.float32)
+    torch.ops._C.per_token_group_fp8_quant(x, x_q, x_s, 128, 1e-10, FP8_E4M3_MIN, FP8_E4M3_MAX,
+                                           False, False, False)
+    return x_q, x_s
+
+
+def _quant_mxfp8_act_xpu(x):
+    assert x.shape[-1] % 32 == 0
+    x_q = torch.empty_like(x, dtype=torch.float8_e4m3fn)
+    x_s = torch.empty(x.shape[:-1] + (x.shape[-1] // 32,), device=x.device, dtype=torch.float32)
+    torch.ops._C.per_token_group_fp8_quant(x, x_q, x_s, 32, 1e-10, FP8_E4M3_MIN, FP8_E4M3_MAX,
+                                           True, False, False)
+    return x_q, x_s.to(torch.float8_e8m0fnu)
+
+
+def _quant_mxfp4_act_xpu(x):
+    M, N = x.shape
+    x_q = torch.empty(M, N // 2, device=x.device, dtype=torch.uint8)
+    x_s = torch.empty(M, N // 32, device=x.device, dtype=torch.float32)
+    torch.ops._C.per_token_group_quant_mxfp4(x, x_q, x_s, 32, 1e-10)
+    return x_q.view(torch.float4_e2m1fn_x2), x_s.to(torch.float8_e8m0fnu)
+
+
+def quant_mxfp_act_xpu(x, recipe):
+    assert recipe in ("mxfp8", "mxfp4")
+    return _quant_mxfp8_act_xpu(x) if recipe == "mxfp8" else _quant_mxfp4_act_xpu(x)
+
+
+def quant_act_xpu(x, recipe):
+    if recipe in ("mxfp4", "mxfp8"):
+        return quant_mxfp_act_xpu(x, recipe)
+    if recipe == "fp8block":
+        return quant_fp8_block_act(x)
+    raise NotImplementedError(f"Unsupported recipe for quant_act_xpu: {recipe}")
+
+
+def dequant_act(x, x_scale, recipe):
+    if recipe == "fp8block":
+        return dequant_fp8_block_act(x, x_scale)
+    if recipe == "mxfp4":
+        return dequant_mxfp4(x, _as_e8m0(x_scale))
+    if recipe == "mxfp8":
+        return dequant_mxfp8(x, _as_e8m0(x_scale))
+    return x
+
+
+def dequant_wei(wei, wei_scale, recipe):
+    if recipe in ("mxfp4", "mxfp4_fp8"):
+        return dequant_mxfp4(wei, _as_e8m0(wei_scale))
+    if recipe == "fp8block":
+        return dequant_fp8_block_wei(wei, wei_scale)
+    if recipe == "fp8":
+        return wei.float() * wei_scale.float()
+    return wei
