@@ -1,0 +1,196 @@
+"""Grouped GEMM on the tensor cores against the CPU oracle (dequantise, then
+fp32 matmul per expert) and, at sizes a CPU cannot reach, against the plain
+CUDA-core evaluation of the same contract.  Tolerance: 2e-2 absolute+relative,
+the reference's bf16 bound (tests/fused_moe/test_grouped_gemm.py there)."""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+EPI_STORE, EPI_SILU, EPI_OAI = 0, 1, 2
+KN, NK = 0, 1
+
+
+def ragged_rows(E, avg, seed, zero_some=True):
+    g = torch.Generator().manual_seed(seed)
+    rows = torch.randint(0, 2 * avg + 1, (E,), generator=g).to(torch.int32)
+    if zero_some and E > 2:
+        rows[1] = 0
+        rows[E - 1] = 0
+    return rows
+
+
+def close(out, ref, tol=2e-2):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    err = (out - ref).abs()
+    bound = tol + tol * ref.abs()
+    assert (err <= bound).all(), (
+        f"max err {err.max().item():.4g} at {torch.nonzero(err > bound)[:5].tolist()} "
+        f"({int((err > bound).sum())} of {err.numel()} outside {tol})")
+
+
+def make_bf16(E, K, N, seed):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(E, K, N, generator=g) / K ** 0.5).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("E,avg,K,N", [(1, 64, 64, 128), (4, 100, 256, 256), (8, 16, 1024, 4096),
+                                       (3, 200, 72, 136), (16, 4, 512, 384), (2, 300, 4096, 1024)])
+@pytest.mark.parametrize("layout", [KN, NK])
+def test_bf16_store(ops, E, avg, K, N, layout):
+    rows = ragged_rows(E, avg, E + K)
+    R = int(rows.sum())
+    if R == 0:
+        rows[0] = 5
+        R = 5
+    g = torch.Generator().manual_seed(N)
+    A = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    B = make_bf16(E, K, N, K)
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(torch.bfloat16)
+    ref = O.grouped_gemm("bf16", A, B, None, bias, rows, torch.float32)
+    Bdev = B.to(DEV) if layout == KN else B.transpose(1, 2).contiguous().to(DEV)
+    D = torch.zeros(R, N, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(A.to(DEV), None, Bdev, None, bias.to(DEV), D, rows.to(DEV), N, K, E,
+                                 EPI_STORE, layout)
+    close(D, ref)
+    if layout == KN:  # the reference-named entry is the same path
+        D2 = torch.zeros_like(D)
+        r = ops._xpu_C.cutlass_grouped_gemm_interface(A.to(DEV), None, Bdev, None, bias.to(DEV), D2,
+                                                      rows.to(DEV), N, K, E)
+        assert r.data_ptr() == D2.data_ptr() and torch.equal(D, D2)
+
+
+def test_rows_beyond_an_expert_are_untouched(ops):
+    E, K, N = 3, 128, 128
+    rows = torch.tensor([5, 0, 130], dtype=torch.int32)
+    R = 200                                     # more rows than the experts own
+    A = torch.randn(R, K).to(torch.bfloat16)
+    B = make_bf16(E, K, N, 1)
+    D = torch.full((R, N), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(A.to(DEV), None, B.to(DEV), None, None, D, rows.to(DEV), N, K, E,
+                                 EPI_STORE, KN)
+    assert (D[135:] == 7.0).all()
+    ref = O.grouped_gemm("bf16", A[:135], B, None, None, rows, torch.float32)
+    close(D[:135], ref)
+
+
+@pytest.mark.parametrize("epi", [EPI_SILU, EPI_OAI])
+@pytest.mark.parametrize("layout", [KN, NK])
+@pytest.mark.parametrize("E,avg,K,N", [(4, 90, 256, 512), (8, 40, 1024, 4096), (2, 150, 192, 5760)])
+def test_bf16_gated_epilogue(ops, epi, layout, E, avg, K, N):
+    rows = ragged_rows(E, avg, 3)
+    R = int(rows.sum())
+    g = torch.Generator().manual_seed(5)
+    A = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    B = make_bf16(E, K, N, 9)
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(torch.bfloat16)
+    h = O.grouped_gemm("bf16", A, B, None, bias, rows, torch.float32)
+    ref = O.silu_mul_fp32(h) if epi == EPI_SILU else O.swigluoai_and_mul(h)
+    Bdev = B.to(DEV) if layout == KN else B.transpose(1, 2).contiguous().to(DEV)
+    D = torch.zeros(R, N // 2, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(A.to(DEV), None, Bdev, None, bias.to(DEV), D, rows.to(DEV), N, K, E,
+                                 epi, layout, 1.702, 7.0)
+    close(D, ref)
+
+
+@pytest.mark.parametrize("E,avg,K,N", [(1, 128, 128, 128), (4, 100, 512, 256), (8, 30, 4096, 1024),
+                                       (2, 260, 7168, 512)])
+def test_fp8_block(ops, E, avg, K, N):
+    rows = ragged_rows(E, avg, K)
+    R = max(int(rows.sum()), 1)
+    if int(rows.sum()) == 0:
+        rows[0] = 1
+    g = torch.Generator().manual_seed(N + 1)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    Aq, As = O.per_token_group_fp8_quant(x, 128)
+    Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / K ** 0.5) for _ in range(E)])
+    Bq, Bs = torch.stack(Bq), torch.stack(Bs)
+    # distinct scales per block so that a mis-indexed scale shows
+    Bs = Bs * (1.0 + 0.25 * torch.rand(Bs.shape, generator=g))
+    ref = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As), Bq, Bs, None, rows, torch.float32)
+    D = torch.zeros(R, N, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, D, rows.to(DEV),
+                                 N, K, E, EPI_STORE, KN)
+    close(D, ref)
+
+
+def test_fp8_weights_with_16bit_activations(ops):
+    # what the reference kernel does natively: weights expanded, activations untouched
+    E, K, N = 3, 256, 384
+    rows = torch.tensor([70, 0, 33], dtype=torch.int32)
+    g = torch.Generator().manual_seed(2)
+    A = torch.randn(103, K, generator=g).to(torch.bfloat16)
+    Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / 16) for _ in range(E)])
+    Bq, Bs = torch.stack(Bq), torch.stack(Bs)
+    ref = O.grouped_gemm("fp8block", A, Bq, Bs, None, rows, torch.float32)
+    D = torch.zeros(103, N, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.cutlass_grouped_gemm_interface(A.to(DEV), None, Bq.to(DEV), Bs.to(DEV), None, D,
+                                              rows.to(DEV), N, K, E)
+    close(D, ref)
+
+
+def test_mxfp4_weights(ops):
+    E, K, N = 4, 320, 256
+    rows = torch.tensor([50, 7, 0, 131], dtype=torch.int32)
+    g = torch.Generator().manual_seed(4)
+    A = torch.randn(188, K, generator=g).to(torch.bfloat16)
+    q, s = zip(*[O.quant_mxfp4_weight(torch.randn(N, K, generator=g) / 16) for _ in range(E)])
+    q, s = torch.stack(q), torch.stack(s)
+    bias = (torch.randn(E, N, generator=g) * 0.02).to(torch.bfloat16)
+    ref = O.grouped_gemm("mxfp4", A, q, s, bias, rows, torch.float32)
+    D = torch.zeros(188, N, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.cutlass_grouped_gemm_interface(A.to(DEV), None, q.to(DEV).view(torch.float4_e2m1fn_x2),
+                                              s.to(DEV), bias.to(DEV), D, rows.to(DEV), N, K, E)
+    close(D, ref)
+    # the one-time expansion is exact
+    w16 = ops._xpu_C.b200_dequant_weights(q.to(DEV), s.to(DEV))
+    assert torch.equal(w16.cpu().float(), torch.stack([O.dequant_mxfp4(q[e], s[e]) for e in range(E)]))
+
+
+def test_c_abi_direct_call():
+    """Through ctypes with raw pointers: what a non-torch host would do."""
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+    E, K, N = 2, 128, 256
+    rows = torch.tensor([100, 60], dtype=torch.int32, device=DEV)
+    A = torch.randn(160, K, device=DEV).to(torch.bfloat16)
+    B = (torch.randn(E, K, N, device=DEV) / 11).to(torch.bfloat16)
+    D = torch.zeros(160, N, dtype=torch.bfloat16, device=DEV)
+    a = capi.GemmArgs(recipe=capi.RECIPE_BF16, epilogue=capi.EPI_STORE, a_dtype=capi.BF16,
+                      d_dtype=capi.BF16, A=A.data_ptr(), B=B.data_ptr(), b_layout=capi.B_LAYOUT_KN,
+                      D=D.data_ptr(), rows_per_expert=rows.data_ptr(), R=160, N=N, K=K, E=E)
+    assert lib.b200moe_grouped_gemm_workspace_bytes(ctypes.byref(a)) == 0
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.b200moe_grouped_gemm(ctypes.byref(a), None, 0, st) == capi.OK
+    torch.cuda.synchronize()
+    ref = O.grouped_gemm("bf16", A.cpu(), B.cpu(), None, None, rows.cpu(), torch.float32)
+    close(D, ref)
+    a.N = 7
+    assert lib.b200moe_grouped_gemm(ctypes.byref(a), None, 0, st) == capi.INVALID_ARG
+
+
+@pytest.mark.parametrize("recipe", ["bf16", "fp8block"])
+def test_large_against_cuda_core_check(ops, recipe):
+    """Mixtral-sized K and a slice of N: too big for the CPU oracle, so the
+    tensor-core result is compared with one-thread-per-element CUDA arithmetic."""
+    E, K, N, R = 8, 4096, 2048, 8192
+    g = torch.Generator().manual_seed(0)
+    rows = torch.tensor([1000, 1100, 900, 1024, 1050, 998, 1120, 1000], dtype=torch.int32, device=DEV)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    D = torch.zeros(R, N, dtype=torch.bfloat16, device=DEV)
+    ref = torch.zeros(R, N, dtype=torch.float32, device=DEV)
+    if recipe == "bf16":
+        B = (torch.randn(E, K, N, generator=g) / 64).to(torch.bfloat16).to(DEV)
+        ops._xpu_C.b200_grouped_gemm(x.to(DEV), None, B, None, None, D, rows, N, K, E, EPI_STORE, KN)
+        ops._xpu_C.b200_grouped_gemm_check(x.to(DEV), None, B, None, None, ref, rows, N, K, E, KN)
+    else:
+        Aq, As = O.per_token_group_fp8_quant(x, 128)
+        Bq = (torch.randn(E, K, N, generator=g) * 100).clamp(-448, 448).to(torch.float8_e4m3fn).to(DEV)
+        Bs = (torch.rand(E, K // 128, N // 128, generator=g) * 2e-4 + 1e-4).to(DEV)
+        ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq, Bs, None, D, rows, N, K, E, EPI_STORE, KN)
+        ops._xpu_C.b200_grouped_gemm_check(Aq.to(DEV), As.to(DEV), Bq, Bs, None, ref, rows, N, K, E, KN)
+    close(D, ref)

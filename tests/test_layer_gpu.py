@@ -1,0 +1,126 @@
+"""The whole layer through XpuFusedMoe.apply against the layer oracle, on the
+benchmark configurations: the tiny bf16 one at full size, the others with the
+token count (and, for the CPU-side check, the set of experts) cut down so the
+fp32 oracle finishes in seconds.  Tolerance 2e-2 for bf16 (the stated bound),
+5e-2 for block-FP8 (the reference's own bound for that recipe,
+tests/fused_moe/test_fused_moe.py:676,798 there)."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def to_dev(t):
+    return None if t is None else t.to(DEV)
+
+
+def build(cfg, layer, ep_rank=0, ep_size=1):
+    from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
+    w13, w2 = to_dev(layer["w13"]), to_dev(layer["w2"])
+    s13, s2 = to_dev(layer["w13_scale"]), to_dev(layer["w2_scale"])
+    if cfg["recipe"] == "mxfp4":
+        w13, w2 = w13.view(torch.float4_e2m1fn_x2), w2.view(torch.float4_e2m1fn_x2)
+    E_loc = w13.shape[0]
+    return XpuFusedMoe(w13, s13, to_dev(layer["w13_bias"]), w2, s2, to_dev(layer["w2_bias"]),
+                       cfg["k"], cfg["activation"], E_loc, ep_rank=ep_rank, ep_size=ep_size)
+
+
+def route_gpu(ops, cfg, layer):
+    T = layer["logits"].shape[0]
+    if cfg["routing"] == "softmax":
+        w = torch.empty(T, cfg["k"], dtype=torch.float32, device=DEV)
+        ids = torch.empty(T, cfg["k"], dtype=torch.int32, device=DEV)
+        src = torch.empty(T, cfg["k"], dtype=torch.int32, device=DEV)
+        ops._moe_C.topk_softmax(w, ids, src, to_dev(layer["logits"]), True, None, None)
+        return w, ids
+    return ops._moe_C.grouped_topk(to_dev(layer["logits"]), cfg["n_group"], cfg["topk_group"], cfg["k"],
+                                   True, cfg["scale"], to_dev(layer["score_bias"]), 1)
+
+
+def check(out, ref, tol):
+    out, ref = out.float().cpu(), ref.float()
+    err = (out - ref).abs()
+    bound = tol + tol * ref.abs()
+    assert (err <= bound).all(), f"max err {err.max():.4g}, {int((err > bound).sum())} of {err.numel()} out of bound"
+    # and in the aggregate the match is tighter than the element bound
+    assert err.mean() < 0.5 * tol * max(ref.abs().mean().item(), 1e-3) + 1e-3
+
+
+def test_c0_full(ops):
+    cfg = O.CONFIGS["c0"]
+    layer = O.make_layer(cfg)
+    moe = build(cfg, layer)
+    w, ids = route_gpu(ops, cfg, layer)
+    rw, rids = O.route(cfg, layer)
+    assert torch.equal(ids.cpu(), rids)
+    out = torch.empty(cfg["T"], cfg["H"], dtype=torch.bfloat16, device=DEV)
+    moe.apply(out, to_dev(layer["x"]), w, ids)
+    ref = O.fused_moe("bf16", layer["x"], layer["w13"], None, None, layer["w2"], None, None, rw, rids,
+                      "silu", out_dtype=torch.float32)
+    check(out, ref, 2e-2)
+
+
+@pytest.mark.parametrize("name,T,E_limit,tol", [("c1", 96, None, 5e-2), ("c2", 160, 24, 2e-2),
+                                                ("c3", 48, 20, 5e-2)])
+def test_reduced_configs(ops, name, T, E_limit, tol):
+    """Real H/I/E of the config, few tokens.  Only the first E_limit experts'
+    weights are built, and the routing is steered onto them with an expert_map
+    that marks the rest non-local (the layer's own expert-parallel masking), so
+    the CPU oracle stays small while every kernel runs at the real widths."""
+    cfg = dict(O.CONFIGS[name])
+    layer = O.make_layer(cfg, T=T, E_limit=E_limit)
+    E = cfg["E"]
+    E_loc = E_limit or E
+    w, ids = route_gpu(ops, cfg, layer)
+    rw, rids = O.route(cfg, layer)
+    assert torch.equal(ids.cpu(), rids)
+    emap = None
+    if E_limit:
+        emap = torch.full((E,), -1, dtype=torch.int32)
+        emap[:E_loc] = torch.arange(E_loc, dtype=torch.int32)
+    moe = build(cfg, layer)
+    if E_limit:
+        moe.total_experts_num = E
+    out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=DEV)
+    moe.apply(out, to_dev(layer["x"]), w, ids, expert_map=to_dev(emap))
+    ref = O.fused_moe(cfg["recipe"], layer["x"], layer["w13"], layer["w13_scale"], layer["w13_bias"],
+                      layer["w2"], layer["w2_scale"], layer["w2_bias"], rw, rids, cfg["activation"],
+                      expert_map=emap, num_local_experts=E_loc,
+                      quant_act=cfg["recipe"] == "fp8block", out_dtype=torch.float32)
+    check(out, ref, tol)
+
+
+def test_expert_parallel_partial_sums(ops):
+    """Each rank sees all tokens and masks non-local experts; the partial
+    outputs of the ranks add up to the single-rank result."""
+    cfg = O.CONFIGS["c0"]
+    layer = O.make_layer(cfg)
+    w, ids = route_gpu(ops, cfg, layer)
+    full = torch.empty(cfg["T"], cfg["H"], dtype=torch.bfloat16, device=DEV)
+    build(cfg, layer).apply(full, to_dev(layer["x"]), w, ids)
+    acc = torch.zeros(cfg["T"], cfg["H"], dtype=torch.float32, device=DEV)
+    ep = 4
+    per = cfg["E"] // ep
+    for r in range(ep):
+        part = {k: (v[r * per:(r + 1) * per] if k.startswith("w") and v is not None else v)
+                for k, v in layer.items()}
+        out = torch.empty_like(full)
+        build(cfg, part, ep_rank=r, ep_size=ep).apply(out, to_dev(layer["x"]), w, ids)
+        acc += out.float()
+    assert torch.allclose(acc, full.float(), atol=3e-2, rtol=3e-2)
+
+
+def test_already_quantised_activations(ops):
+    cfg = dict(O.CONFIGS["c1"], H=512, I=1024)
+    layer = O.make_layer(cfg, T=64)
+    w, ids = route_gpu(ops, cfg, layer)
+    moe = build(cfg, layer)
+    out1 = torch.empty(64, 512, dtype=torch.bfloat16, device=DEV)
+    moe.apply(out1, to_dev(layer["x"]), w, ids)
+    xq, xs = O.per_token_group_fp8_quant(layer["x"], 128)
+    out2 = torch.empty_like(out1)
+    moe.apply(out2, to_dev(xq), w, ids, a1q_scale=to_dev(xs))
+    assert torch.equal(out1, out2)

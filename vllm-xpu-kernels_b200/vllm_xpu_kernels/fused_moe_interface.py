@@ -24,6 +24,7 @@ Recipes, detected from the weight dtypes as the reference does
   bf16 number) and run on the 16-bit path with bf16 activations, which is the
   W4A16 arithmetic of the reference kernel.
 """
+import contextlib
 from typing import Optional
 
 import torch
@@ -126,6 +127,11 @@ class XpuFusedMoe:
             self._w2_16 = torch.ops._xpu_C.b200_dequant_weights(
                 w2.view(torch.uint8), w2_scales.view(torch.uint8))
 
+        # Optional list; when set, apply() appends (stage, start_event, end_event)
+        # for each stage, the way the reference's benchmark brackets its stages
+        # (benchmark/src/fused_moe_interface_.py:84-168 there).
+        self.stage_timer = None
+
         self.expert_map = expert_map
         if self.expert_map is None and self.ep_size > 1:
             self.expert_map = torch.empty((self.num_experts * self.ep_size), dtype=torch.int32,
@@ -137,6 +143,25 @@ class XpuFusedMoe:
         else:
             self.total_experts_num = self.num_experts * self.ep_size
         self.local_experts_num = self.num_experts
+
+    @contextlib.contextmanager
+    def _stage(self, name):
+        if self.stage_timer is None:
+            yield
+            return
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        yield
+        end.record()
+        self.stage_timer.append((name, start, end))
+
+    def launches_per_apply(self, num_rows: int) -> int:
+        """Kernels one apply() enqueues for `num_rows` already-quantised tokens."""
+        permute = 2 if num_rows * self.n_experts_per_token <= 2048 else 4
+        if self.is_block_fp8:
+            return permute + 4  # gemm1, silu+quant, gemm2, gather
+        return permute + 3      # gemm1 (activation fused), gemm2, gather
 
     # ------------------------------------------------------------------
     def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
@@ -169,17 +194,20 @@ class XpuFusedMoe:
                            if act_quant else None)
         rows_per_expert = torch.zeros((self.num_experts,), dtype=torch.int32, device=dev)
         row_map = torch.empty((num_rows, k), dtype=torch.int32, device=dev)
-        torch.ops._moe_C.remap_hidden_states(hidden_states, a1q_scale, remapped, remapped_scales,
-                                             expert_map, rows_per_expert, row_map, topk_ids,
-                                             self.total_experts_num, self.local_experts_num)
+        with self._stage("remap"):
+            torch.ops._moe_C.remap_hidden_states(hidden_states, a1q_scale, remapped,
+                                                 remapped_scales, expert_map, rows_per_expert,
+                                                 row_map, topk_ids, self.total_experts_num,
+                                                 self.local_experts_num)
 
         I, E = self.inter_size, self.num_experts
         oai = _is_swigluoai(self.activation)
         gemm = torch.ops._xpu_C.b200_grouped_gemm
         if self.is_block_fp8:
             gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
-            gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
-                 gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
+            with self._stage("gemm1"):
+                gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
+                     gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
             self._clamp(gemm1_out)
             if oai:
                 act = torch.empty((R, I), dtype=output.dtype, device=dev)
@@ -189,10 +217,12 @@ class XpuFusedMoe:
             else:
                 act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
                 act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
-                torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
+                with self._stage("act_quant"):
+                    torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
             gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
-            gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
-                 rows_per_expert, hidden_size, I, E, EPI_STORE, B_LAYOUT_KN)
+            with self._stage("gemm2"):
+                gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
+                     rows_per_expert, hidden_size, I, E, EPI_STORE, B_LAYOUT_KN)
         else:
             if self.is_mxfp4:
                 w13, w2, layout = self._w13_16, self._w2_16, B_LAYOUT_NK
@@ -209,20 +239,22 @@ class XpuFusedMoe:
                 else:
                     torch.ops._C.silu_and_mul(act, gemm1_out)
             else:
-                gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
-                     hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702, 7.0)
+                with self._stage("gemm1"):
+                    gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
+                         hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702,
+                         7.0)
             gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
-            gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, I, E,
-                 EPI_STORE, layout)
+            with self._stage("gemm2"):
+                gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, I,
+                     E, EPI_STORE, layout)
 
-        torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
+        with self._stage("gather"):
+            torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
+                                        self.num_experts)
 
     def _clamp(self, gemm1_out):
         lim = self.gemm1_clamp_limit
         if lim is not None and lim > 0:
-            if _is_swigluoai(self.activation):
-                gemm1_out[:, 0::2].clamp_(max=lim)
-                gemm1_out[:, 1::2].clamp_(min=-lim, max=lim)
-            else:
-                gemm1_out[:, :self.inter_size].clamp_(max=lim)
-                gemm1_out[:, self.inter_size:].clamp_(min=-lim, max=lim)
+            # first half / second half, as fused_moe_interface.py:436-441 of the reference
+            gemm1_out[:, :self.inter_size].clamp_(max=lim)
+            gemm1_out[:, self.inter_size:].clamp_(min=-lim, max=lim)
