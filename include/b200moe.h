@@ -3,10 +3,8 @@
  *
  * Plain pointers and sizes only: every pointer is a DEVICE pointer unless the
  * parameter name ends in `_host`; `stream` is a cudaStream_t passed as void*.
- * No call allocates, synchronises or creates streams (one entry at the end of
- * this header is the documented exception for allocation-free callers and it
- * allocates nothing either).  Scratch memory is passed in by the caller; its
- * size comes from the matching *_workspace_bytes() query.
+ * No call allocates, synchronises or creates streams.  Scratch memory is passed
+ * in by the caller; its size comes from the matching *_workspace_bytes() query.
  *
  * Every function returns one of the B200MOE_* status codes below and never
  * throws or aborts.  Citations name the operator of vllm-xpu-kernels that an
@@ -193,7 +191,9 @@ typedef struct b200moe_gemm_args {
   const void* bias;  /* [E,N] of bias_dtype or NULL                             */
   int bias_dtype;
   void* D;           /* [R,N] or [R,N/2] for the gated epilogues                */
-  float* d_scale;    /* [R,(N/2)/128] f32 when d_dtype == E4M3                  */
+  float* d_scale;    /* [R,(N/2)/128] f32 when d_dtype == E4M3 (FP8_BLOCK recipe
+                        with EPI_SILU_MUL only: the activation leaves the GEMM
+                        already quantised per token per 128 columns)             */
   const int32_t* rows_per_expert; /* i32 [E], device                           */
   int64_t R;         /* rows of A (upper bound on sum(rows_per_expert))         */
   int N, K, E;

@@ -118,6 +118,66 @@ def test_fp8_block(ops, E, avg, K, N):
     close(D, ref)
 
 
+@pytest.mark.parametrize("tile_n", ["128", "256"])
+@pytest.mark.parametrize("kind", ["bf16_kn", "bf16_nk", "fp8"])
+def test_both_tile_widths(ops, tile_n, kind, monkeypatch):
+    """The tile width is normally picked from the problem size; force each one."""
+    monkeypatch.setenv("B200MOE_TILE_N", tile_n)
+    E, K, N = 3, 512, 768
+    rows = torch.tensor([130, 0, 257], dtype=torch.int32)
+    R = 387
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    D = torch.zeros(R, N, dtype=torch.bfloat16, device=DEV)
+    if kind == "fp8":
+        Aq, As = O.per_token_group_fp8_quant(x, 128)
+        Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / K ** 0.5) for _ in range(E)])
+        Bq, Bs = torch.stack(Bq), torch.stack(Bs) * (1.0 + 0.25 * torch.rand(E, K // 128, N // 128, generator=g))
+        ref = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As), Bq, Bs, None, rows, torch.float32)
+        ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, D, rows.to(DEV),
+                                     N, K, E, EPI_STORE, KN)
+    else:
+        B = make_bf16(E, K, N, 3)
+        bias = (torch.randn(E, N, generator=g) * 0.1).to(torch.bfloat16)
+        ref = O.grouped_gemm("bf16", x, B, None, bias, rows, torch.float32)
+        layout = KN if kind == "bf16_kn" else NK
+        Bd = B.to(DEV) if layout == KN else B.transpose(1, 2).contiguous().to(DEV)
+        ops._xpu_C.b200_grouped_gemm(x.to(DEV), None, Bd, None, bias.to(DEV), D, rows.to(DEV), N, K, E,
+                                     EPI_STORE, layout)
+        for epi in (EPI_SILU, EPI_OAI):
+            D2 = torch.zeros(R, N // 2, dtype=torch.bfloat16, device=DEV)
+            ops._xpu_C.b200_grouped_gemm(x.to(DEV), None, Bd, None, bias.to(DEV), D2, rows.to(DEV), N, K, E,
+                                         epi, layout, 1.702, 7.0)
+            close(D2, O.silu_mul_fp32(ref) if epi == EPI_SILU else O.swigluoai_and_mul(ref))
+    close(D, ref)
+
+
+@pytest.mark.parametrize("E,avg,K,N", [(2, 100, 256, 512), (8, 60, 4096, 2048), (3, 200, 512, 28672 // 8)])
+def test_fp8_fused_silu_quant_epilogue(ops, E, avg, K, N):
+    """GEMM1 of the block-FP8 layer: SiLU*mul and the per-token-group-128
+    re-quantisation happen in the epilogue; output is e4m3 [R, N/2] + f32 scales."""
+    rows = ragged_rows(E, avg, K + 1)
+    R = int(rows.sum())
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    Aq, As = O.per_token_group_fp8_quant(x, 128)
+    Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / K ** 0.5) for _ in range(E)])
+    Bq, Bs = torch.stack(Bq), torch.stack(Bs)
+    h = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As), Bq, Bs, None, rows, torch.float32)
+    act = O.silu_mul_fp32(h)
+    I = N // 2
+    gact = act.view(R, I // 128, 128)
+    rs = torch.maximum(gact.abs().amax(-1) / 448.0, torch.tensor(O.FP8_MIN_SCALE))
+    Dq = torch.zeros(R, I, dtype=torch.float8_e4m3fn, device=DEV)
+    Ds = torch.zeros(R, I // 128, dtype=torch.float32, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, Dq, rows.to(DEV),
+                                 N, K, E, EPI_SILU, KN, 1.702, 7.0, Ds)
+    assert torch.allclose(Ds.cpu(), rs, rtol=1e-3, atol=1e-9)
+    deq = Dq.cpu().float().view(R, -1, 128) * Ds.cpu().unsqueeze(-1)
+    # within one e4m3 step of the exact activation (half a step of rounding + accumulation order)
+    assert ((deq - gact).abs() <= 0.07 * gact.abs() + 2e-3 * rs.unsqueeze(-1) + 1e-6).all()
+
+
 def test_fp8_weights_with_16bit_activations(ops):
     # what the reference kernel does natively: weights expanded, activations untouched
     E, K, N = 3, 256, 384

@@ -27,6 +27,8 @@
 // (frees tensor memory) instead of hanging.
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "common.cuh"
@@ -213,16 +215,20 @@ struct Config {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int CHUNK_COLS = kStageRowBytes / ELT;  // N columns per MN-major TMA box
   static constexpr int N_CHUNKS = BN / CHUNK_COLS;
-  static constexpr int ACC_BUFS = PROMOTE ? (512 / BN) : 2;
-  static constexpr int TMEM_COLS = ACC_BUFS * BN;        // 256 or 512
-  static constexpr int EPI_WARPS = BN / 32 >= 8 ? 8 : 4;
-  static constexpr int THREADS = 64 + EPI_WARPS * 32;
-  static constexpr int COLS_PER_THREAD = BN / (EPI_WARPS / 4);
+  static constexpr int ACC_BUFS = 512 / BN;              // tensor-memory accumulator ring (all 512 columns)
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int EPI_WARPS = 8;                    // two reader warps per TMEM lane quadrant
+  static constexpr int THREADS = 128 + EPI_WARPS * 32;   // warps 0..3: producer, MMA, 2 spare
+  static constexpr int CPT = BN / 2;                     // accumulator columns per reader thread
+  static constexpr int NCH = CPT / 32;                   // 32-column tcgen05.ld chunks per thread
   static constexpr bool GATED_SPLIT = EPI == B200MOE_EPI_SILU_MUL;  // tile = [gate half | up half]
+  // The fp8 128x256 tile keeps 128 fp32 accumulators per reader thread: the reader
+  // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
+  static constexpr bool REBALANCE_REGS = BN == 256;
   static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES;
-  static_assert(!(GATED_SPLIT && EPI_WARPS == 8), "split gated tiles are laid out for 4 reader warps");
   static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && N_CHUNKS < 2), "a split gated tile needs two weight boxes");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed by the tensor-memory allocation");
+  static_assert(NCH == 2 || NCH == 4, "reader pipeline alternates two 32-column buffers");
 };
 
 struct alignas(8) Barriers {
@@ -231,6 +237,89 @@ struct alignas(8) Barriers {
   uint64_t tfull[4];
   uint64_t tempty[4];
 };
+
+// Tensor-memory column (inside one accumulator buffer) of chunk c of a reader
+// thread in column group g.  In a split gated tile the thread reads CPT/2 gate
+// columns and the CPT/2 up columns that go with them.
+template <typename C>
+__device__ __forceinline__ int chunk_tmem_col(int g, int c) {
+  if (C::GATED_SPLIT)
+    return c < C::NCH / 2 ? g * (C::CPT / 2) + c * 32
+                          : C::BN / 2 + g * (C::CPT / 2) + (c - C::NCH / 2) * 32;
+  return g * C::CPT + c * 32;
+}
+
+// Column of the full-N problem that tensor-memory column `tcol` of tile `n_tile` holds.
+template <typename C>
+__device__ __forceinline__ int problem_col(int n_tile, int tcol, int N) {
+  if (C::GATED_SPLIT)
+    return (tcol < C::BN / 2 ? 0 : N / 2 - C::BN / 2) + n_tile * (C::BN / 2) + tcol;
+  return n_tile * C::BN + tcol;
+}
+
+// acc[] -> global memory for one row of one tile.
+template <typename C>
+__device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoord& tc, int g,
+                                              bool row_ok, int64_t grow, float (&acc)[C::CPT],
+                                              float* xchg) {
+  constexpr int CPT = C::CPT;
+  if (p.bias) {
+#pragma unroll
+    for (int c = 0; c < C::NCH; ++c) {
+      const int col0 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, c), p.N);
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < p.N)
+          acc[c * 32 + j] += load_bias(p.bias, p.bias_dtype,
+                                       static_cast<int64_t>(tc.expert) * p.N + col0 + j);
+    }
+  }
+  if constexpr (C::EPI == B200MOE_EPI_STORE) {
+    const int col0 = tc.n_tile * C::BN + g * CPT;
+    if (row_ok && col0 < p.N) store_row16<CPT>(p.D, p.d_dtype, grow * p.ldd + col0, acc, p.N - col0);
+  } else if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
+    constexpr int HALF = CPT / 2;
+    const int half_n = p.N / 2;
+    const int col0 = tc.n_tile * (C::BN / 2) + g * HALF;
+    float o[HALF];
+#pragma unroll
+    for (int j = 0; j < HALF; ++j) o[j] = silu_f32(acc[j]) * acc[HALF + j];
+    if (p.d_dtype == B200MOE_E4M3) {
+      // per-token-group-128 quantisation of the activation: the 128 output columns of
+      // this tile are one group, held by two threads (column groups 0 and 1)
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < HALF; ++j) amax = fmaxf(amax, fabsf(o[j]));
+      const int row = threadIdx.x & 127;  // quad*32 + lane for reader warps 4..11
+      xchg[g * 128 + row] = amax;
+      asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+      amax = fmaxf(amax, xchg[(g ^ 1) * 128 + row]);
+      const float s = fmaxf(amax / 448.0f, 1.0f / (448.0f * 512.0f));
+      if (row_ok && col0 < half_n) {
+        if (g == 0) p.d_scale[grow * (half_n / 128) + tc.n_tile] = s;
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.D) + grow * p.ldd + col0;
+#pragma unroll
+        for (int j = 0; j < HALF; j += 16) {
+          alignas(16) uint8_t q[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            q[i] = f32_to_e4m3(fmaxf(-448.0f, fminf(o[j + i] / s, 448.0f)));
+          *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(q);
+        }
+      }
+    } else if (row_ok && col0 < half_n) {
+      store_row16<HALF>(p.D, p.d_dtype, grow * p.ldd + col0, o, half_n - col0);
+    }
+  } else {  // SWIGLU_OAI: (gate, up) pairs are adjacent columns
+    const int col0 = tc.n_tile * C::BN + g * CPT;
+    float o[CPT / 2];
+#pragma unroll
+    for (int j = 0; j < CPT / 2; ++j)
+      o[j] = swiglu_oai_f32(acc[2 * j], acc[2 * j + 1], p.alpha, p.limit);
+    if (row_ok && col0 < p.N)
+      store_row16<CPT / 2>(p.D, p.d_dtype, grow * p.ldd + col0 / 2, o, (p.N - col0) / 2);
+  }
+}
 
 template <typename C>
 __global__ void __launch_bounds__(C::THREADS, 1)
@@ -241,6 +330,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float xchg[2][256];  // group-amax exchange of the quantising epilogue, by tile parity
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -276,9 +366,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   const int num_tiles = total_tiles(sched);
   volatile int* abort_p = &abort_flag;
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
-    if (lane == 0) {
+  if (warp < 4) {
+    if constexpr (C::REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == 0 && lane == 0) {
+      // ---------------- TMA producer ----------------
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -294,18 +385,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if constexpr (C::B_MN_MAJOR) {
 #pragma unroll
             for (int c = 0; c < C::N_CHUNKS; ++c) {
-              int col;
-              if constexpr (C::GATED_SPLIT) {
-                const int half = C::N_CHUNKS / 2;
-                col = (c < half ? 0 : p.N / 2) + tc.n_tile * (C::BN / 2) + (c % half) * C::CHUNK_COLS;
-              } else {
-                col = tc.n_tile * C::BN + c * C::CHUNK_COLS;
-              }
+              const int col = problem_col<C>(tc.n_tile, c * C::CHUNK_COLS, p.N);
               tma_load_3d(b_dst + c * (C::BK * kStageRowBytes), &map_b, &bars.full[stage], col,
                           kb * C::BK, tc.expert);
             }
           } else {
-            if (C::GATED_SPLIT) {
+            if constexpr (C::GATED_SPLIT) {
               tma_load_3d(b_dst, &map_b, &bars.full[stage], kb * C::BK, tc.n_tile * (C::BN / 2),
                           tc.expert);
               tma_load_3d(b_dst + (C::BN / 2) * kStageRowBytes, &map_b, &bars.full[stage],
@@ -318,10 +403,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ---------------- MMA issuer ----------------
       const uint32_t idesc = make_idesc(p.ab_fmt, p.ab_fmt, 0u, C::B_MN_MAJOR ? 1u : 0u, BM, C::BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -350,9 +433,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                       ? make_sdesc_sw128(b_addr + kk * C::UMMA_K * kStageRowBytes,
                                          C::BK * kStageRowBytes, 1024)
                       : make_sdesc_sw128(b_addr + kk * 32, 16, 1024);
-              const uint32_t acc = (kb > 0 || kk > 0) ? 1u : 0u;
-              if (C::KIND == KIND_F16) mma_f16(d_tmem, a_desc, b_desc, idesc, acc);
-              else mma_f8(d_tmem, a_desc, b_desc, idesc, acc);
+              const uint32_t accum = (kb > 0 || kk > 0) ? 1u : 0u;
+              if (C::KIND == KIND_F16) mma_f16(d_tmem, a_desc, b_desc, idesc, accum);
+              else mma_f8(d_tmem, a_desc, b_desc, idesc, accum);
             }
             mma_commit(&bars.empty[stage]);
             if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -364,142 +447,94 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else {
     // ---------------- accumulator readers / epilogue ----------------
-    const int ew = warp - 2;
-    const int quad = warp & 3;                       // TMEM lane quadrant this warp may read
-    const int col_group = C::EPI_WARPS == 8 ? (ew >> 2) : 0;
+    if constexpr (C::REBALANCE_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int ew = warp - 4;
+    const int quad = warp & 3;   // TMEM lane quadrant this warp may read
+    const int g = ew >> 2;       // column group
     const int row_in_tile = quad * 32 + lane;
-    constexpr int CPT = C::COLS_PER_THREAD;
-    constexpr int NCH = CPT / 32;
+    constexpr int CPT = C::CPT;
+    constexpr int NCH = C::NCH;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    const int nb_count = p.N / 128;
+    const int phases_per_tile = C::PROMOTE ? num_kb : 1;
     int buf = 0;
     uint32_t buf_phase = 0;
     bool ok = true;
-    const int phases_per_tile = C::PROMOTE ? num_kb : 1;
-    const int nb_count = p.N / 128;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    int tile_parity = 0;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_parity ^= 1) {
       const TileCoord tc = decode_tile(sched, t);
       const bool row_ok = row_in_tile < tc.rows_valid;
       const int64_t grow = static_cast<int64_t>(tc.row_start) + row_in_tile;
-      // Column of the full-N problem that TMEM column (col_group*CPT + j) holds.
-      // For the split gated tile the first BN/2 TMEM columns are gate columns
-      // and the second half the matching up columns.
-      float acc[C::PROMOTE ? CPT : 1];
+      float acc[CPT];
+      float ta[32], tb[32];
+      // weight-scale blocks of the first / second half of this thread's columns
+      int nb0 = 0, nb1 = 0;
+      const float* sa_ptr = nullptr;
+      const float* sb_ptr = nullptr;
+      float sa_n = 0.f, sb0_n = 0.f, sb1_n = 0.f;
       if constexpr (C::PROMOTE) {
 #pragma unroll
         for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+        nb0 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, 0), p.N) / 128;
+        nb1 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, NCH / 2), p.N) / 128;
+        nb0 = nb0 < nb_count ? nb0 : nb_count - 1;
+        nb1 = nb1 < nb_count ? nb1 : nb_count - 1;
+        sa_ptr = p.a_scale + grow * num_kb;
+        sb_ptr = p.b_scale + static_cast<int64_t>(tc.expert) * num_kb * nb_count;
+        sa_n = row_ok ? sa_ptr[0] : 0.f;
+        sb0_n = sb_ptr[nb0];
+        sb1_n = sb_ptr[nb1];
       }
-      const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+      // first load of the tile
+      ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
+      if (!ok) break;
+      tc_fence_after();
+      tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 0), ta);
 
       for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
-        ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t t_addr = tmem_base + lane_addr + buf * C::BN + col_group * CPT;
+        float s0 = 1.f, s1 = 1.f;
         if constexpr (C::PROMOTE) {
-          const float sa = row_ok ? p.a_scale[grow * num_kb + ph] : 0.f;
-#pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            // 128-column weight-scale block of this chunk
-            int gcol;
-            const int tcol = col_group * CPT + c * 32;
-            if (C::GATED_SPLIT)
-              gcol = (tcol < C::BN / 2 ? 0 : p.N / 2 - C::BN / 2) + tc.n_tile * (C::BN / 2) + tcol;
-            else
-              gcol = tc.n_tile * C::BN + tcol;
-            const int nb = gcol / 128 < nb_count ? gcol / 128 : nb_count - 1;
-            const float sb =
-                p.b_scale[(static_cast<int64_t>(tc.expert) * num_kb + ph) * nb_count + nb];
-            const float s = sa * sb;
-            float v[32];
-            tmem_ld_32x32(t_addr + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, v[j], acc[c * 32 + j]);
+          s0 = sa_n * sb0_n;
+          s1 = sa_n * sb1_n;
+          if (ph + 1 < phases_per_tile) {  // scales of the next K block, ahead of use
+            sa_n = row_ok ? sa_ptr[ph + 1] : 0.f;
+            sb0_n = sb_ptr[(ph + 1) * nb_count + nb0];
+            sb1_n = sb_ptr[(ph + 1) * nb_count + nb1];
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars.tempty[buf]);
         }
-        if (!C::PROMOTE || ph == phases_per_tile - 1) {
-          // ---- final epilogue of the tile ----
-          auto get_chunk = [&](int c, float (&v)[32]) {
-            if constexpr (C::PROMOTE) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = acc[c * 32 + j];
-            } else {
-              tmem_ld_32x32(t_addr + c * 32, v);
-              tmem_ld_wait();
-            }
-          };
-          if constexpr (C::EPI == B200MOE_EPI_STORE) {
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-              float v[32];
-              get_chunk(c, v);
-              const int col0 = tc.n_tile * C::BN + col_group * CPT + c * 32;
-              if (p.bias) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N)
-                    v[j] += load_bias(p.bias, p.bias_dtype,
-                                      static_cast<int64_t>(tc.expert) * p.N + col0 + j);
-              }
-              if (row_ok && col0 < p.N)
-                store_row16<32>(p.D, p.d_dtype, grow * p.ldd + col0, v, p.N - col0);
-            }
-          } else if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
-            // this thread: gate columns [0, CPT/2) and up columns [CPT/2, CPT) of its group
-            constexpr int HALF_CH = NCH / 2;
-            const int half_n = p.N / 2;
-#pragma unroll
-            for (int c = 0; c < HALF_CH; ++c) {
-              float g[32], u[32];
-              get_chunk(c, g);
-              get_chunk(c + HALF_CH, u);
-              const int col0 = tc.n_tile * (C::BN / 2) + c * 32;
-              if (p.bias) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < half_n) {
-                    g[j] += load_bias(p.bias, p.bias_dtype,
-                                      static_cast<int64_t>(tc.expert) * p.N + col0 + j);
-                    u[j] += load_bias(p.bias, p.bias_dtype,
-                                      static_cast<int64_t>(tc.expert) * p.N + half_n + col0 + j);
-                  }
-              }
-#pragma unroll
-              for (int j = 0; j < 32; ++j) g[j] = silu_f32(g[j]) * u[j];
-              if (row_ok && col0 < half_n)
-                store_row16<32>(p.D, p.d_dtype, grow * p.ldd + col0, g, half_n - col0);
-            }
-          } else {  // SWIGLU_OAI: (gate, up) pairs are adjacent columns
-#pragma unroll
-            for (int c = 0; c < NCH; ++c) {
-              float v[32];
-              get_chunk(c, v);
-              const int col0 = tc.n_tile * C::BN + col_group * CPT + c * 32;
-              if (p.bias) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (col0 + j < p.N)
-                    v[j] += load_bias(p.bias, p.bias_dtype,
-                                      static_cast<int64_t>(tc.expert) * p.N + col0 + j);
-              }
-              float o[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                o[j] = swiglu_oai_f32(v[2 * j], v[2 * j + 1], p.alpha, p.limit);
-              if (row_ok && col0 < p.N)
-                store_row16<16>(p.D, p.d_dtype, grow * p.ldd + col0 / 2, o, (p.N - col0) / 2);
-            }
-          }
-          if (!C::PROMOTE) {
+        for (int c = 0; c < NCH; ++c) {
+          float(&cur)[32] = (c & 1) ? tb : ta;
+          float(&nxt)[32] = (c & 1) ? ta : tb;
+          tmem_ld_wait_on(cur);
+          if (c + 1 < NCH) {
+            tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, c + 1), nxt);
+          } else {
+            // every column of this buffer is in registers: hand it back, start on the next
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars.tempty[buf]);
+            if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
+            if (ph + 1 < phases_per_tile) {
+              ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
+              if (ok) {
+                tc_fence_after();
+                tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 0), nxt);
+              }
+            }
+          }
+          if constexpr (C::PROMOTE) {
+            const float s = c < NCH / 2 ? s0 : s1;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, cur[j], acc[c * 32 + j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = cur[j];
           }
         }
-        if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
       }
+      if (!ok) break;
+      tile_epilogue<C>(p, tc, g, row_ok, grow, acc, xchg[tile_parity]);
     }
   }
 
@@ -593,7 +628,7 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   p.N = a.N;
   p.K = a.K;
   p.E = a.E;
-  p.ldd = a.epilogue == B200MOE_EPI_STORE ? a.N : a.N / 2;
+  p.ldd = a.epilogue == B200MOE_EPI_STORE ? a.N : a.N / 2;  // elements (bytes for e4m3)
   p.alpha = a.alpha;
   p.limit = a.limit;
   p.ab_fmt = a.a_dtype == B200MOE_BF16 ? 1 : 0;  // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
@@ -768,6 +803,7 @@ static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cu
     case B200MOE_EPI_STORE:
       return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, STAGES>>(a, B, b_dtype, st);
     case B200MOE_EPI_SILU_MUL:
+      // an MN-major split tile needs one weight box for the gate half and one for the up half
       if constexpr (MN && BN * (KIND == KIND_F16 ? 2 : 1) < 256) return B200MOE_UNSUPPORTED;
       else return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SILU_MUL, STAGES>>(a, B, b_dtype, st);
     case B200MOE_EPI_SWIGLU_OAI:
@@ -777,20 +813,39 @@ static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cu
   }
 }
 
+// 128x256 tiles halve the shared-memory and L2 traffic per flop; 128x128 tiles
+// give more CTAs something to do when the problem is small.
+static bool want_wide_tile(const b200moe_gemm_args& a) {
+  const char* force = getenv("B200MOE_TILE_N");
+  if (force) return atoi(force) == 256;
+  const int64_t n_eff = a.epilogue == B200MOE_EPI_SILU_MUL ? a.N / 2 : a.N;
+  const int64_t m_tiles = (a.R + BM - 1) / BM;
+  return n_eff % 128 == 0 && n_eff >= 256 && m_tiles * (n_eff / 128) >= 2 * kNumSMs;
+}
+
 extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspace,
                                     size_t workspace_bytes, void* stream) {
   int rc = validate(args);
   if (rc != B200MOE_OK || args->R == 0) return rc;
   b200moe_gemm_args a = *args;
   cudaStream_t st = as_stream(stream);
-  if (a.d_dtype != B200MOE_BF16 && a.d_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
   if (a.epilogue != B200MOE_EPI_STORE && (a.N % 2 != 0)) return B200MOE_INVALID_ARG;
+  const bool quant_out = a.d_dtype == B200MOE_E4M3;
+  if (!quant_out && a.d_dtype != B200MOE_BF16 && a.d_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
+  if (quant_out && (a.epilogue != B200MOE_EPI_SILU_MUL || !a.d_scale || (a.N / 2) % 128 != 0))
+    return B200MOE_UNSUPPORTED;
+  const bool wide = want_wide_tile(a);
 
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3) {
     if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
-    if (a.epilogue == B200MOE_EPI_SILU_MUL) return B200MOE_UNSUPPORTED;
+    if (a.epilogue == B200MOE_EPI_SILU_MUL) {
+      if ((a.N / 2) % 128 != 0) return B200MOE_UNSUPPORTED;
+      return launch_epi<KIND_F8, true, true, 256, 4>(a, a.B, B200MOE_E4M3, st);
+    }
+    if (wide) return launch_epi<KIND_F8, true, true, 256, 4>(a, a.B, B200MOE_E4M3, st);
     return launch_epi<KIND_F8, true, true, 128, 6>(a, a.B, B200MOE_E4M3, st);
   }
+  if (quant_out) return B200MOE_UNSUPPORTED;
 
   // 16-bit activations: weights must be 16-bit too; quantised weights are
   // expanded into the workspace first (slow path kept for API compatibility).
@@ -807,7 +862,11 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
     b_nk = a.recipe == B200MOE_RECIPE_MXFP4;
   }
   if (a.K % 8 != 0) return B200MOE_INVALID_ARG;
-  if (b_nk) return launch_epi<KIND_F16, false, false, 128, 6>(a, B, a.a_dtype, st);
+  if (b_nk) {
+    if (wide) return launch_epi<KIND_F16, false, false, 256, 4>(a, B, a.a_dtype, st);
+    return launch_epi<KIND_F16, false, false, 128, 6>(a, B, a.a_dtype, st);
+  }
+  if (wide) return launch_epi<KIND_F16, true, false, 256, 4>(a, B, a.a_dtype, st);
   return launch_epi<KIND_F16, true, false, 128, 6>(a, B, a.a_dtype, st);
 }
 

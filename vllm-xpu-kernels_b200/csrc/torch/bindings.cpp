@@ -397,7 +397,8 @@ int act_code(const Tensor& t, const char* op) {
 Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
                          const OptTensor& B_scale, const OptTensor& bias, Tensor D,
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
-                         int64_t epilogue, int64_t b_layout, double alpha, double limit) {
+                         int64_t epilogue, int64_t b_layout, double alpha, double limit,
+                         const OptTensor& D_scale = std::nullopt) {
   const char* op = "cutlass_grouped_gemm_interface";
   TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && D.is_contiguous(), op, ": A, B and D must be contiguous");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
@@ -412,6 +413,11 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
   a.B = B.data_ptr();
   a.b_layout = static_cast<int>(b_layout);
   a.D = D.data_ptr();
+  if (D_scale.has_value()) {
+    TORCH_CHECK(D_scale->scalar_type() == at::kFloat && D_scale->is_contiguous(), op,
+                ": output scales must be contiguous float32");
+    a.d_scale = D_scale->data_ptr<float>();
+  }
   a.rows_per_expert = rows_per_expert.data_ptr<int>();
   a.R = A.numel() / K;
   a.N = N;
@@ -467,9 +473,10 @@ Tensor cutlass_grouped_gemm_interface(const Tensor& ptr_A, const OptTensor& ptr_
 Tensor b200_grouped_gemm(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
                          const OptTensor& B_scale, const OptTensor& bias, Tensor D,
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
-                         int64_t epilogue, int64_t b_layout, double alpha, double limit) {
+                         int64_t epilogue, int64_t b_layout, double alpha, double limit,
+                         const OptTensor& D_scale) {
   return grouped_gemm_impl(A, A_scale, B, B_scale, bias, D, rows_per_expert, N, K, num_experts,
-                           epilogue, b_layout, alpha, limit);
+                           epilogue, b_layout, alpha, limit, D_scale);
 }
 
 Tensor b200_grouped_gemm_check(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
@@ -599,7 +606,7 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
   m.def(
       "b200_grouped_gemm(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? bias, "
       "Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, int "
-      "b_layout, float alpha=1.702, float limit=7.0) -> Tensor");
+      "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None) -> Tensor");
   m.def(
       "b200_grouped_gemm_check(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? "
       "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "

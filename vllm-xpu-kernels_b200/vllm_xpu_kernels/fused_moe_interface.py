@@ -159,9 +159,7 @@ class XpuFusedMoe:
     def launches_per_apply(self, num_rows: int) -> int:
         """Kernels one apply() enqueues for `num_rows` already-quantised tokens."""
         permute = 2 if num_rows * self.n_experts_per_token <= 2048 else 4
-        if self.is_block_fp8:
-            return permute + 4  # gemm1, silu+quant, gemm2, gather
-        return permute + 3      # gemm1 (activation fused), gemm2, gather
+        return permute + 3  # gemm1 (activation [+ quantisation] fused), gemm2, gather
 
     # ------------------------------------------------------------------
     def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
@@ -204,21 +202,31 @@ class XpuFusedMoe:
         oai = _is_swigluoai(self.activation)
         gemm = torch.ops._xpu_C.b200_grouped_gemm
         if self.is_block_fp8:
-            gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
-            with self._stage("gemm1"):
-                gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
-                     gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
-            self._clamp(gemm1_out)
-            if oai:
-                act = torch.empty((R, I), dtype=output.dtype, device=dev)
-                torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
-                from .moe_utils import quant_fp8_block_act
-                act_q, act_s = quant_fp8_block_act(act)
-            else:
+            clamp = self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0
+            if not oai and not clamp and I % 128 == 0:
+                # SiLU*mul and the group-128 re-quantisation run in the GEMM's epilogue
                 act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
                 act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
-                with self._stage("act_quant"):
-                    torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
+                with self._stage("gemm1"):
+                    gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
+                         act_q, rows_per_expert, 2 * I, hidden_size, E, EPI_SILU_MUL, B_LAYOUT_KN,
+                         1.702, 7.0, act_s)
+            else:
+                gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
+                with self._stage("gemm1"):
+                    gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
+                         gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
+                self._clamp(gemm1_out)
+                if oai:
+                    act = torch.empty((R, I), dtype=output.dtype, device=dev)
+                    torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
+                    from .moe_utils import quant_fp8_block_act
+                    act_q, act_s = quant_fp8_block_act(act)
+                else:
+                    act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
+                    act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
+                    with self._stage("act_quant"):
+                        torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
             gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
             with self._stage("gemm2"):
                 gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
