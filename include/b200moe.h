@@ -101,6 +101,30 @@ int b200moe_moe_align_block_size(const void* topk_ids, int ids_dtype,
                                  int32_t* num_tokens_post_pad, void* workspace,
                                  size_t workspace_bytes, void* stream);
 
+/* moe_align_block_size for hosts that are not allowed to allocate device memory
+ * around the call: an inference server that handed all of HBM to its own pools at
+ * start-up, a plug-in interface whose contract forbids cudaMalloc on the request
+ * path, a C host with no allocator to lend a workspace from.  It has no
+ * counterpart in vllm-xpu-kernels (whose operator allocates its scratch with
+ * torch).  Same arguments and results as b200moe_moe_align_block_size minus the
+ * workspace: the scratch is a 256 KiB array built into the library (every GPU
+ * that loads the library carries it until the process ends).
+ *   Limit: ceil(numel / 2048) * num_experts <= 65536; larger problems get
+ *   B200MOE_WORKSPACE_TOO_SMALL and a message in b200moe_last_error().
+ *   The first call on each device looks the array's device address up once, with
+ *   that device current; make that first call before any stream capture.
+ *   All calls on a device share the array: two calls whose kernels can overlap
+ *   on the GPU (different streams) race; calls on one stream are safe, and
+ *   nothing needs clearing between them.
+ * Calls no cudaMalloc / cudaFree or allocating library routine. */
+int b200moe_moe_align_block_size_static(const void* topk_ids, int ids_dtype,
+                                        int64_t numel, int num_experts,
+                                        int block_size, const int32_t* expert_map,
+                                        int32_t* sorted_token_ids,
+                                        int64_t sorted_capacity, int32_t* expert_ids,
+                                        int64_t blocks_capacity,
+                                        int32_t* num_tokens_post_pad, void* stream);
+
 /* init_expert_map (csrc/moe/torch_bindings.cpp:86-91, csrc/moe/init_expert_map.cpp:78-95). */
 int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,
                             int ep_rank, int ep_size, void* stream);

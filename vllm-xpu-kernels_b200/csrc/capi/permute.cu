@@ -13,6 +13,10 @@
 //                 rank among equal experts comes from a warp match plus
 //                 per-warp running offsets, never from atomics.
 // Inputs that fit one chunk take a single fused launch.
+#include <stdio.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -348,7 +352,7 @@ __global__ void init_expert_map_kernel(int32_t* map, int num_local, int ep_rank,
 
 using namespace b200moe;
 
-static size_t grouping_workspace(int64_t numel, int num_keys) {
+size_t grouping_workspace(int64_t numel, int num_keys) {
   const int64_t n_cta = (numel + kChunk - 1) / kChunk;
   return n_cta <= 1 ? 0 : static_cast<size_t>(n_cta) * num_keys * sizeof(int);
 }
@@ -417,4 +421,75 @@ extern "C" int b200moe_remap_hidden_states(const void* hidden, const void* scale
     rc = launch_status("copy_rows_kernel");
   }
   return rc;
+}
+
+// ---- moe_align_block_size for callers that cannot allocate ----------------------
+
+namespace b200moe {
+namespace {
+
+// Scratch of the allocation-free entry point: 64 Ki ints = 256 KiB of every GPU
+// that loads this library, held until the process exits.
+constexpr int kStaticScratchInts = 64 * 1024;
+static __device__ __align__(256) int g_align_static_scratch[kStaticScratchInts];
+
+constexpr int kMaxDevices = 64;
+
+// Device address of the array above on the current device.  In host code the
+// array's name is only a handle for the runtime, never a pointer a kernel could
+// use, so the address is looked up once per device (with that device current).
+int* static_scratch_on_current_device() {
+  static std::mutex mu;
+  static int* cached[kMaxDevices] = {};
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_last_error("moe_align_block_size_static: cudaGetDevice", err);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_align_static_scratch);
+    if (err != cudaSuccess || !ptr) {
+      set_last_error("moe_align_block_size_static: cudaGetSymbolAddress", err);
+      return nullptr;
+    }
+    cached[dev] = static_cast<int*>(ptr);
+  }
+  return cached[dev];
+}
+
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_moe_align_block_size_static(const void* topk_ids, int ids_dtype,
+                                                   int64_t numel, int num_experts, int block_size,
+                                                   const int32_t* expert_map,
+                                                   int32_t* sorted_token_ids,
+                                                   int64_t sorted_capacity, int32_t* expert_ids,
+                                                   int64_t blocks_capacity,
+                                                   int32_t* num_tokens_post_pad, void* stream) {
+  if (numel < 0 || num_experts <= 0) return B200MOE_INVALID_ARG;
+  const size_t need = grouping_workspace(numel, num_experts);
+  if (need > sizeof(int) * static_cast<size_t>(kStaticScratchInts)) {
+    static thread_local char msg[160];
+    snprintf(msg, sizeof(msg),
+             "moe_align_block_size_static: ceil(numel/2048)*num_experts = %zu ints exceeds the "
+             "built-in scratch of %d ints; use b200moe_moe_align_block_size with a workspace",
+             need / sizeof(int), kStaticScratchInts);
+    set_last_error(msg, cudaErrorInvalidValue);
+    return B200MOE_WORKSPACE_TOO_SMALL;
+  }
+  int* scratch = nullptr;
+  if (need > 0) {
+    scratch = static_scratch_on_current_device();
+    if (!scratch) return B200MOE_CUDA_ERROR;
+  }
+  // Nothing in the scratch has to start at zero: the count pass overwrites every
+  // entry the scan and placement passes read.
+  return b200moe_moe_align_block_size(topk_ids, ids_dtype, numel, num_experts, block_size,
+                                      expert_map, sorted_token_ids, sorted_capacity, expert_ids,
+                                      blocks_capacity, num_tokens_post_pad, scratch,
+                                      sizeof(int) * static_cast<size_t>(kStaticScratchInts), stream);
 }

@@ -42,6 +42,9 @@ SIGNATURES = {
     "b200moe_moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p,
                                              c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                              c_void_p, c_size_t, c_void_p]),
+    "b200moe_moe_align_block_size_static": (c_int, [c_void_p, c_int, c_int64, c_int, c_int,
+                                                    c_void_p, c_void_p, c_int64, c_void_p,
+                                                    c_int64, c_void_p, c_void_p]),
     "b200moe_init_expert_map": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200moe_remap_hidden_states_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "b200moe_remap_hidden_states": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
