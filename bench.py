@@ -83,16 +83,18 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
-def make_device_layer(cfg, dev, seed=0):
+def make_device_layer(cfg, dev, seed=0, experts=None):
     """Synthetic layer generated on the device (the CPU generator of the oracle is too slow at
-    1.4 GB of weights): weights N(0, 1/fan_in) quantised to e4m3 per 128x128 block."""
+    1.4 GB of weights): weights N(0, 1/fan_in) quantised to e4m3 per 128x128 block.  Each
+    expert has its own seed, so a rank that owns a slice of the experts builds only those."""
     import vllm_xpu_kernels._C  # noqa: F401
-    g = torch.Generator(device=dev).manual_seed(seed)
-    H, I, E = cfg["H"], cfg["I"], cfg["E"]
+    H, I = cfg["H"], cfg["I"]
+    experts = list(range(cfg["E"])) if experts is None else list(experts)
 
     def quant(K, N):
         qs, ss = [], []
-        for _ in range(E):
+        for e in experts:
+            g = torch.Generator(device=dev).manual_seed(seed * 100003 + e * 7 + (K % 5))
             w = torch.randn(K, N, generator=g, device=dev) / K ** 0.5
             blk = w.view(K // 128, 128, N // 128, 128)
             s = (blk.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
@@ -117,13 +119,18 @@ def make_inputs(cfg, T, seed):
 class Layer:
     """Routing + quantisation + XpuFusedMoe.apply, the sequence a caller runs per batch."""
 
-    def __init__(self, cfg, weights, T, dev):
+    def __init__(self, cfg, weights, T, dev, group=None):
         from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
         from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
         self.cfg, self.T, self.dev = cfg, T, dev
         self.quant = quant_fp8_block_act
+        E_loc = weights["w13"].shape[0]
         self.moe = XpuFusedMoe(weights["w13"], weights["w13_scale"], None, weights["w2"],
-                               weights["w2_scale"], None, cfg["k"], cfg["activation"], cfg["E"])
+                               weights["w2_scale"], None, cfg["k"], cfg["activation"], E_loc)
+        self.ep = None
+        if group is not None:
+            from vllm_xpu_kernels.ep import ExpertParallel, make_local_fn
+            self.ep = ExpertParallel(group, E_loc, make_local_fn(self.moe))
         k = cfg["k"]
         self.w = torch.empty(T, k, dtype=torch.float32, device=dev)
         self.ids = torch.empty(T, k, dtype=torch.int32, device=dev)
@@ -133,7 +140,10 @@ class Layer:
     def step(self, x, logits):
         torch.ops._moe_C.topk_softmax(self.w, self.ids, self.src, logits, True, None, None)
         xq, xs = self.quant(x)
-        self.moe.apply(self.out, xq, self.w, self.ids, a1q_scale=xs)
+        if self.ep is not None:
+            self.ep.apply(self.out, xq, self.w, self.ids, scales=xs)
+        else:
+            self.moe.apply(self.out, xq, self.w, self.ids, a1q_scale=xs)
         return self.out
 
 
@@ -181,9 +191,12 @@ def run_reference(args, cfg):
 
 
 def workload_config(args, cfg):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    par = "1 GPU" if world == 1 else (f"expert-parallel over {world} GPUs ({cfg['E'] // world} experts each), "
+                                      "tokens data-parallel, NCCL all-to-all dispatch/combine")
     return {"workload": f"{args.config}: Mixtral-8x7B-shaped fused-MoE layer, FP8 e4m3 weights with "
                         "128x128 fp32 block scales, per-token-group-128 FP8 activations, softmax top-2",
-            "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
+            "parallelism": par, "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
             "experts": cfg["E"], "topk": cfg["k"], "l2": "256 MiB buffer written between timed steps"}
 
 
@@ -217,8 +230,10 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     T = cfg["T"]
-    weights = make_device_layer(cfg, dev)
-    layer = Layer(cfg, weights, T, dev)
+    assert cfg["E"] % world == 0, "the expert count must divide over the ranks"
+    per = cfg["E"] // world
+    weights = make_device_layer(cfg, dev, experts=range(rank * per, (rank + 1) * per))
+    layer = Layer(cfg, weights, T, dev, group=dist.group.WORLD if world > 1 else None)
     x_host, logits_host = make_inputs(cfg, T, seed=rank)
     x_pin, logits_pin = x_host.pin_memory(), logits_host.pin_memory()
     out_pin = torch.empty(T, cfg["H"], dtype=torch.bfloat16).pin_memory()
@@ -301,7 +316,7 @@ def main():
                          "ms_per_launch": gemm1_ms},
             "clocks": clk.summary(),
         }
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
             Tc = cpu_sample_tokens(cfg)

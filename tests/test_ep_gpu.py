@@ -1,0 +1,63 @@
+"""Expert-parallel layer on two GPUs (NCCL): tokens data-parallel, experts sharded,
+all-to-all dispatch/combine around the local CUDA layer; result = single-GPU oracle."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from conftest import PKG_DIR, ROOT
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, recipe, result):
+    for p in (ROOT, PKG_DIR):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import vllm_xpu_kernels._C  # noqa: F401
+    import vllm_xpu_kernels._moe_C  # noqa: F401
+    from vllm_xpu_kernels.ep import ExpertParallel, make_local_fn
+    from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
+    from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
+    cfg = dict(O.CONFIGS["c0" if recipe == "bf16" else "c1"], T=96, H=256, I=512)
+    layer = O.make_layer(cfg, seed=0)
+    per = cfg["E"] // world
+    sl = slice(rank * per, (rank + 1) * per)
+    d = lambda t: None if t is None else t[sl].to(dev)  # noqa: E731
+    moe = XpuFusedMoe(d(layer["w13"]), d(layer["w13_scale"]), None, d(layer["w2"]), d(layer["w2_scale"]),
+                      None, cfg["k"], "silu", per)
+    ep = ExpertParallel(dist.group.WORLD, per, make_local_fn(moe))
+    tok = O.make_layer(dict(cfg, E=cfg["E"]), seed=50 + rank, E_limit=1)
+    x, logits = tok["x"], tok["logits"]
+    w, ids = O.topk_softmax(logits, cfg["k"], True)
+    out = torch.empty(cfg["T"], cfg["H"], dtype=torch.bfloat16, device=dev)
+    xd, scales = x.to(dev), None
+    if recipe == "fp8block":
+        xd, scales = quant_fp8_block_act(xd)
+    ep.apply(out, xd, w.to(dev), ids.to(dev), scales=scales)
+    torch.cuda.synchronize()
+    ref = O.fused_moe(recipe, x, layer["w13"], layer["w13_scale"], None, layer["w2"], layer["w2_scale"],
+                      None, w, ids, "silu", out_dtype=torch.float32)
+    err = (out.float().cpu() - ref).abs()
+    tol = 2e-2 if recipe == "bf16" else 5e-2
+    result[rank] = bool((err <= tol + tol * ref.abs()).all())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("recipe", ["bf16", "fp8block"])
+def test_expert_parallel_two_gpus(recipe):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with mp.Manager() as m:
+        result = m.dict()
+        mp.spawn(_worker, args=(2, 29621 + (recipe != "bf16"), recipe, result), nprocs=2, join=True)
+        assert result[0] and result[1]

@@ -171,7 +171,7 @@ class XpuFusedMoe:
         weights.  ``topk_weights`` is f32 ``[T, k]``; ``topk_ids`` int32/int64
         global expert ids; ``expert_map`` int32 global -> local id or -1."""
         num_rows, hidden_size = hidden_states.shape
-        k = self.n_experts_per_token
+        k = topk_ids.shape[1]  # n_experts_per_token, or 1 for rows that arrive already dispatched
         R = num_rows * k
         dev = hidden_states.device
         if expert_map is None and self.ep_size > 1:
