@@ -31,6 +31,28 @@ sys.path.insert(0, os.path.join(ROOT, "vllm-xpu-kernels_b200"))
 
 import torch  # noqa: E402
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one w13 GEMM launch, from the ncu capture
+# summarised under profiles/ (captured on a 2-expert slice, scaled by the expert count).
+TRAFFIC_BYTES_PER_LAUNCH = {}
+
+# The benchmark configurations (shapes of BASELINE.json's configs 0-3).
+CONFIGS = {
+    "c0": dict(T=64, H=1024, I=2048, E=8, k=2, recipe="bf16", routing="softmax", activation="silu",
+               bias=False, name="tiny bf16 layer"),
+    "c1": dict(T=4096, H=4096, I=14336, E=8, k=2, recipe="fp8block", routing="softmax",
+               activation="silu", bias=False,
+               name="Mixtral-8x7B-shaped layer, FP8 e4m3 weights with 128x128 fp32 block scales, "
+                    "per-token-group-128 FP8 activations, softmax top-2"),
+    "c2": dict(T=8192, H=2880, I=2880, E=128, k=4, recipe="mxfp4", routing="softmax",
+               activation="swigluoai", bias=True,
+               name="gpt-oss-120b-shaped layer, MXFP4 weights (expanded to bf16 once, W4A16), bf16 "
+                    "biases, SwigluOAI, softmax top-4"),
+    "c3": dict(T=16384, H=7168, I=2048, E=256, k=8, recipe="fp8block", routing="grouped",
+               activation="silu", bias=False, n_group=8, topk_group=4, scale=2.5,
+               name="DeepSeek-V3-shaped routed experts, FP8 block-scaled, sigmoid + bias grouped "
+                    "top-8 (8 groups, 4 kept), scale 2.5; shared expert not included"),
+}
+
 
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -83,36 +105,72 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
+def _quant_fp8_block(w):
+    K, N = w.shape
+    blk = w.view(K // 128, 128, N // 128, 128)
+    s = (blk.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+    q = (blk / s.view(K // 128, 1, N // 128, 1)).clamp(-448, 448).view(K, N).to(torch.float8_e4m3fn)
+    return q, s
+
+
+def _quant_mxfp4(w):
+    """[N, K] -> packed e2m1 pairs [N, K/2] + e8m0 [N, K/32], scale rounded up to a power of two,
+    values to the nearest code point."""
+    N, K = w.shape
+    g = w.view(N, K // 32, 32)
+    amax = g.abs().amax(-1).clamp_min(1e-30)
+    e = torch.ceil(torch.log2(amax / 6.0)).clamp(-127, 127)
+    y = (g * torch.exp2(-e).unsqueeze(-1)).clamp(-6.0, 6.0)
+    a = y.abs()
+    code = torch.zeros_like(a, dtype=torch.uint8)
+    for bnd in (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0):
+        code += (a > bnd).to(torch.uint8)
+    code |= (y < 0).to(torch.uint8) << 3
+    code = code.view(N, K)
+    return (code[:, 1::2] << 4) | code[:, 0::2], (e + 127).to(torch.uint8)
+
+
 def make_device_layer(cfg, dev, seed=0, experts=None):
-    """Synthetic layer generated on the device (the CPU generator of the oracle is too slow at
-    1.4 GB of weights): weights N(0, 1/fan_in) quantised to e4m3 per 128x128 block.  Each
-    expert has its own seed, so a rank that owns a slice of the experts builds only those."""
+    """Synthetic weights generated on the device (the CPU generator of the oracle is too slow
+    at GB sizes): N(0, 1/fan_in), quantised per recipe, in the layouts the operators take.
+    Each expert has its own seed, so a rank that owns a slice of the experts builds only those."""
     import vllm_xpu_kernels._C  # noqa: F401
-    H, I = cfg["H"], cfg["I"]
+    H, I, recipe = cfg["H"], cfg["I"], cfg["recipe"]
     experts = list(range(cfg["E"])) if experts is None else list(experts)
 
-    def quant(K, N):
+    def build(K, N, tag):
         qs, ss = [], []
         for e in experts:
-            g = torch.Generator(device=dev).manual_seed(seed * 100003 + e * 7 + (K % 5))
+            g = torch.Generator(device=dev).manual_seed(seed * 100003 + e * 7 + tag)
             w = torch.randn(K, N, generator=g, device=dev) / K ** 0.5
-            blk = w.view(K // 128, 128, N // 128, 128)
-            s = (blk.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
-            qs.append((blk / s.view(K // 128, 1, N // 128, 1)).clamp(-448, 448).view(K, N)
-                      .to(torch.float8_e4m3fn))
+            if recipe == "fp8block":
+                q, s = _quant_fp8_block(w)
+            elif recipe == "mxfp4":
+                q, s = _quant_mxfp4(w.t().contiguous())
+            else:
+                q, s = w.to(torch.bfloat16), None
+            qs.append(q)
             ss.append(s)
-            del w, blk
-        return torch.stack(qs), torch.stack(ss)
+            del w
+        return torch.stack(qs), (torch.stack(ss) if ss[0] is not None else None)
 
-    w13, s13 = quant(H, 2 * I)
-    w2, s2 = quant(I, H)
-    return dict(w13=w13, w13_scale=s13, w2=w2, w2_scale=s2)
+    w13, s13 = build(H, 2 * I, 1)
+    w2, s2 = build(I, H, 2)
+    out = dict(w13=w13, w13_scale=s13, w2=w2, w2_scale=s2, w13_bias=None, w2_bias=None)
+    if cfg["bias"]:
+        g = torch.Generator(device=dev).manual_seed(seed + 17)
+        out["w13_bias"] = (torch.randn(len(experts), 2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        out["w2_bias"] = (torch.randn(len(experts), H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    return out
 
 
 def make_inputs(cfg, T, seed):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(T, cfg["H"], generator=g).to(torch.bfloat16)
     logits = torch.randn(T, cfg["E"], generator=g)
+    if cfg.get("skew"):  # Zipf-like expert load of the decode sweep
+        rank = torch.randperm(cfg["E"], generator=torch.Generator().manual_seed(1)) + 1
+        logits = logits + 1.5 * torch.log(1.0 / rank.float())
     return x, logits
 
 
@@ -125,8 +183,11 @@ class Layer:
         self.cfg, self.T, self.dev = cfg, T, dev
         self.quant = quant_fp8_block_act
         E_loc = weights["w13"].shape[0]
-        self.moe = XpuFusedMoe(weights["w13"], weights["w13_scale"], None, weights["w2"],
-                               weights["w2_scale"], None, cfg["k"], cfg["activation"], E_loc)
+        w13, w2 = weights["w13"], weights["w2"]
+        if cfg["recipe"] == "mxfp4":
+            w13, w2 = w13.view(torch.float4_e2m1fn_x2), w2.view(torch.float4_e2m1fn_x2)
+        self.moe = XpuFusedMoe(w13, weights["w13_scale"], weights["w13_bias"], w2, weights["w2_scale"],
+                               weights["w2_bias"], cfg["k"], cfg["activation"], E_loc)
         self.ep = None
         if group is not None:
             from vllm_xpu_kernels.ep import ExpertParallel, make_local_fn
@@ -136,15 +197,32 @@ class Layer:
         self.ids = torch.empty(T, k, dtype=torch.int32, device=dev)
         self.src = torch.empty(T, k, dtype=torch.int32, device=dev)
         self.out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=dev)
+        self.score_bias = None
+        if cfg["routing"] == "grouped":
+            g = torch.Generator().manual_seed(3)
+            self.score_bias = (torch.randn(cfg["E"], generator=g) * 0.01).to(dev)
+
+    def route(self, logits):
+        cfg = self.cfg
+        if cfg["routing"] == "softmax":
+            torch.ops._moe_C.topk_softmax(self.w, self.ids, self.src, logits, True, None, None)
+            return self.w, self.ids
+        return torch.ops._moe_C.grouped_topk(logits, cfg["n_group"], cfg["topk_group"], cfg["k"], True,
+                                             cfg["scale"], self.score_bias, 1)
 
     def step(self, x, logits):
-        torch.ops._moe_C.topk_softmax(self.w, self.ids, self.src, logits, True, None, None)
-        xq, xs = self.quant(x)
+        w, ids = self.route(logits)
+        scales = None
+        if self.cfg["recipe"] == "fp8block":
+            x, scales = self.quant(x)
         if self.ep is not None:
-            self.ep.apply(self.out, xq, self.w, self.ids, scales=xs)
+            self.ep.apply(self.out, x, w, ids, scales=scales)
         else:
-            self.moe.apply(self.out, xq, self.w, self.ids, a1q_scale=xs)
+            self.moe.apply(self.out, x, w, ids, a1q_scale=scales)
         return self.out
+
+    def launches_per_step(self):
+        return 1 + (1 if self.cfg["recipe"] == "fp8block" else 0) + self.moe.launches_per_apply(self.T)
 
 
 def flops_per_token(cfg):
@@ -152,13 +230,21 @@ def flops_per_token(cfg):
 
 
 def cpu_layer_step(cfg, layer_cpu, x, logits, O):
-    w, ids = O.topk_softmax(logits, cfg["k"], True)
-    return O.fused_moe(cfg["recipe"], x, layer_cpu["w13"], layer_cpu["w13_scale"], None,
-                       layer_cpu["w2"], layer_cpu["w2_scale"], None, w, ids, cfg["activation"])
+    """One pass of the CPU oracle (a port of the reference's torch path) over a token sample."""
+    if cfg["routing"] == "softmax":
+        w, ids = O.topk_softmax(logits, cfg["k"], True)
+    else:
+        bias = torch.randn(cfg["E"], generator=torch.Generator().manual_seed(3)) * 0.01
+        w, ids = O.grouped_topk(logits, cfg["k"], True, cfg["n_group"], cfg["topk_group"], "sigmoid",
+                                cfg["scale"], bias)
+    return O.fused_moe(cfg["recipe"], x, layer_cpu["w13"], layer_cpu["w13_scale"], layer_cpu["w13_bias"],
+                       layer_cpu["w2"], layer_cpu["w2_scale"], layer_cpu["w2_bias"], w, ids,
+                       cfg["activation"], quant_act=cfg["recipe"] == "fp8block")
 
 
 def cpu_sample_tokens(cfg):
-    return 256
+    """Tokens per CPU pass: sized so one pass is seconds, not minutes, on a 16-core host."""
+    return 256 if cfg["E"] <= 8 else 64
 
 
 def run_reference(args, cfg):
@@ -169,9 +255,9 @@ def run_reference(args, cfg):
     from oracle import moe_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    Tc = cpu_sample_tokens(cfg)
-    layer = O.make_layer(cfg, T=Tc)
-    x, logits = layer["x"], layer["logits"]
+    Tc = min(cpu_sample_tokens(cfg), cfg["T"])
+    layer = make_device_layer(cfg, torch.device("cpu"))
+    x, logits = make_inputs(cfg, Tc, seed=0)
     for _ in range(min(args.warmup, 1)):
         cpu_layer_step(cfg, layer, x, logits, O)
     t0 = time.perf_counter()
@@ -194,9 +280,7 @@ def workload_config(args, cfg):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     par = "1 GPU" if world == 1 else (f"expert-parallel over {world} GPUs ({cfg['E'] // world} experts each), "
                                       "tokens data-parallel, NCCL all-to-all dispatch/combine")
-    return {"workload": f"{args.config}: Mixtral-8x7B-shaped fused-MoE layer, FP8 e4m3 weights with "
-                        "128x128 fp32 block scales, per-token-group-128 FP8 activations, softmax top-2",
-            "parallelism": par, "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
+    return {"workload": f"{args.config}: {cfg['name']}", "parallelism": par, "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
             "experts": cfg["E"], "topk": cfg["k"], "l2": "256 MiB buffer written between timed steps"}
 
 
@@ -210,9 +294,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling, sweeps)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling)")
+    ap.add_argument("--skew", action="store_true", help="Zipf-like expert load (decode sweep)")
     args = ap.parse_args()
-    from oracle import moe_oracle as O  # workload table (and the CPU baseline leg)
-    cfg = dict(O.CONFIGS[args.config])
+    cfg = dict(CONFIGS[args.config])
+    if args.skew:
+        cfg["skew"] = True
     if args.tokens:
         cfg["T"] = args.tokens
     if args.experts:
@@ -296,30 +382,38 @@ def main():
         R = T * cfg["k"]
         gemm1_flops = 2.0 * R * cfg["H"] * 2 * cfg["I"]
         achieved = gemm1_flops / (gemm1_ms * 1e-3) / 1e12 if gemm1_ms > 0 else 0.0
-        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        fp8 = cfg["recipe"] == "fp8block"
+        peak = (2.0 if fp8 else 1.0) * peaks["bf16_tflops_sustained"]
         line = {
             "metric": "fused_moe_layer_tokens_per_s", "value": world * T / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "fp8_e4m3 (fp32 accumulate)", "data": "synthetic",
+            "dtype": {"fp8block": "fp8_e4m3 (fp32 accumulate)", "bf16": "bf16 (fp32 accumulate)",
+                      "mxfp4": "mxfp4 weights as bf16 x bf16 (fp32 accumulate)"}[cfg["recipe"]],
+            "data": "synthetic",
             "config": workload_config(args, cfg),
             "tflops": world * T * flops_per_token(cfg) / (ms * 1e-3) / 1e12,
             "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s",
                     "h2d_bytes_per_step": x_pin.numel() * 2 + logits_pin.numel() * 4,
                     "d2h_bytes_per_step": out_pin.numel() * 2},
-            "gpu_launches": (2 + layer.moe.launches_per_apply(T)) * args.steps,  # + topk, quant
-            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (w13, fp8 block-scaled)",
+            "gpu_launches": layer.launches_per_step() * args.steps,
+            "roofline": {"bound": "tensor",
+                         "kernel": "grouped_gemm_kernel (w13" + (", fp8 block-scaled, fused SiLU*mul + "
+                                                                 "group quantisation)" if fp8 else ")"),
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None,
-                         "peak_source": f"2 x {peaks['source']} sustained bf16 cuBLAS rate "
-                                        "(fp8 runs at twice the bf16 rate on tcgen05)",
-                         "ms_per_launch": gemm1_ms},
+                         "frac": achieved / peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(args.config)
+                         if not (args.tokens or args.experts) else None,
+                         "peak_source": (f"2 x {peaks['source']} sustained bf16 cuBLAS rate (fp8 issues at "
+                                         "twice the bf16 rate on tcgen05; MEASURED_PEAKS has no fp8 figure)")
+                         if fp8 else f"{peaks['source']} sustained bf16 cuBLAS rate",
+                         "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms},
             "clocks": clk.summary(),
         }
         if not args.no_cpu_baseline and world == 1:
+            from oracle import moe_oracle as O  # CPU-baseline leg only
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
-            Tc = cpu_sample_tokens(cfg)
+            Tc = min(cpu_sample_tokens(cfg), T)
             cpu_layer = {k: (v.cpu() if v is not None else None) for k, v in weights.items()}
             xs, ls = x_host[:Tc], logits_host[:Tc]
             t0 = time.perf_counter()

@@ -118,11 +118,13 @@ def test_fp8_block(ops, E, avg, K, N):
     close(D, ref)
 
 
-@pytest.mark.parametrize("tile_n", ["128", "256"])
+@pytest.mark.parametrize("tile_n,pair", [("128", "0"), ("256", "0"), ("256", "1")])
 @pytest.mark.parametrize("kind", ["bf16_kn", "bf16_nk", "fp8"])
-def test_both_tile_widths(ops, tile_n, kind, monkeypatch):
-    """The tile width is normally picked from the problem size; force each one."""
+def test_every_tile_shape(ops, tile_n, pair, kind, monkeypatch):
+    """Tile width and CTA pairing (two CTAs sharing one 256-row MMA) are normally
+    picked from the problem size; force each combination."""
     monkeypatch.setenv("B200MOE_TILE_N", tile_n)
+    monkeypatch.setenv("B200MOE_PAIR", pair)
     E, K, N = 3, 512, 768
     rows = torch.tensor([130, 0, 257], dtype=torch.int32)
     R = 387
@@ -152,10 +154,13 @@ def test_both_tile_widths(ops, tile_n, kind, monkeypatch):
     close(D, ref)
 
 
+@pytest.mark.parametrize("pair", ["0", "1"])
 @pytest.mark.parametrize("E,avg,K,N", [(2, 100, 256, 512), (8, 60, 4096, 2048), (3, 200, 512, 28672 // 8)])
-def test_fp8_fused_silu_quant_epilogue(ops, E, avg, K, N):
-    """GEMM1 of the block-FP8 layer: SiLU*mul and the per-token-group-128
-    re-quantisation happen in the epilogue; output is e4m3 [R, N/2] + f32 scales."""
+def test_fp8_fused_silu_quant_epilogue(ops, E, avg, K, N, pair, monkeypatch):
+    monkeypatch.setenv("B200MOE_PAIR", pair)
+    monkeypatch.setenv("B200MOE_TILE_N", "256")
+    # GEMM1 of the block-FP8 layer: SiLU*mul and the per-token-group-128
+    # re-quantisation happen in the epilogue; output is e4m3 [R, N/2] + f32 scales.
     rows = ragged_rows(E, avg, K + 1)
     R = int(rows.sum())
     g = torch.Generator().manual_seed(N)

@@ -77,11 +77,12 @@ struct Schedule {
   int row_prefix[kMaxExpertsSmem + 1];
   int num_experts;
   int n_tiles;
+  int tile_m;  // rows per scheduled M tile: 128, or 256 for a CTA pair
 };
 
 // Prefix sums of rows and of M tiles per expert, by warp 0 of the CTA.
 __device__ __forceinline__ void build_schedule(Schedule& s, const int32_t* rows_per_expert, int E,
-                                               int64_t R, int n_tiles) {
+                                               int64_t R, int n_tiles, int tile_m) {
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
     int tile_run = 0;
@@ -91,7 +92,7 @@ __device__ __forceinline__ void build_schedule(Schedule& s, const int32_t* rows_
       long long rows = e < E ? rows_per_expert[e] : 0;
       if (rows < 0) rows = 0;
       long long incl_rows = rows;
-      int tiles = static_cast<int>((rows + BM - 1) / BM);
+      int tiles = static_cast<int>((rows + tile_m - 1) / tile_m);
       int incl_tiles = tiles;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -115,6 +116,7 @@ __device__ __forceinline__ void build_schedule(Schedule& s, const int32_t* rows_
       s.tile_prefix[E] = tile_run;
       s.num_experts = E;
       s.n_tiles = n_tiles;
+      s.tile_m = tile_m;
     }
   }
 }
@@ -144,18 +146,20 @@ __device__ __forceinline__ TileCoord decode_tile(const Schedule& s, int t) {
   c.expert = lo;
   const int local = m - s.tile_prefix[lo];
   const int rows_e = s.row_prefix[lo + 1] - s.row_prefix[lo];
-  c.row_start = s.row_prefix[lo] + local * BM;
-  const int left = rows_e - local * BM;
-  c.rows_valid = left < BM ? (left < 0 ? 0 : left) : BM;
+  c.row_start = s.row_prefix[lo] + local * s.tile_m;
+  const int left = rows_e - local * s.tile_m;
+  c.rows_valid = left < s.tile_m ? (left < 0 ? 0 : left) : s.tile_m;
   return c;
 }
 
-__device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
+// Epilogue math uses the hardware exp2/reciprocal units: the results are rounded
+// to bf16 or e4m3 right after, and the reader warps have no issue slots to spare.
+__device__ __forceinline__ float silu_f32(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
 
 __device__ __forceinline__ float swiglu_oai_f32(float g, float u, float alpha, float limit) {
   g = fminf(g, limit);
   u = fmaxf(fminf(u, limit), -limit);
-  return (u + 1.0f) * (g * (1.0f / (1.0f + expf(-g * alpha))));
+  return (u + 1.0f) * (g * __frcp_rn(1.0f + __expf(-g * alpha)));
 }
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int64_t i) {
@@ -199,9 +203,16 @@ __device__ __forceinline__ void store_row16(void* D, int d_dtype, int64_t elem_o
   }
 }
 
-template <int KIND_, bool B_MN_MAJOR_, bool PROMOTE_, int BN_, int EPI_, int STAGES_>
+template <int KIND_, bool B_MN_MAJOR_, bool PROMOTE_, int BN_, int EPI_, int STAGES_,
+          bool PAIR_ = false>
 struct Config {
   static constexpr int KIND = KIND_;
+  // PAIR: two CTAs of a cluster share each MMA (cta_group::2).  The scheduled tile is
+  // 256 x BN; each CTA loads its own 128 rows of A and half of the B columns, so the
+  // bytes a CTA pulls from L2 per flop drop by a third against two independent CTAs.
+  static constexpr bool PAIR = PAIR_;
+  static constexpr int TILE_M = PAIR_ ? 256 : 128;
+  static constexpr int B_COLS = PAIR_ ? BN_ / 2 : BN_;  // B columns this CTA loads
   static constexpr bool B_MN_MAJOR = B_MN_MAJOR_;
   static constexpr bool PROMOTE = PROMOTE_;
   static constexpr int BN = BN_;
@@ -211,10 +222,10 @@ struct Config {
   static constexpr int BK = kStageRowBytes / ELT;       // elements of K per stage
   static constexpr int UMMA_K = 32 / ELT;                // K per MMA instruction
   static constexpr int A_BYTES = BM * kStageRowBytes;
-  static constexpr int B_BYTES = BN * kStageRowBytes;
+  static constexpr int B_BYTES = B_COLS * kStageRowBytes;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int CHUNK_COLS = kStageRowBytes / ELT;  // N columns per MN-major TMA box
-  static constexpr int N_CHUNKS = BN / CHUNK_COLS;
+  static constexpr int N_CHUNKS = B_COLS / CHUNK_COLS;      // boxes this CTA loads per stage
   static constexpr int ACC_BUFS = 512 / BN;              // tensor-memory accumulator ring (all 512 columns)
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_WARPS = 8;                    // two reader warps per TMEM lane quadrant
@@ -226,7 +237,9 @@ struct Config {
   // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
   static constexpr bool REBALANCE_REGS = BN == 256;
   static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES;
-  static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && N_CHUNKS < 2), "a split gated tile needs two weight boxes");
+  static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && !PAIR_ && N_CHUNKS < 2),
+                "a split gated tile needs two weight boxes");
+  static_assert(!PAIR_ || BN_ == 256, "CTA pairs are laid out for 256-column tiles");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed by the tensor-memory allocation");
   static_assert(NCH == 2 || NCH == 4, "reader pipeline alternates two 32-column buffers");
 };
@@ -255,6 +268,24 @@ __device__ __forceinline__ int problem_col(int n_tile, int tcol, int N) {
   if (C::GATED_SPLIT)
     return (tcol < C::BN / 2 ? 0 : N / 2 - C::BN / 2) + n_tile * (C::BN / 2) + tcol;
   return n_tile * C::BN + tcol;
+}
+
+// acc[0..32) += s * t[0..32) with the packed two-wide fp32 FMA of sm_100 (or a
+// plain copy when the tile has a single accumulation phase).
+template <bool PROMOTE>
+__device__ __forceinline__ void accumulate32(float* acc, const float (&t)[32], float s) {
+  if constexpr (PROMOTE) {
+    const float2 s2 = make_float2(s, s);
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float2 r = __ffma2_rn(s2, make_float2(t[j], t[j + 1]), make_float2(acc[j], acc[j + 1]));
+      acc[j] = r.x;
+      acc[j + 1] = r.y;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[j] = t[j];
+  }
 }
 
 // acc[] -> global memory for one row of one tile.
@@ -295,6 +326,7 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
       asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
       amax = fmaxf(amax, xchg[(g ^ 1) * 128 + row]);
       const float s = fmaxf(amax / 448.0f, 1.0f / (448.0f * 512.0f));
+      const float inv_s = 1.0f / s;
       if (row_ok && col0 < half_n) {
         if (g == 0) p.d_scale[grow * (half_n / 128) + tc.n_tile] = s;
         uint8_t* dst = reinterpret_cast<uint8_t*>(p.D) + grow * p.ldd + col0;
@@ -303,7 +335,7 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
           alignas(16) uint8_t q[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            q[i] = f32_to_e4m3(fmaxf(-448.0f, fminf(o[j + i] / s, 448.0f)));
+            q[i] = f32_to_e4m3(fmaxf(-448.0f, fminf(o[j + i] * inv_s, 448.0f)));
           *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(q);
         }
       }
@@ -318,6 +350,36 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
       o[j] = swiglu_oai_f32(acc[2 * j], acc[2 * j + 1], p.alpha, p.limit);
     if (row_ok && col0 < p.N)
       store_row16<CPT / 2>(p.D, p.d_dtype, grow * p.ldd + col0 / 2, o, (p.N - col0) / 2);
+  }
+}
+
+// One pipeline stage of operands for K block `kb` of tile `tc`: this CTA's A box
+// (its 128 rows) and its B box(es).  In a CTA pair, rank 1 takes the second 128 rows
+// and the second half of the tile's columns, and every load reports to the leader's
+// barrier.
+template <typename C>
+__device__ __forceinline__ void issue_stage(const CUtensorMap& map_a, const CUtensorMap& map_b,
+                                            const GemmParams& p, const TileCoord& tc, int kb,
+                                            int rank, uint8_t* stage_smem, uint64_t* bar) {
+  uint8_t* a_dst = stage_smem;
+  uint8_t* b_dst = stage_smem + C::A_BYTES;
+  auto b_box = [&](int off, int x, int y, int z) {
+    if constexpr (C::PAIR) tma_load_3d_pair(b_dst + off, &map_b, bar, x, y, z);
+    else tma_load_3d(b_dst + off, &map_b, bar, x, y, z);
+  };
+  if constexpr (C::PAIR) tma_load_2d_pair(a_dst, &map_a, bar, kb * C::BK, tc.row_start + rank * BM);
+  else tma_load_2d(a_dst, &map_a, bar, kb * C::BK, tc.row_start);
+  const int tcol0 = rank * C::B_COLS;  // first tile column this CTA loads
+  if constexpr (C::B_MN_MAJOR) {
+#pragma unroll
+    for (int c = 0; c < C::N_CHUNKS; ++c)
+      b_box(c * (C::BK * kStageRowBytes),
+            problem_col<C>(tc.n_tile, tcol0 + c * C::CHUNK_COLS, p.N), kb * C::BK, tc.expert);
+  } else if constexpr (C::GATED_SPLIT && !C::PAIR) {
+    b_box(0, kb * C::BK, tc.n_tile * (C::BN / 2), tc.expert);
+    b_box((C::BN / 2) * kStageRowBytes, kb * C::BK, p.N / 2 + tc.n_tile * (C::BN / 2), tc.expert);
+  } else {
+    b_box(0, kb * C::BK, problem_col<C>(tc.n_tile, tcol0, p.N), tc.expert);
   }
 }
 
@@ -348,20 +410,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int b = 0; b < C::ACC_BUFS; ++b) {
       mbar_init(&bars.tfull[b], 1);
-      mbar_init(&bars.tempty[b], C::EPI_WARPS);
+      mbar_init(&bars.tempty[b], C::EPI_WARPS * (C::PAIR ? 2 : 1));  // both CTAs' readers
     }
     mbar_fence_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
   }
-  build_schedule(sched, p.rows_per_expert, p.E, p.R, n_tiles);
+  build_schedule(sched, p.rows_per_expert, p.E, p.R, n_tiles, C::TILE_M);
   if (warp == 1) {
-    tmem_alloc(&tmem_base_slot, C::TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (C::PAIR) {
+      tmem_alloc_pair(&tmem_base_slot, C::TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&tmem_base_slot, C::TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if constexpr (C::PAIR) cluster_sync();  // the peer's barriers exist before anything signals them
   tc_fence_after();
+  const int rank = C::PAIR ? static_cast<int>(cluster_ctarank()) : 0;
+  const int sched_id = C::PAIR ? blockIdx.x / 2 : blockIdx.x;      // position in the tile sequence
+  const int sched_stride = C::PAIR ? gridDim.x / 2 : gridDim.x;
   const uint32_t tmem_base = tmem_base_slot;
   const int num_tiles = total_tiles(sched);
   volatile int* abort_p = &abort_flag;
@@ -373,39 +444,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
         const TileCoord tc = decode_tile(sched, t);
         for (int kb = 0; kb < num_kb && ok; ++kb) {
           ok = mbar_wait(&bars.empty[stage], phase ^ 1u, abort_p);
           if (!ok) break;
-          uint8_t* a_dst = tiles + stage * C::STAGE_BYTES;
-          uint8_t* b_dst = a_dst + C::A_BYTES;
-          mbar_arrive_expect_tx(&bars.full[stage], C::STAGE_BYTES);
-          tma_load_2d(a_dst, &map_a, &bars.full[stage], kb * C::BK, tc.row_start);
-          if constexpr (C::B_MN_MAJOR) {
-#pragma unroll
-            for (int c = 0; c < C::N_CHUNKS; ++c) {
-              const int col = problem_col<C>(tc.n_tile, c * C::CHUNK_COLS, p.N);
-              tma_load_3d(b_dst + c * (C::BK * kStageRowBytes), &map_b, &bars.full[stage], col,
-                          kb * C::BK, tc.expert);
-            }
-          } else {
-            if constexpr (C::GATED_SPLIT) {
-              tma_load_3d(b_dst, &map_b, &bars.full[stage], kb * C::BK, tc.n_tile * (C::BN / 2),
-                          tc.expert);
-              tma_load_3d(b_dst + (C::BN / 2) * kStageRowBytes, &map_b, &bars.full[stage],
-                          kb * C::BK, p.N / 2 + tc.n_tile * (C::BN / 2), tc.expert);
-            } else {
-              tma_load_3d(b_dst, &map_b, &bars.full[stage], kb * C::BK, tc.n_tile * C::BN,
-                          tc.expert);
-            }
-          }
+          // the leader's barrier counts the bytes of both CTAs of a pair
+          if (rank == 0)
+            mbar_arrive_expect_tx(&bars.full[stage], C::STAGE_BYTES * (C::PAIR ? 2 : 1));
+          issue_stage<C>(map_a, map_b, p, tc, kb, rank, tiles + stage * C::STAGE_BYTES,
+                         &bars.full[stage]);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-    } else if (warp == 1 && lane == 0) {
-      // ---------------- MMA issuer ----------------
-      const uint32_t idesc = make_idesc(p.ab_fmt, p.ab_fmt, 0u, C::B_MN_MAJOR ? 1u : 0u, BM, C::BN);
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+      // ---------------- MMA issuer (the even CTA of a pair) ----------------
+      const uint32_t idesc =
+          make_idesc(p.ab_fmt, p.ab_fmt, 0u, C::B_MN_MAJOR ? 1u : 0u, C::TILE_M, C::BN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -413,7 +468,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       bool ok = true;
       const int phases_per_tile = C::PROMOTE ? num_kb : 1;
       const int kb_per_phase = C::PROMOTE ? 1 : num_kb;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
         for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
           ok = mbar_wait(&bars.tempty[buf], buf_phase ^ 1u, abort_p);
           if (!ok) break;
@@ -434,13 +489,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
                                          C::BK * kStageRowBytes, 1024)
                       : make_sdesc_sw128(b_addr + kk * 32, 16, 1024);
               const uint32_t accum = (kb > 0 || kk > 0) ? 1u : 0u;
-              if (C::KIND == KIND_F16) mma_f16(d_tmem, a_desc, b_desc, idesc, accum);
-              else mma_f8(d_tmem, a_desc, b_desc, idesc, accum);
+              if constexpr (C::PAIR) {
+                if (C::KIND == KIND_F16) mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accum);
+                else mma_f8_pair(d_tmem, a_desc, b_desc, idesc, accum);
+              } else {
+                if (C::KIND == KIND_F16) mma_f16(d_tmem, a_desc, b_desc, idesc, accum);
+                else mma_f8(d_tmem, a_desc, b_desc, idesc, accum);
+              }
             }
-            mma_commit(&bars.empty[stage]);
+            if constexpr (C::PAIR) mma_commit_pair(&bars.empty[stage]);
+            else mma_commit(&bars.empty[stage]);
             if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
           }
-          if (ok) mma_commit(&bars.tfull[buf]);
+          if (ok) {
+            if constexpr (C::PAIR) mma_commit_pair(&bars.tfull[buf]);
+            else mma_commit(&bars.tfull[buf]);
+          }
           if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
         }
       }
@@ -461,10 +525,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     uint32_t buf_phase = 0;
     bool ok = true;
     int tile_parity = 0;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, tile_parity ^= 1) {
+    for (int t = sched_id; t < num_tiles && ok; t += sched_stride, tile_parity ^= 1) {
       const TileCoord tc = decode_tile(sched, t);
-      const bool row_ok = row_in_tile < tc.rows_valid;
-      const int64_t grow = static_cast<int64_t>(tc.row_start) + row_in_tile;
+      const bool row_ok = rank * BM + row_in_tile < tc.rows_valid;
+      const int64_t grow = static_cast<int64_t>(tc.row_start) + rank * BM + row_in_tile;
       float acc[CPT];
       float ta[32], tb[32];
       // weight-scale blocks of the first / second half of this thread's columns
@@ -485,12 +549,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         sb0_n = sb_ptr[nb0];
         sb1_n = sb_ptr[nb1];
       }
-      // first load of the tile
+      // first two loads of the tile
       ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
       if (!ok) break;
       tc_fence_after();
       tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 0), ta);
+      tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 1), tb);
 
+      // Two 32-column loads are kept in flight: both are waited for together, then
+      // each buffer is consumed and immediately refilled with the chunk after next.
       for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
         float s0 = 1.f, s1 = 1.f;
         if constexpr (C::PROMOTE) {
@@ -502,35 +569,39 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
             sb1_n = sb_ptr[(ph + 1) * nb_count + nb1];
           }
         }
+        int cur_buf = buf;
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
-          float(&cur)[32] = (c & 1) ? tb : ta;
-          float(&nxt)[32] = (c & 1) ? ta : tb;
-          tmem_ld_wait_on(cur);
-          if (c + 1 < NCH) {
-            tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, c + 1), nxt);
-          } else {
-            // every column of this buffer is in registers: hand it back, start on the next
+        for (int q = 0; q < NCH / 2; ++q) {
+          tmem_ld_wait();
+          const bool last_pair = q + 1 == NCH / 2;
+          bool more = true;
+          if (last_pair) {
+            // every column of this buffer is in registers: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars.tempty[buf]);
+            if (lane == 0) {
+              if constexpr (C::PAIR) mbar_arrive_cluster(&bars.tempty[buf], 0);
+              else mbar_arrive(&bars.tempty[buf]);
+            }
             if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
-            if (ph + 1 < phases_per_tile) {
+            more = ph + 1 < phases_per_tile;
+            if (more) {
               ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
-              if (ok) {
-                tc_fence_after();
-                tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 0), nxt);
-              }
+              more = ok;
+              if (ok) tc_fence_after();
+              cur_buf = buf;
             }
           }
-          if constexpr (C::PROMOTE) {
-            const float s = c < NCH / 2 ? s0 : s1;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(s, cur[j], acc[c * 32 + j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c * 32 + j] = cur[j];
-          }
+          const int c0 = 2 * q, c1 = 2 * q + 1;
+          const int n0 = last_pair ? 0 : c0 + 2, n1 = last_pair ? 1 : c1 + 2;
+          const float sc0 = c0 < NCH / 2 ? s0 : s1;
+          const float sc1 = c1 < NCH / 2 ? s0 : s1;
+          accumulate32<C::PROMOTE>(acc + c0 * 32, ta, sc0);
+          if (more)
+            tmem_ld_32x32(tmem_base + lane_addr + cur_buf * C::BN + chunk_tmem_col<C>(g, n0), ta);
+          accumulate32<C::PROMOTE>(acc + c1 * 32, tb, sc1);
+          if (more)
+            tmem_ld_32x32(tmem_base + lane_addr + cur_buf * C::BN + chunk_tmem_col<C>(g, n1), tb);
         }
       }
       if (!ok) break;
@@ -547,9 +618,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
     __syncthreads();
   }
+  if constexpr (C::PAIR) cluster_sync();  // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if constexpr (C::PAIR) tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+    else tmem_dealloc(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -612,7 +685,8 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   if (C::B_MN_MAJOR)
     rc = make_map(&map_b, b_dtype, B, a.N, a.K, a.E, C::CHUNK_COLS, C::BK);
   else
-    rc = make_map(&map_b, b_dtype, B, a.K, a.N, a.E, C::BK, C::GATED_SPLIT ? C::BN / 2 : C::BN);
+    rc = make_map(&map_b, b_dtype, B, a.K, a.N, a.E, C::BK,
+                  (C::GATED_SPLIT || C::PAIR) ? C::BN / 2 : C::BN);
   if (rc != B200MOE_OK) return rc;
 
   GemmParams p;
@@ -646,10 +720,31 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   }
   const int n_tiles = C::GATED_SPLIT ? (a.N / 2 + C::BN / 2 - 1) / (C::BN / 2)
                                      : (a.N + C::BN - 1) / C::BN;
-  const int64_t max_m_tiles = (a.R + BM - 1) / BM + a.E;
-  int64_t grid = max_m_tiles * n_tiles;
+  const int64_t max_m_tiles = (a.R + C::TILE_M - 1) / C::TILE_M + a.E;
+  int64_t grid = max_m_tiles * n_tiles * (C::PAIR ? 2 : 1);
   if (grid > kNumSMs) grid = kNumSMs;
   if (grid < 1) grid = 1;
+  if (C::PAIR) {
+    grid = grid < 2 ? 2 : grid & ~1ll;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<C>, map_a, map_b, p);
+    if (e != cudaSuccess) {
+      set_last_error("grouped_gemm_kernel (cluster launch)", e);
+      return B200MOE_CUDA_ERROR;
+    }
+    return launch_status("grouped_gemm_kernel");
+  }
   grouped_gemm_kernel<C><<<static_cast<int>(grid), C::THREADS, C::SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_kernel");
 }
@@ -797,17 +892,17 @@ extern "C" int b200moe_dequant_weights(int recipe, const void* B, const void* b_
   return launch_status("dequant_weights");
 }
 
-template <int KIND, bool MN, bool PROMOTE, int BN, int STAGES>
+template <int KIND, bool MN, bool PROMOTE, int BN, int STAGES, bool PAIR = false>
 static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaStream_t st) {
   switch (a.epilogue) {
     case B200MOE_EPI_STORE:
-      return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, STAGES>>(a, B, b_dtype, st);
+      return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, STAGES, PAIR>>(a, B, b_dtype, st);
     case B200MOE_EPI_SILU_MUL:
       // an MN-major split tile needs one weight box for the gate half and one for the up half
-      if constexpr (MN && BN * (KIND == KIND_F16 ? 2 : 1) < 256) return B200MOE_UNSUPPORTED;
-      else return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SILU_MUL, STAGES>>(a, B, b_dtype, st);
+      if constexpr (MN && !PAIR && BN * (KIND == KIND_F16 ? 2 : 1) < 256) return B200MOE_UNSUPPORTED;
+      else return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SILU_MUL, STAGES, PAIR>>(a, B, b_dtype, st);
     case B200MOE_EPI_SWIGLU_OAI:
-      return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SWIGLU_OAI, STAGES>>(a, B, b_dtype, st);
+      return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SWIGLU_OAI, STAGES, PAIR>>(a, B, b_dtype, st);
     default:
       return B200MOE_INVALID_ARG;
   }
@@ -815,6 +910,16 @@ static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cu
 
 // 128x256 tiles halve the shared-memory and L2 traffic per flop; 128x128 tiles
 // give more CTAs something to do when the problem is small.
+static bool want_pair(const b200moe_gemm_args& a, bool wide) {
+  const char* force = getenv("B200MOE_PAIR");
+  if (force) return atoi(force) != 0 && wide;
+  // CTA pairs schedule 256-row tiles: worth it once the experts are that tall on average.
+  // Measured on the Mixtral shapes: +3 % for 16-bit operands; nothing for the FP8 recipe,
+  // whose per-K-block accumulator hand-off gets slower across two CTAs.
+  const bool promote = a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3;
+  return wide && !promote && a.R / a.E >= 256;
+}
+
 static bool want_wide_tile(const b200moe_gemm_args& a) {
   const char* force = getenv("B200MOE_TILE_N");
   if (force) return atoi(force) == 256;
@@ -835,14 +940,14 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   if (quant_out && (a.epilogue != B200MOE_EPI_SILU_MUL || !a.d_scale || (a.N / 2) % 128 != 0))
     return B200MOE_UNSUPPORTED;
   const bool wide = want_wide_tile(a);
+  const bool pair = want_pair(a, wide);
 
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3) {
     if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
-    if (a.epilogue == B200MOE_EPI_SILU_MUL) {
-      if ((a.N / 2) % 128 != 0) return B200MOE_UNSUPPORTED;
+    if (a.epilogue == B200MOE_EPI_SILU_MUL && (a.N / 2) % 128 != 0) return B200MOE_UNSUPPORTED;
+    if (pair) return launch_epi<KIND_F8, true, true, 256, 6, true>(a, a.B, B200MOE_E4M3, st);
+    if (wide || a.epilogue == B200MOE_EPI_SILU_MUL)
       return launch_epi<KIND_F8, true, true, 256, 4>(a, a.B, B200MOE_E4M3, st);
-    }
-    if (wide) return launch_epi<KIND_F8, true, true, 256, 4>(a, a.B, B200MOE_E4M3, st);
     return launch_epi<KIND_F8, true, true, 128, 6>(a, a.B, B200MOE_E4M3, st);
   }
   if (quant_out) return B200MOE_UNSUPPORTED;
@@ -863,9 +968,11 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   }
   if (a.K % 8 != 0) return B200MOE_INVALID_ARG;
   if (b_nk) {
+    if (pair) return launch_epi<KIND_F16, false, false, 256, 6, true>(a, B, a.a_dtype, st);
     if (wide) return launch_epi<KIND_F16, false, false, 256, 4>(a, B, a.a_dtype, st);
     return launch_epi<KIND_F16, false, false, 128, 6>(a, B, a.a_dtype, st);
   }
+  if (pair) return launch_epi<KIND_F16, true, false, 256, 6, true>(a, B, a.a_dtype, st);
   if (wide) return launch_epi<KIND_F16, true, false, 256, 4>(a, B, a.a_dtype, st);
   return launch_epi<KIND_F16, true, false, 128, 6>(a, B, a.a_dtype, st);
 }
