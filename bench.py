@@ -33,7 +33,7 @@ import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one w13 GEMM launch, from the ncu capture
 # summarised under profiles/ (captured on a 2-expert slice, scaled by the expert count).
-TRAFFIC_BYTES_PER_LAUNCH = {}
+TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 267.66e6}  # profiles/grouped_gemm_fp8_c1_small.md
 
 # The benchmark configurations (shapes of BASELINE.json's configs 0-3).
 CONFIGS = {
@@ -371,6 +371,10 @@ def main():
         layer.moe.stage_timer = None
     gemm1 = [s.elapsed_time(e) for name, s, e in gemm_ms if name == "gemm1"]
     gemm1_ms = sum(gemm1) / max(len(gemm1), 1)
+    stages = {}
+    for name, s, e in gemm_ms:
+        stages.setdefault(name, []).append(s.elapsed_time(e))
+    stages = {k: round(sum(v) / len(v), 4) for k, v in stages.items()}
 
     t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
     if world > 1:
@@ -408,6 +412,7 @@ def main():
                          if fp8 else f"{peaks['source']} sustained bf16 cuBLAS rate",
                          "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms},
             "clocks": clk.summary(),
+            "stages_ms": stages,
         }
         if not args.no_cpu_baseline and world == 1:
             from oracle import moe_oracle as O  # CPU-baseline leg only

@@ -917,7 +917,7 @@ static bool want_pair(const b200moe_gemm_args& a, bool wide) {
   // Measured on the Mixtral shapes: +3 % for 16-bit operands; nothing for the FP8 recipe,
   // whose per-K-block accumulator hand-off gets slower across two CTAs.
   const bool promote = a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3;
-  return wide && !promote && a.R / a.E >= 256;
+  return wide && !promote && a.R / a.E >= 1024;
 }
 
 static bool want_wide_tile(const b200moe_gemm_args& a) {

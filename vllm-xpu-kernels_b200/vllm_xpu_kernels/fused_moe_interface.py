@@ -25,6 +25,7 @@ Recipes, detected from the weight dtypes as the reference does
   W4A16 arithmetic of the reference kernel.
 """
 import contextlib
+import os
 from typing import Optional
 
 import torch
@@ -203,7 +204,7 @@ class XpuFusedMoe:
         gemm = torch.ops._xpu_C.b200_grouped_gemm
         if self.is_block_fp8:
             clamp = self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0
-            if not oai and not clamp and I % 128 == 0:
+            if not oai and not clamp and I % 128 == 0 and not os.environ.get("B200MOE_UNFUSED_ACT"):
                 # SiLU*mul and the group-128 re-quantisation run in the GEMM's epilogue
                 act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
                 act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
