@@ -152,14 +152,24 @@ __device__ __forceinline__ TileCoord decode_tile(const Schedule& s, int t) {
   return c;
 }
 
-// Epilogue math uses the hardware exp2/reciprocal units: the results are rounded
-// to bf16 or e4m3 right after, and the reader warps have no issue slots to spare.
-__device__ __forceinline__ float silu_f32(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
+// Epilogue math uses the special-function unit directly (ex2.approx, rcp.approx: two
+// MUFU operations per sigmoid, relative error ~1e-6).  The correctly rounded
+// reciprocal and expf are instruction sequences an order of magnitude longer, and
+// the reader warps run the epilogue while the MMA warp waits for them; the results
+// are rounded to bf16 or e4m3 right after.
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-1.4426950408889634f * x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return r;
+}
+
+__device__ __forceinline__ float silu_f32(float g) { return g * fast_sigmoid(g); }
 
 __device__ __forceinline__ float swiglu_oai_f32(float g, float u, float alpha, float limit) {
   g = fminf(g, limit);
   u = fmaxf(fminf(u, limit), -limit);
-  return (u + 1.0f) * (g * __frcp_rn(1.0f + __expf(-g * alpha)));
+  return (u + 1.0f) * (g * fast_sigmoid(g * alpha));
 }
 
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int64_t i) {
@@ -323,20 +333,28 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
       for (int j = 0; j < HALF; ++j) amax = fmaxf(amax, fabsf(o[j]));
       const int row = threadIdx.x & 127;  // quad*32 + lane for reader warps 4..11
       xchg[g * 128 + row] = amax;
-      asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+      // the two warps that hold the same 32 rows (column groups 0 and 1) meet on their own barrier
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");
       amax = fmaxf(amax, xchg[(g ^ 1) * 128 + row]);
-      const float s = fmaxf(amax / 448.0f, 1.0f / (448.0f * 512.0f));
+      const float s = fmaxf(amax * (1.0f / 448.0f), 1.0f / (448.0f * 512.0f));
       const float inv_s = 1.0f / s;
       if (row_ok && col0 < half_n) {
         if (g == 0) p.d_scale[grow * (half_n / 128) + tc.n_tile] = s;
         uint8_t* dst = reinterpret_cast<uint8_t*>(p.D) + grow * p.ldd + col0;
 #pragma unroll
         for (int j = 0; j < HALF; j += 16) {
-          alignas(16) uint8_t q[16];
+          uint32_t w[4];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            q[i] = f32_to_e4m3(fmaxf(-448.0f, fminf(o[j + i] * inv_s, 448.0f)));
-          *reinterpret_cast<uint4*>(dst + j) = *reinterpret_cast<const uint4*>(q);
+          for (int i = 0; i < 4; ++i) {
+            const float v0 = fmaxf(-448.0f, fminf(o[j + 4 * i + 0] * inv_s, 448.0f));
+            const float v1 = fmaxf(-448.0f, fminf(o[j + 4 * i + 1] * inv_s, 448.0f));
+            const float v2 = fmaxf(-448.0f, fminf(o[j + 4 * i + 2] * inv_s, 448.0f));
+            const float v3 = fmaxf(-448.0f, fminf(o[j + 4 * i + 3] * inv_s, 448.0f));
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v0, v1), __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v2, v3), __NV_SATFINITE, __NV_E4M3);
+            w[i] = lo | (hi << 16);
+          }
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     } else if (row_ok && col0 < half_n) {
