@@ -426,6 +426,15 @@ def main():
         achieved = gemm1_flops / (gemm1_ms * 1e-3) / 1e12 if gemm1_ms > 0 else 0.0
         fp8 = cfg["recipe"] == "fp8block"
         peak = (2.0 if fp8 else 1.0) * peaks["bf16_tflops_sustained"]
+        # distinct experts this batch touches: in the decode regime the layer streams their weights
+        # once and the w13 GEMM is bound by HBM, not by the tensor pipe
+        _, ids_now = layer.route(logits)
+        active = int(torch.unique(ids_now).numel())
+        wbytes = {"fp8block": 1.0, "bf16": 2.0, "mxfp4": 2.0}[cfg["recipe"]]
+        gemm1_bytes = (active * cfg["H"] * 2 * cfg["I"] * wbytes
+                       + (active * (cfg["H"] // 128) * (2 * cfg["I"] // 128) * 4 if fp8 else 0)
+                       + R * cfg["H"] * (1 if fp8 else 2) + R * cfg["I"] * (1 if fp8 else 2))
+        decode = R / max(active, 1) < 64
         line = {
             "metric": "fused_moe_layer_tokens_per_s", "value": world * T / (ms * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -450,8 +459,15 @@ def main():
                          if fp8 else f"{peaks['source']} sustained bf16 cuBLAS rate",
                          "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms},
             "clocks": clk.summary(),
-            "stages_ms": stages,
+            "stages_ms": stages, "active_experts": active,
         }
+        if decode and gemm1_ms > 0:
+            gbs = gemm1_bytes / (gemm1_ms * 1e-3) / 1e9
+            line["roofline"] = {"bound": "hbm", "kernel": "grouped_gemm_kernel (w13), weight streaming",
+                                "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                                "peak_source": f"{peaks['source']} copy bandwidth",
+                                "bytes_per_launch": gemm1_bytes, "ms_per_launch": gemm1_ms}
         if not args.no_cpu_baseline and world == 1:
             from oracle import moe_oracle as O  # CPU-baseline leg only
             cores = os.cpu_count() or 1
