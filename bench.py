@@ -189,9 +189,17 @@ class Layer:
         self.moe = XpuFusedMoe(w13, weights["w13_scale"], weights["w13_bias"], w2, weights["w2_scale"],
                                weights["w2_bias"], cfg["k"], cfg["activation"], E_loc)
         self.ep = None
+        self.ep_backend = None
         if group is not None:
-            from vllm_xpu_kernels.ep import ExpertParallel, make_local_fn
-            self.ep = ExpertParallel(group, E_loc, make_local_fn(self.moe))
+            from vllm_xpu_kernels.ep import ExpertParallel, PeerExpertParallel, make_local_fn
+            self.ep_backend = os.environ.get("B200MOE_EP", "peer")
+            if self.ep_backend == "peer":
+                fp8 = cfg["recipe"] == "fp8block"
+                self.ep = PeerExpertParallel(group, self.moe, T, cfg["k"], cfg["H"],
+                                             cfg["H"] * (1 if fp8 else 2),
+                                             (cfg["H"] // 128) * 4 if fp8 else 0, E_loc, dev)
+            else:
+                self.ep = ExpertParallel(group, E_loc, make_local_fn(self.moe))
         k = cfg["k"]
         self.w = torch.empty(T, k, dtype=torch.float32, device=dev)
         self.ids = torch.empty(T, k, dtype=torch.int32, device=dev)
@@ -278,8 +286,11 @@ def run_reference(args, cfg):
 
 def workload_config(args, cfg):
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    how = ("NCCL all-to-all dispatch/combine" if os.environ.get("B200MOE_EP", "peer") == "nccl" else
+           "dispatch and combine as stores into peer GPU memory from the library's own kernels "
+           "(second GEMM's epilogue writes the combine)")
     par = "1 GPU" if world == 1 else (f"expert-parallel over {world} GPUs ({cfg['E'] // world} experts each), "
-                                      "tokens data-parallel, NCCL all-to-all dispatch/combine")
+                                      f"tokens data-parallel, {how}")
     return {"workload": f"{args.config}: {cfg['name']}", "parallelism": par, "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
             "experts": cfg["E"], "topk": cfg["k"],
             "l2": "value: 256 MiB buffer written between timed steps; e2e: no flush, each step streams "

@@ -222,6 +222,11 @@ typedef struct b200moe_gemm_args {
   int64_t R;         /* rows of A (upper bound on sum(rows_per_expert))         */
   int N, K, E;
   float alpha, limit; /* SWIGLU_OAI parameters                                  */
+  const int64_t* d_row_ptr; /* optional, EPI_STORE only: device table with one
+                        address per row of A; row r of the result is stored at
+                        that address (N elements) instead of D + r*N.  The
+                        addresses may be peer-mapped memory of other GPUs: this
+                        is how the expert-parallel combine leaves the GEMM.      */
 } b200moe_gemm_args;
 
 /* cutlass_grouped_gemm_interface (csrc/xpu/torch_bindings.cpp:58-67,
@@ -246,6 +251,48 @@ int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* stream);
 /* Reads (and clears) the sticky device status word that bounded waits inside
  * the tensor-core kernels set when they give up; 0 = none.  Synchronises. */
 int b200moe_device_status(void* stream, int* status_host);
+
+/* ---- expert-parallel exchange over peer-mapped memory -------------------------
+ * vllm-xpu-kernels has no exchange step (its expert-parallel mode masks
+ * non-local experts, csrc/moe/init_expert_map.cpp:45-52, and leaves the
+ * all-to-all to vLLM); these four entry points are that step for GPUs of one
+ * NVLink/NVSwitch domain.  `peer_bases_host` is a HOST array of `world` device
+ * addresses: the base of every rank's symmetric allocation, mapped into this
+ * process.  Offsets are byte offsets inside that allocation, the same on every
+ * rank.  All four only enqueue kernels that write; the device-wide barriers
+ * between them are the caller's. */
+
+/* Writes my per-destination row counts into row `my_rank` of every rank's i32
+ * [world, world] matrix at `counts_offset`. */
+int b200moe_ep_put_counts(const int32_t* send_counts, const int64_t* peer_bases_host,
+                          int64_t counts_offset, int my_rank, int world, void* stream);
+
+/* From the complete matrix (local copy): send_base i32 [world+1] (prefix of my
+ * row), dst_base i32 [world] (my first row inside each destination's receive
+ * buffer), recv_base i32 [world+1] (first row of each source in mine).  Rows
+ * [recv_base[world], capacity) of recv_expert are set to -1. */
+int b200moe_ep_offsets(const int32_t* counts, int my_rank, int world, int32_t* send_base,
+                       int32_t* dst_base, int32_t* recv_base, int32_t* recv_expert,
+                       int64_t capacity, void* stream);
+
+/* Stores my send rows (grouped by destination, as remap_hidden_states with an
+ * expert->rank map leaves them), their scale rows and local expert ids into the
+ * destinations' receive buffers. */
+int b200moe_ep_push(const void* send_rows, const void* send_scales,
+                    const int32_t* send_expert, int64_t num_rows, int64_t row_bytes,
+                    int64_t scale_row_bytes, int world, const int32_t* send_base,
+                    const int32_t* dst_base, const int64_t* peer_bases_host,
+                    int64_t rows_offset, int64_t scales_offset, int64_t expert_offset,
+                    int64_t capacity, void* stream);
+
+/* dst_addr[row_map[j]] = address, in the return buffer of the rank that sent
+ * received row j, of the slot that row came from; feed it to
+ * b200moe_gemm_args.d_row_ptr of the second grouped GEMM. */
+int b200moe_ep_return_table(const int32_t* row_map, const int32_t* recv_base,
+                            const int32_t* counts, int my_rank, int world,
+                            const int64_t* peer_bases_host, int64_t return_offset,
+                            int64_t row_bytes, int64_t capacity, int64_t* dst_addr,
+                            void* stream);
 
 #ifdef __cplusplus
 }

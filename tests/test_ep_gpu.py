@@ -13,7 +13,7 @@ from oracle import moe_oracle as O
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, recipe, result):
+def _worker(rank, world, port, recipe, backend, result):
     for p in (ROOT, PKG_DIR):
         if p not in sys.path:
             sys.path.insert(0, p)
@@ -24,6 +24,7 @@ def _worker(rank, world, port, recipe, result):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     import vllm_xpu_kernels._C  # noqa: F401
     import vllm_xpu_kernels._moe_C  # noqa: F401
+    import vllm_xpu_kernels._xpu_C  # noqa: F401
     from vllm_xpu_kernels.ep import ExpertParallel, make_local_fn
     from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
     from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
@@ -34,30 +35,44 @@ def _worker(rank, world, port, recipe, result):
     d = lambda t: None if t is None else t[sl].to(dev)  # noqa: E731
     moe = XpuFusedMoe(d(layer["w13"]), d(layer["w13_scale"]), None, d(layer["w2"]), d(layer["w2_scale"]),
                       None, cfg["k"], "silu", per)
-    ep = ExpertParallel(dist.group.WORLD, per, make_local_fn(moe))
-    tok = O.make_layer(dict(cfg, E=cfg["E"]), seed=50 + rank, E_limit=1)
-    x, logits = tok["x"], tok["logits"]
-    w, ids = O.topk_softmax(logits, cfg["k"], True)
-    out = torch.empty(cfg["T"], cfg["H"], dtype=torch.bfloat16, device=dev)
-    xd, scales = x.to(dev), None
-    if recipe == "fp8block":
-        xd, scales = quant_fp8_block_act(xd)
-    ep.apply(out, xd, w.to(dev), ids.to(dev), scales=scales)
-    torch.cuda.synchronize()
-    ref = O.fused_moe(recipe, x, layer["w13"], layer["w13_scale"], None, layer["w2"], layer["w2_scale"],
-                      None, w, ids, "silu", out_dtype=torch.float32)
-    err = (out.float().cpu() - ref).abs()
-    tol = 2e-2 if recipe == "bf16" else 5e-2
-    result[rank] = bool((err <= tol + tol * ref.abs()).all())
+    if backend == "peer":
+        from vllm_xpu_kernels.ep import PeerExpertParallel
+        fp8 = recipe == "fp8block"
+        ep = PeerExpertParallel(dist.group.WORLD, moe, cfg["T"], cfg["k"], cfg["H"],
+                                cfg["H"] * (1 if fp8 else 2), (cfg["H"] // 128) * 4 if fp8 else 0, per, dev)
+    else:
+        ep = ExpertParallel(dist.group.WORLD, per, make_local_fn(moe))
+    ok = True
+    for call in range(2):   # twice: the exchange buffers are reused from call to call
+        tok = O.make_layer(dict(cfg, E=cfg["E"]), seed=50 + rank + 10 * call, E_limit=1)
+        x, logits = tok["x"], tok["logits"]
+        w, ids = O.topk_softmax(logits, cfg["k"], True)
+        out = torch.empty(cfg["T"], cfg["H"], dtype=torch.bfloat16, device=dev)
+        xd, scales = x.to(dev), None
+        if recipe == "fp8block":
+            xd, scales = quant_fp8_block_act(xd)
+        ep.apply(out, xd, w.to(dev), ids.to(dev), scales=scales)
+        torch.cuda.synchronize()
+        ref = O.fused_moe(recipe, x, layer["w13"], layer["w13_scale"], None, layer["w2"], layer["w2_scale"],
+                          None, w, ids, "silu", out_dtype=torch.float32)
+        err = (out.float().cpu() - ref).abs()
+        tol = 2e-2 if recipe == "bf16" else 5e-2
+        ok = ok and bool((err <= tol + tol * ref.abs()).all())
+    ok = ok and torch.ops._xpu_C.b200_device_status() == 0
+    result[rank] = ok
     dist.barrier()
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("backend", ["nccl", "peer"])
 @pytest.mark.parametrize("recipe", ["bf16", "fp8block"])
-def test_expert_parallel_two_gpus(recipe):
+def test_expert_parallel_two_gpus(recipe, backend):
+    """backend 'nccl': all-to-all-v through torch.distributed; 'peer': this library's kernels
+    storing into the other GPU's memory, the second GEMM's epilogue included."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    port = 29621 + 2 * (recipe != "bf16") + (backend == "peer")
     with mp.Manager() as m:
         result = m.dict()
-        mp.spawn(_worker, args=(2, 29621 + (recipe != "bf16"), recipe, result), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, port, recipe, backend, result), nprocs=2, join=True)
         assert result[0] and result[1]

@@ -62,6 +62,7 @@ struct GemmParams {
   int N, K, E;
   int ldd;     // row stride of D in elements
   int ab_fmt;  // operand format code of the instruction descriptor
+  const int64_t* d_row_ptr;  // optional per-row destination addresses (store epilogue)
   float alpha, limit;
 };
 
@@ -317,7 +318,12 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
   }
   if constexpr (C::EPI == B200MOE_EPI_STORE) {
     const int col0 = tc.n_tile * C::BN + g * CPT;
-    if (row_ok && col0 < p.N) store_row16<CPT>(p.D, p.d_dtype, grow * p.ldd + col0, acc, p.N - col0);
+    if (row_ok && col0 < p.N) {
+      if (p.d_row_ptr)  // the row's home may be another GPU's memory
+        store_row16<CPT>(reinterpret_cast<void*>(p.d_row_ptr[grow]), p.d_dtype, col0, acc, p.N - col0);
+      else
+        store_row16<CPT>(p.D, p.d_dtype, grow * p.ldd + col0, acc, p.N - col0);
+    }
   } else if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
     constexpr int HALF = CPT / 2;
     const int half_n = p.N / 2;
@@ -723,6 +729,7 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   p.ldd = a.epilogue == B200MOE_EPI_STORE ? a.N : a.N / 2;  // elements (bytes for e4m3)
   p.alpha = a.alpha;
   p.limit = a.limit;
+  p.d_row_ptr = a.epilogue == B200MOE_EPI_STORE ? a.d_row_ptr : nullptr;
   p.ab_fmt = a.a_dtype == B200MOE_BF16 ? 1 : 0;  // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
 
   static bool attr_set = false;  // per template instantiation
@@ -875,7 +882,7 @@ static int validate(const b200moe_gemm_args* a) {
   if (a->R < 0 || a->N <= 0 || a->K <= 0 || a->E <= 0 || a->E > kMaxExpertsSmem) return B200MOE_INVALID_ARG;
   if (a->N % 8 != 0) return B200MOE_INVALID_ARG;
   if (a->R == 0) return B200MOE_OK;
-  if (!a->A || !a->B || !a->D || !a->rows_per_expert) return B200MOE_INVALID_ARG;
+  if (!a->A || !a->B || (!a->D && !a->d_row_ptr) || !a->rows_per_expert) return B200MOE_INVALID_ARG;
   if (a->R >= (1ll << 31)) return B200MOE_UNSUPPORTED;
   return B200MOE_OK;
 }

@@ -398,7 +398,8 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const OptTensor& B_scale, const OptTensor& bias, Tensor D,
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
-                         const OptTensor& D_scale = std::nullopt) {
+                         const OptTensor& D_scale = std::nullopt,
+                         const OptTensor& D_row_ptr = std::nullopt) {
   const char* op = "cutlass_grouped_gemm_interface";
   TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && D.is_contiguous(), op, ": A, B and D must be contiguous");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
@@ -417,6 +418,12 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
     TORCH_CHECK(D_scale->scalar_type() == at::kFloat && D_scale->is_contiguous(), op,
                 ": output scales must be contiguous float32");
     a.d_scale = D_scale->data_ptr<float>();
+  }
+  if (D_row_ptr.has_value()) {
+    TORCH_CHECK(D_row_ptr->scalar_type() == at::kLong && D_row_ptr->is_contiguous() &&
+                    D_row_ptr->numel() >= A.numel() / K,
+                op, ": the row address table must be int64 with one entry per row of A");
+    a.d_row_ptr = D_row_ptr->data_ptr<int64_t>();
   }
   a.rows_per_expert = rows_per_expert.data_ptr<int>();
   a.R = A.numel() / K;
@@ -474,9 +481,9 @@ Tensor b200_grouped_gemm(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const OptTensor& B_scale, const OptTensor& bias, Tensor D,
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
-                         const OptTensor& D_scale) {
+                         const OptTensor& D_scale, const OptTensor& D_row_ptr) {
   return grouped_gemm_impl(A, A_scale, B, B_scale, bias, D, rows_per_expert, N, K, num_experts,
-                           epilogue, b_layout, alpha, limit, D_scale);
+                           epilogue, b_layout, alpha, limit, D_scale, D_row_ptr);
 }
 
 Tensor b200_grouped_gemm_check(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
@@ -606,7 +613,8 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
   m.def(
       "b200_grouped_gemm(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? bias, "
       "Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, int "
-      "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None) -> Tensor");
+      "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None, Tensor? D_row_ptr=None) "
+      "-> Tensor");
   m.def(
       "b200_grouped_gemm_check(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? "
       "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "

@@ -22,7 +22,7 @@ class GemmArgs(Structure):
         ("A", c_void_p), ("a_scale", c_void_p), ("B", c_void_p), ("b_layout", c_int),
         ("b_scale", c_void_p), ("bias", c_void_p), ("bias_dtype", c_int), ("D", c_void_p),
         ("d_scale", c_void_p), ("rows_per_expert", c_void_p), ("R", c_int64), ("N", c_int),
-        ("K", c_int), ("E", c_int), ("alpha", c_float), ("limit", c_float),
+        ("K", c_int), ("E", c_int), ("alpha", c_float), ("limit", c_float), ("d_row_ptr", c_void_p),
     ]
 
 
@@ -74,6 +74,14 @@ SIGNATURES = {
                                         c_void_p]),
     "b200moe_grouped_gemm_check": (c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_device_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "b200moe_ep_put_counts": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200moe_ep_offsets": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int64, c_void_p]),
+    "b200moe_ep_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+                                c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                c_void_p]),
+    "b200moe_ep_return_table": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
+                                        c_int64, c_int64, c_void_p, c_void_p]),
 }
 
 _lib = None

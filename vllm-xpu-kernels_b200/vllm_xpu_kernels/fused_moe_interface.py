@@ -164,13 +164,18 @@ class XpuFusedMoe:
 
     # ------------------------------------------------------------------
     def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
-              a1q_scale=None):
+              a1q_scale=None, row_destinations=None):
         """output[T, H] = sum_j w[t, j] * Expert_{ids[t, j]}(hidden_states[t]).
 
         ``hidden_states`` is bf16/fp16 ``[T, H]``, or already quantised
         (e4m3 ``[T, H]`` with ``a1q_scale`` f32 ``[T, H/128]``) for block-FP8
         weights.  ``topk_weights`` is f32 ``[T, k]``; ``topk_ids`` int32/int64
-        global expert ids; ``expert_map`` int32 global -> local id or -1."""
+        global expert ids; ``expert_map`` int32 global -> local id or -1.
+
+        ``row_destinations`` (not in the reference signature; used by the expert-parallel
+        exchange): a callable that gets the ``[T, k]`` row map and returns an int64 device
+        table with, per permuted row, the address the second GEMM must store that row at.
+        ``output`` is then not written and the weighted combine is the caller's."""
         num_rows, hidden_size = hidden_states.shape
         k = topk_ids.shape[1]  # n_experts_per_token, or 1 for rows that arrive already dispatched
         R = num_rows * k
@@ -199,6 +204,7 @@ class XpuFusedMoe:
                                                  row_map, topk_ids, self.total_experts_num,
                                                  self.local_experts_num)
 
+        row_ptr = row_destinations(row_map) if row_destinations is not None else None
         I, E = self.inter_size, self.num_experts
         oai = _is_swigluoai(self.activation)
         gemm = torch.ops._xpu_C.b200_grouped_gemm
@@ -228,10 +234,12 @@ class XpuFusedMoe:
                     act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
                     with self._stage("act_quant"):
                         torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
-            gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
+            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=output.dtype,
+                                    device=dev)
             with self._stage("gemm2"):
                 gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
-                     rows_per_expert, hidden_size, I, E, EPI_STORE, B_LAYOUT_KN)
+                     rows_per_expert, hidden_size, I, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None,
+                     row_ptr)
         else:
             if self.is_mxfp4:
                 w13, w2, layout = self._w13_16, self._w2_16, B_LAYOUT_NK
@@ -252,11 +260,14 @@ class XpuFusedMoe:
                     gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
                          hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702,
                          7.0)
-            gemm2_out = torch.empty((R, hidden_size), dtype=output.dtype, device=dev)
+            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=output.dtype,
+                                    device=dev)
             with self._stage("gemm2"):
                 gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, I,
-                     E, EPI_STORE, layout)
+                     E, EPI_STORE, layout, 1.702, 7.0, None, row_ptr)
 
+        if row_ptr is not None:
+            return
         with self._stage("gather"):
             torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
                                         self.num_experts)
