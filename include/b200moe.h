@@ -85,6 +85,18 @@ int b200moe_grouped_topk(const void* scores, int in_dtype, const void* bias,
                          float routed_scaling_factor, int scoring_func,
                          float* values, int32_t* ids, void* stream);
 
+/* topk_softplus_sqrt (csrc/moe/torch_bindings.cpp:73-78,
+ * csrc/moe/topk_softplus_sqrt_kernels.cpp:742-817): scores = sqrt(softplus(x)) in
+ * fp32; selection and weights as topk_sigmoid.  With `tid2eid` (i32 [vocab, k])
+ * and `input_ids` [T] the experts of row t are tid2eid[input_ids[t]] (hash
+ * routing) and only the weights come from the scores. */
+int b200moe_topk_softplus_sqrt(const void* logits, int in_dtype, int T, int E, int k,
+                               int renormalize, float routed_scaling_factor,
+                               const float* bias, const void* input_ids,
+                               int input_ids_dtype, const int32_t* tid2eid,
+                               const uint8_t* is_padding, float* weights, void* ids,
+                               int ids_dtype, int32_t* src_rows, void* stream);
+
 /* ---- permutation ------------------------------------------------------ */
 
 /* moe_align_block_size (csrc/moe/torch_bindings.cpp:14-20,
@@ -124,6 +136,24 @@ int b200moe_moe_align_block_size_static(const void* topk_ids, int ids_dtype,
                                         int64_t sorted_capacity, int32_t* expert_ids,
                                         int64_t blocks_capacity,
                                         int32_t* num_tokens_post_pad, void* stream);
+
+/* batched_moe_align_block_size (csrc/moe/torch_bindings.cpp:24-33,
+ * csrc/moe/moe_align_sum_kernels.cpp:1183-1222): batch b owns token slots
+ * [b*max_tokens, b*max_tokens + n_b); sorted_ids has ceil(max_tokens/bs)*bs*B
+ * entries (sentinel B*max_tokens), block_ids one entry per block (-1 unused). */
+int b200moe_batched_moe_align_block_size(int max_tokens_per_batch, int block_size,
+                                         const int32_t* batch_num_tokens,
+                                         int num_batches, int32_t* sorted_ids,
+                                         int32_t* block_ids,
+                                         int32_t* num_tokens_post_pad, void* stream);
+
+/* reorder_mxfp_scales (csrc/moe/torch_bindings.cpp:103-106,
+ * csrc/moe/reorder_mxfp_scales.cpp:174-234): e8m0 scales [total_rows, scale_k],
+ * experts back to back -> per expert [scale_k, rows padded to 4], written into
+ * `out` (total_padded_rows * scale_k bytes; the tail is zero-filled). */
+int b200moe_reorder_mxfp_scales(const uint8_t* scales, const int32_t* rows_per_expert,
+                                int num_experts, int scale_k, int64_t total_padded_rows,
+                                uint8_t* out, void* stream);
 
 /* init_expert_map (csrc/moe/torch_bindings.cpp:86-91, csrc/moe/init_expert_map.cpp:78-95). */
 int b200moe_init_expert_map(int32_t* expert_map, int num_local_experts,
@@ -247,6 +277,11 @@ int b200moe_dequant_weights(int recipe, const void* B, const void* b_scale,
 /* Plain CUDA-core evaluation of the same contract, one thread per output
  * element, for checking the tensor-core path on sizes a CPU cannot reach. */
 int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* stream);
+
+/* Launches one warp that waits, for at most `budget_cycles`, on a barrier nobody
+ * arrives at: the wait gives up, B200MOE_TIMEOUT lands in the device status word
+ * and the kernel returns.  A check of the give-up path without a hung GPU. */
+int b200moe_selftest_wait_timeout(long long budget_cycles, void* stream);
 
 /* Reads (and clears) the sticky device status word that bounded waits inside
  * the tensor-core kernels set when they give up; 0 = none.  Synchronises. */

@@ -74,6 +74,27 @@ def topk_sigmoid(gating_output, topk, renormalize, bias=None,
                         routed_scaling_factor, is_padding)
 
 
+def topk_softplus_sqrt(gating_output, topk, renormalize, routed_scaling_factor=1.0, bias=None,
+                       input_ids=None, hash_indices_table=None, is_padding=None):
+    """sqrt(softplus(x)) scores in fp32; experts by stable top-k of score(+bias) or, with a
+    hash table, looked up by the token's input id (tests/test_topk_softplus_sqrt.py:20-55)."""
+    scores = torch.nn.functional.softplus(gating_output.float()).sqrt()
+    if hash_indices_table is not None:
+        ids = hash_indices_table[input_ids.long()]
+    else:
+        _, ids = stable_topk(scores + bias.unsqueeze(0) if bias is not None else scores, topk)
+    w = scores.gather(1, ids.long())
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    if routed_scaling_factor != 1.0:
+        w = w * routed_scaling_factor
+    if is_padding is not None:
+        w, ids = w.clone(), ids.clone()
+        w[is_padding] = 0
+        ids[is_padding] = -1
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
 def token_expert_indices(num_tokens: int, topk: int) -> torch.Tensor:
     """Third output of topk_softmax/sigmoid: entry (t, j) = j*T + t
     (csrc/moe/topk.cpp:578)."""
@@ -180,6 +201,37 @@ def moe_align_block_size(topk_ids, block_size, num_experts, expert_map=None,
     expert_ids[: owner.numel()] = owner.to(torch.int32)
     total = torch.tensor([int(padded.sum())], dtype=torch.int32)
     return sorted_ids, expert_ids, total
+
+
+def batched_moe_align_block_size(max_tokens_per_batch, block_size, expert_num_tokens):
+    """Batch b owns token slots [b*max, b*max + n_b); runs padded to the block size, sentinel
+    B*max, unused blocks -1 (tests/test_moe_align_block_size.py:346-392)."""
+    B = expert_num_tokens.numel()
+    per = (max_tokens_per_batch + block_size - 1) // block_size * block_size
+    sorted_ids = torch.full((per * B,), B * max_tokens_per_batch, dtype=torch.int32)
+    block_ids = torch.full((per * B // block_size,), -1, dtype=torch.int32)
+    pos = 0
+    for b, n in enumerate(expert_num_tokens.tolist()):
+        sorted_ids[pos: pos + n] = torch.arange(n, dtype=torch.int32) + b * max_tokens_per_batch
+        nb = (n + block_size - 1) // block_size
+        block_ids[pos // block_size: pos // block_size + nb] = b
+        pos += nb * block_size
+    return sorted_ids, block_ids, torch.tensor([pos], dtype=torch.int32)
+
+
+def reorder_mxfp_scales(scales_u8, rows_per_expert, total_padded_rows):
+    """Per expert: [rows, scale_k] -> [scale_k, rows padded to 4], blocks back to back, zero
+    tail (tests/fused_moe/test_reorder_mxfp_scales.py:26-43)."""
+    scale_k = scales_u8.shape[1]
+    out = torch.zeros((total_padded_rows, scale_k), dtype=torch.uint8)
+    src = dst = 0
+    for r in rows_per_expert.tolist():
+        pr = (r + 3) & ~3
+        if r:
+            out[dst: dst + pr].view(scale_k, pr)[:, :r] = scales_u8[src: src + r].t()
+        src += r
+        dst += pr
+    return out
 
 
 def init_expert_map(num_local_experts: int, ep_rank: int, ep_size: int):

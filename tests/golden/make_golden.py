@@ -148,6 +148,22 @@ def main(root):
     s8 = torch.rand(2, 3, generator=g) + 0.5
     save("fp8_block_w", w=w8, s=s8, deq=mu.dequant_fp8_block_wei(w8, s8))
 
+    # ---- the "next" operators of the registry ------------------------------
+    from tests.test_topk_softplus_sqrt import _torch_topk_softplus_sqrt
+    from tests.fused_moe.test_reorder_mxfp_scales import ref_reorder
+    logits = torch.randn(29, 64, generator=g)
+    bias = torch.randn(64, generator=g) * 0.05
+    table = torch.stack([torch.randperm(64, generator=g)[:6] for _ in range(50)]).to(torch.int32)
+    iid = torch.randint(0, 50, (29,), generator=g).to(torch.int32)
+    pad = torch.rand(29, generator=g) < 0.2
+    w1, i1 = _torch_topk_softplus_sqrt(logits, 6, True, 2.5, bias, None, None, pad)
+    w2, i2 = _torch_topk_softplus_sqrt(logits, 6, False, 1.0, None, iid, table, None)
+    save("softplus_sqrt", logits=logits, bias=bias, table=table, iid=iid, pad=pad, w1=w1, i1=i1, w2=w2, i2=i2)
+    rows = [16, 0, 33, 100, 1]
+    sc = torch.randint(0, 256, (sum(rows), 8), generator=g, dtype=torch.uint8)
+    ref, tot = ref_reorder(sc, rows, 8)
+    save("reorder_scales", scales=sc, rows=torch.tensor(rows, dtype=torch.int32), out=ref, total=tot)
+
     # ---- whole layer, tiny bf16 -----------------------------------------
     T, H, I, E, k = 16, 64, 128, 4, 2
     x = torch.randn(T, H, generator=g).to(torch.bfloat16)

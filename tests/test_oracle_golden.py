@@ -142,3 +142,24 @@ def test_token_expert_indices():
 
 def test_init_expert_map():
     assert O.init_expert_map(2, 1, 3).tolist() == [-1, -1, 0, 1, -1, -1]
+
+
+def test_softplus_sqrt_matches_reference():
+    g = load_golden("softplus_sqrt")
+    w, i = O.topk_softplus_sqrt(g["logits"], 6, True, 2.5, g["bias"], None, None, g["pad"])
+    assert torch.equal(i, g["i1"]) and torch.equal(w, g["w1"])
+    w, i = O.topk_softplus_sqrt(g["logits"], 6, False, 1.0, None, g["iid"], g["table"], None)
+    assert torch.equal(i, g["i2"]) and torch.equal(w, g["w2"])
+
+
+def test_reorder_scales_matches_reference():
+    g = load_golden("reorder_scales")
+    out = O.reorder_mxfp_scales(g["scales"], g["rows"], g["total"])
+    assert torch.equal(out, g["out"])
+
+
+def test_batched_align_known_answer():
+    # 3 batches of up to 5 tokens, block 4: runs [0,1,2 | pad] [10..14 | pad pad pad] [] 
+    s, b, n = O.batched_moe_align_block_size(5, 4, torch.tensor([3, 5, 0], dtype=torch.int32))
+    assert s.tolist() == [0, 1, 2, 15, 5, 6, 7, 8, 9, 15, 15, 15] + [15] * 12
+    assert b.tolist() == [0, 1, 1, -1, -1, -1] and n.item() == 12

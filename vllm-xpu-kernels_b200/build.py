@@ -52,6 +52,10 @@ def build_capi(force=False):
         tag = _hash([src] + headers, " ".join(NVCC_FLAGS))
         obj = os.path.join(BUILD, os.path.basename(src)[:-3] + "." + tag + ".o")
         objs.append(obj)
+        stem = os.path.basename(src)[:-3] + "."
+        for old in os.listdir(BUILD):  # objects of earlier versions of this source
+            if old.startswith(stem) and old.endswith(".o") and os.path.join(BUILD, old) != obj:
+                os.remove(os.path.join(BUILD, old))
         if force or not os.path.exists(obj):
             jobs.append(["nvcc"] + NVCC_FLAGS + ["-c", src, "-o", obj])
     with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:

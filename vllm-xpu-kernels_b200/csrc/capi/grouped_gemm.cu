@@ -1011,6 +1011,36 @@ extern "C" int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* s
   return launch_status("gemm_check_kernel");
 }
 
+// A wait that can never be satisfied, with a budget of `budget_cycles`: exercises the path
+// every tensor-core kernel takes when a barrier does not complete (flag raised, status word
+// written, kernel returns) without involving tensor memory or TMA.
+__global__ void wait_timeout_selftest_kernel(long long budget_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    b200moe::sm100::mbar_init(&bar, 1);
+    b200moe::sm100::mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    bool done = false;
+    while (!done && clock64() - t0 < budget_cycles) done = b200moe::sm100::mbar_try_wait(&bar, 0);
+    if (!done) {
+      abort_flag = 1;
+      atomicExch(&b200moe::g_device_status, B200MOE_TIMEOUT);
+    }
+  }
+  __syncthreads();
+}
+
+extern "C" int b200moe_selftest_wait_timeout(long long budget_cycles, void* stream) {
+  if (budget_cycles <= 0 || budget_cycles > 2000000000ll) return B200MOE_INVALID_ARG;
+  wait_timeout_selftest_kernel<<<1, 32, 0, as_stream(stream)>>>(budget_cycles);
+  return launch_status("wait_timeout_selftest_kernel");
+}
+
 extern "C" int b200moe_device_status(void* stream, int* status_host) {
   if (!status_host) return B200MOE_INVALID_ARG;
   cudaStream_t st = as_stream(stream);

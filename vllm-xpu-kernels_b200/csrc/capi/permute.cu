@@ -493,3 +493,110 @@ extern "C" int b200moe_moe_align_block_size_static(const void* topk_ids, int ids
                                       blocks_capacity, num_tokens_post_pad, scratch,
                                       sizeof(int) * static_cast<size_t>(kStaticScratchInts), stream);
 }
+
+// ---- batched_moe_align_block_size and reorder_mxfp_scales ------------------------------
+
+namespace b200moe {
+namespace {
+
+// One CTA: every batch (expert) b owns token slots [b*max_tokens, b*max_tokens + n_b); its
+// run in sorted_ids starts at the padded prefix of the batches before it.
+__global__ void __launch_bounds__(1024) batched_align_kernel(
+    int num_batches, int max_tokens, int block_size, const int32_t* __restrict__ batch_num_tokens,
+    int32_t* __restrict__ sorted_ids, int32_t* __restrict__ block_ids,
+    int32_t* __restrict__ num_tokens_post_pad) {
+  __shared__ int start[1024];
+  __shared__ int warp_tot[32];
+  const int t = threadIdx.x;
+  const int blocks_per_batch = (max_tokens + block_size - 1) / block_size;
+  const int sorted_size = blocks_per_batch * num_batches * block_size;
+  const int sentinel = num_batches * max_tokens;
+  for (int i = t; i < sorted_size; i += 1024) sorted_ids[i] = sentinel;
+  for (int i = t; i < sorted_size / block_size; i += 1024) block_ids[i] = -1;
+  const int n = t < num_batches ? batch_num_tokens[t] : 0;
+  const int padded = (n + block_size - 1) / block_size * block_size;
+  int incl = padded;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int o = __shfl_up_sync(0xffffffffu, incl, off);
+    if ((t & 31) >= off) incl += o;
+  }
+  if ((t & 31) == 31) warp_tot[t >> 5] = incl;
+  __syncthreads();
+  int base = 0;
+  for (int w = 0; w < (t >> 5); ++w) base += warp_tot[w];
+  start[t] = base + incl - padded;
+  if (t == num_batches - 1) num_tokens_post_pad[0] = base + incl;
+  __syncthreads();
+  // fill: all threads walk all batches' tokens
+  for (int b = 0; b < num_batches; ++b) {
+    const int nb = batch_num_tokens[b];
+    const int s0 = start[b];
+    for (int i = t; i < nb; i += 1024) sorted_ids[s0 + i] = b * max_tokens + i;
+    const int blocks = (nb + block_size - 1) / block_size;
+    for (int i = t; i < blocks; i += 1024) block_ids[s0 / block_size + i] = b;
+  }
+}
+
+// Activation scales of an MX-quantised A, [total_rows, scale_k] row-major with experts back
+// to back, re-laid per expert as [scale_k, rows padded to 4] (M-major), experts back to back
+// in the padded numbering.  One thread per destination byte.
+__global__ void reorder_scales_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                      const int32_t* __restrict__ rows_per_expert, int num_experts,
+                                      int scale_k, int64_t total_padded_rows) {
+  const int64_t total = total_padded_rows * scale_k;
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    // find the expert whose padded block holds flat destination byte i
+    int64_t dst_off = 0, src_off = 0;
+    uint8_t v = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      const int r = rows_per_expert[e];
+      const int pr = (r + 3) & ~3;
+      const int64_t block = static_cast<int64_t>(pr) * scale_k;
+      if (i < dst_off * scale_k + block) {
+        const int64_t local = i - dst_off * scale_k;  // inside a [scale_k, pr] block
+        const int kcol = static_cast<int>(local / pr);
+        const int row = static_cast<int>(local % pr);
+        if (row < r) v = src[(src_off + row) * scale_k + kcol];
+        break;
+      }
+      dst_off += pr;
+      src_off += r;
+    }
+    dst[i] = v;
+  }
+}
+
+// Self-test of the bounded wait the tensor-core kernels rely on: waits on a barrier nobody
+// will ever arrive at, with a short budget, and records the time-out in the status word.
+}  // namespace
+}  // namespace b200moe
+
+extern "C" int b200moe_batched_moe_align_block_size(int max_tokens_per_batch, int block_size,
+                                                    const int32_t* batch_num_tokens,
+                                                    int num_batches, int32_t* sorted_ids,
+                                                    int32_t* block_ids,
+                                                    int32_t* num_tokens_post_pad, void* stream) {
+  if (max_tokens_per_batch <= 0 || block_size <= 0 || num_batches <= 0 || num_batches > 1024 ||
+      !batch_num_tokens || !sorted_ids || !block_ids || !num_tokens_post_pad)
+    return B200MOE_INVALID_ARG;
+  batched_align_kernel<<<1, 1024, 0, as_stream(stream)>>>(num_batches, max_tokens_per_batch,
+                                                          block_size, batch_num_tokens, sorted_ids,
+                                                          block_ids, num_tokens_post_pad);
+  return launch_status("batched_align_kernel");
+}
+
+extern "C" int b200moe_reorder_mxfp_scales(const uint8_t* scales, const int32_t* rows_per_expert,
+                                           int num_experts, int scale_k, int64_t total_padded_rows,
+                                           uint8_t* out, void* stream) {
+  if (num_experts < 0 || scale_k < 0 || total_padded_rows < 0) return B200MOE_INVALID_ARG;
+  if (num_experts == 0 || scale_k == 0 || total_padded_rows == 0) return B200MOE_OK;
+  if (!rows_per_expert || !out) return B200MOE_INVALID_ARG;
+  const int64_t total = total_padded_rows * scale_k;
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
+  reorder_scales_kernel<<<static_cast<int>(blocks), 256, 0, as_stream(stream)>>>(
+      scales, out, rows_per_expert, num_experts, scale_k, total_padded_rows);
+  return launch_status("reorder_scales_kernel");
+}

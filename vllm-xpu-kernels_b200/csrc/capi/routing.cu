@@ -56,13 +56,18 @@ __device__ __forceinline__ float group_sum(float v) {
 
 constexpr int kInvalidIdx = 0x7fffffff;
 
-// One row per LANES threads.  SIGMOID selects the scoring function.
-template <typename T, int LANES, int VPT, bool SIGMOID>
+enum : int { SCORE_SOFTMAX = 0, SCORE_SIGMOID = 1, SCORE_SOFTPLUS_SQRT = 2 };
+
+// One row per LANES threads.  SCORE selects the scoring function.  With a hash table
+// (`tid2eid`, [vocab, k] expert ids) the experts of a row are looked up by its input id
+// instead of being selected, and only the weights come from the scores.
+template <typename T, int LANES, int VPT, int SCORE>
 __global__ void __launch_bounds__(128) topk_gating_kernel(
     const T* __restrict__ logits, int num_rows, int E, int k, bool renorm,
     const float* __restrict__ bias, float scale, const uint8_t* __restrict__ is_padding,
     float* __restrict__ weights, void* __restrict__ ids, int ids_dtype,
-    int32_t* __restrict__ src_rows) {
+    int32_t* __restrict__ src_rows, const void* __restrict__ input_ids, int input_ids_dtype,
+    const int32_t* __restrict__ tid2eid) {
   const int rows_per_block = blockDim.x / LANES;
   const int sub = threadIdx.x % LANES;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * rows_per_block + threadIdx.x / LANES;
@@ -79,9 +84,12 @@ __global__ void __launch_bounds__(128) topk_gating_kernel(
     s[i] = x;
     mx = fmaxf(mx, x);
   }
-  if (SIGMOID) {
+  if (SCORE == SCORE_SIGMOID) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) s[i] = round_through<T>(1.0f / (1.0f + expf(-s[i])));
+  } else if (SCORE == SCORE_SOFTPLUS_SQRT) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) s[i] = sqrtf(s[i] > 20.0f ? s[i] : log1pf(expf(s[i])));
   } else {
     mx = group_max<LANES>(mx);
     float sum = 0.f;
@@ -105,20 +113,29 @@ __global__ void __launch_bounds__(128) topk_gating_kernel(
   float my_w = 0.f;
   int my_id = 0;
   float wsum = 0.f;
+  const int64_t hash_row = tid2eid ? load_index(input_ids, input_ids_dtype, r) * k : 0;
   for (int j = 0; j < k; ++j) {
     Best b{-CUDART_INF_F, kInvalidIdx};
     float pay = 0.f;
+    if (tid2eid) {
+      b.idx = tid2eid[hash_row + j];
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int e = sub + LANES * i;
-      if (e < E && !((taken >> i) & 1u) && better(key[i], e, b.key, b.idx)) {
-        b.key = key[i];
-        b.idx = e;
-        pay = s[i];
+      for (int i = 0; i < VPT; ++i)
+        if (sub + LANES * i == b.idx) pay = s[i];
+      pay = group_sum<LANES>(pay);  // exactly one lane holds the expert's score
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int e = sub + LANES * i;
+        if (e < E && !((taken >> i) & 1u) && better(key[i], e, b.key, b.idx)) {
+          b.key = key[i];
+          b.idx = e;
+          pay = s[i];
+        }
       }
+      b = group_argmax<LANES>(b, pay);
+      if (b.idx != kInvalidIdx && (b.idx % LANES) == sub) taken |= 1u << (b.idx / LANES);
     }
-    b = group_argmax<LANES>(b, pay);
-    if (b.idx != kInvalidIdx && (b.idx % LANES) == sub) taken |= 1u << (b.idx / LANES);
     wsum += pay;
     if (j == sub) {  // k <= LANES always holds: k <= E <= LANES when VPT == 1, k <= 32 otherwise
       my_w = pay;
@@ -130,24 +147,26 @@ __global__ void __launch_bounds__(128) topk_gating_kernel(
   const float denom = (renorm && wsum > 0.f) ? wsum : 1.f;
   if (sub < k) {
     float w = renorm ? my_w / denom : my_w;
-    if (SIGMOID) w *= scale;
+    if (SCORE != SCORE_SOFTMAX) w *= scale;
     weights[r * k + sub] = pad ? 0.f : w;
     store_index(ids, ids_dtype, r * k + sub, pad ? -1 : my_id);
     if (src_rows) src_rows[r * k + sub] = static_cast<int32_t>(sub * num_rows + r);
   }
 }
 
-template <typename T, bool SIGMOID>
+template <typename T, int SCORE>
 int launch_topk(const void* logits, int T_, int E, int k, int renorm, const float* bias,
                 float scale, const uint8_t* pad, float* w, void* ids, int ids_dtype,
-                int32_t* src_rows, cudaStream_t st) {
+                int32_t* src_rows, cudaStream_t st, const void* input_ids = nullptr,
+                int input_ids_dtype = B200MOE_I32, const int32_t* tid2eid = nullptr) {
   const T* in = reinterpret_cast<const T*>(logits);
 #define LAUNCH(LANES, VPT)                                                              \
   do {                                                                                  \
     const int rows_per_block = 128 / LANES;                                             \
     const int grid = (T_ + rows_per_block - 1) / rows_per_block;                        \
-    topk_gating_kernel<T, LANES, VPT, SIGMOID><<<grid, 128, 0, st>>>(                   \
-        in, T_, E, k, renorm != 0, bias, scale, pad, w, ids, ids_dtype, src_rows);      \
+    topk_gating_kernel<T, LANES, VPT, SCORE><<<grid, 128, 0, st>>>(                     \
+        in, T_, E, k, renorm != 0, bias, scale, pad, w, ids, ids_dtype, src_rows,       \
+        input_ids, input_ids_dtype, tid2eid);                                           \
     return launch_status("topk_gating_kernel");                                         \
   } while (0)
   if (E <= 4) LAUNCH(4, 1);
@@ -310,7 +329,7 @@ extern "C" int b200moe_topk_softmax(const void* logits, int in_dtype, int T, int
   if (!logits || !weights || !ids) return B200MOE_INVALID_ARG;
   if (k > 32 && E > 32) return B200MOE_UNSUPPORTED;
   return B200MOE_DISPATCH_FLOAT(in_dtype, [&] {
-    return launch_topk<scalar_t, false>(logits, T, E, k, renormalize, bias, 1.f, is_padding,
+    return launch_topk<scalar_t, SCORE_SOFTMAX>(logits, T, E, k, renormalize, bias, 1.f, is_padding,
                                         weights, ids, ids_dtype, src_rows, as_stream(stream));
   });
 }
@@ -325,7 +344,7 @@ extern "C" int b200moe_topk_sigmoid(const void* logits, int in_dtype, int T, int
   if (!logits || !weights || !ids) return B200MOE_INVALID_ARG;
   if (k > 32 && E > 32) return B200MOE_UNSUPPORTED;
   return B200MOE_DISPATCH_FLOAT(in_dtype, [&] {
-    return launch_topk<scalar_t, true>(logits, T, E, k, renormalize, bias, routed_scaling_factor,
+    return launch_topk<scalar_t, SCORE_SIGMOID>(logits, T, E, k, renormalize, bias, routed_scaling_factor,
                                        is_padding, weights, ids, ids_dtype, src_rows,
                                        as_stream(stream));
   });
@@ -348,5 +367,24 @@ extern "C" int b200moe_grouped_topk(const void* scores, int in_dtype, const void
                                             renormalize, routed_scaling_factor, scoring_func,
                                             values, ids, st);
     });
+  });
+}
+
+extern "C" int b200moe_topk_softplus_sqrt(const void* logits, int in_dtype, int T, int E, int k,
+                                          int renormalize, float routed_scaling_factor,
+                                          const float* bias, const void* input_ids,
+                                          int input_ids_dtype, const int32_t* tid2eid,
+                                          const uint8_t* is_padding, float* weights, void* ids,
+                                          int ids_dtype, int32_t* src_rows, void* stream) {
+  if (T < 0 || E <= 0 || k <= 0 || k > E || !is_index_dtype(ids_dtype)) return B200MOE_INVALID_ARG;
+  if ((tid2eid != nullptr) != (input_ids != nullptr)) return B200MOE_INVALID_ARG;
+  if (tid2eid && !is_index_dtype(input_ids_dtype)) return B200MOE_INVALID_ARG;
+  if (T == 0) return B200MOE_OK;
+  if (!logits || !weights || !ids) return B200MOE_INVALID_ARG;
+  if (k > 32 && E > 32) return B200MOE_UNSUPPORTED;
+  return B200MOE_DISPATCH_FLOAT(in_dtype, [&] {
+    return launch_topk<scalar_t, SCORE_SOFTPLUS_SQRT>(
+        logits, T, E, k, renormalize, bias, routed_scaling_factor, is_padding, weights, ids,
+        ids_dtype, src_rows, as_stream(stream), input_ids, input_ids_dtype, tid2eid);
   });
 }

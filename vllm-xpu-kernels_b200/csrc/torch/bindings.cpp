@@ -125,6 +125,53 @@ void topk_sigmoid(Tensor& w, Tensor& ids, Tensor& src, const Tensor& gating, boo
   topk_common(true, w, ids, src, gating, renorm, bias, scale, is_padding);
 }
 
+void topk_softplus_sqrt(Tensor& topk_weights, Tensor& topk_indices, Tensor& token_expert_indices,
+                        const Tensor& gating_output, bool renormalize, double routed_scaling_factor,
+                        const OptTensor& correction_bias, const OptTensor& input_ids,
+                        const OptTensor& tid2eid, const OptTensor& is_padding) {
+  const char* op = "topk_softplus_sqrt";
+  TORCH_CHECK(gating_output.is_contiguous(), op, ": gating_output must be contiguous");
+  const int64_t E = gating_output.size(-1);
+  const int64_t T = gating_output.numel() / E;
+  const int64_t k = topk_weights.size(-1);
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat && topk_weights.is_contiguous() &&
+                  topk_indices.is_contiguous() && token_expert_indices.is_contiguous(),
+              op, ": outputs must be contiguous, weights float32");
+  TORCH_CHECK(token_expert_indices.scalar_type() == at::kInt, op, ": token_expert_indices must be int32");
+  TORCH_CHECK(input_ids.has_value() == tid2eid.has_value(), op, ": input_ids and tid2eid go together");
+  Tensor bias_f, pad_u8, table;
+  const float* bias_p = nullptr;
+  const uint8_t* pad_p = nullptr;
+  if (correction_bias.has_value()) {
+    TORCH_CHECK(correction_bias->numel() == E, op, ": bias must have num_experts entries");
+    bias_f = correction_bias->to(at::kFloat).contiguous();
+    bias_p = bias_f.data_ptr<float>();
+  }
+  if (is_padding.has_value()) {
+    pad_u8 = is_padding->to(at::kBool).contiguous();
+    pad_p = reinterpret_cast<const uint8_t*>(pad_u8.data_ptr());
+  }
+  const void* ids_in = nullptr;
+  int ids_in_dtype = B200MOE_I32;
+  const int32_t* table_p = nullptr;
+  if (tid2eid.has_value()) {
+    TORCH_CHECK(tid2eid->dim() == 2 && tid2eid->size(1) == k, op, ": tid2eid must be [vocab, topk]");
+    TORCH_CHECK(input_ids->is_contiguous() && input_ids->numel() == T, op, ": one input id per token");
+    table = tid2eid->to(at::kInt).contiguous();
+    table_p = table.data_ptr<int>();
+    ids_in = input_ids->data_ptr();
+    ids_in_dtype = index_code(*input_ids, op);
+  }
+  c10::cuda::CUDAGuard guard(gating_output.device());
+  check(b200moe_topk_softplus_sqrt(gating_output.data_ptr(), float_code(gating_output, op), T, E, k,
+                                   renormalize, static_cast<float>(routed_scaling_factor), bias_p,
+                                   ids_in, ids_in_dtype, table_p, pad_p,
+                                   topk_weights.data_ptr<float>(), topk_indices.data_ptr(),
+                                   index_code(topk_indices, op), token_expert_indices.data_ptr<int>(),
+                                   cur_stream()),
+        op);
+}
+
 std::tuple<Tensor, Tensor> grouped_topk(const Tensor& scores, int64_t n_group, int64_t topk_group,
                                         int64_t topk, bool renormalize, double scale,
                                         const Tensor& bias, int64_t scoring_func) {
@@ -169,6 +216,43 @@ void moe_align_block_size(const Tensor& topk_ids, int64_t num_experts, int64_t b
             experts_ids.numel(), num_tokens_post_pad.data_ptr<int>(), w.data_ptr(), ws,
             cur_stream()),
         "moe_align_block_size");
+}
+
+void batched_moe_align_block_size(int64_t max_tokens_per_batch, int64_t block_size,
+                                  const Tensor& expert_num_tokens, Tensor& sorted_token_ids,
+                                  Tensor& experts_ids, Tensor& num_tokens_post_pad) {
+  const int64_t B = expert_num_tokens.size(0);
+  const int64_t blocks = (max_tokens_per_batch + block_size - 1) / block_size * B;
+  TORCH_CHECK(expert_num_tokens.scalar_type() == at::kInt && expert_num_tokens.is_contiguous(),
+              "batched_moe_align_block_size: expert_num_tokens must be contiguous int32");
+  TORCH_CHECK(sorted_token_ids.size(0) == blocks * block_size);
+  TORCH_CHECK(experts_ids.size(0) == blocks);
+  TORCH_CHECK(num_tokens_post_pad.size(0) == 1);
+  TORCH_CHECK(B <= 1024);
+  c10::cuda::CUDAGuard guard(expert_num_tokens.device());
+  check(b200moe_batched_moe_align_block_size(max_tokens_per_batch, block_size,
+                                             expert_num_tokens.data_ptr<int>(), B,
+                                             sorted_token_ids.data_ptr<int>(),
+                                             experts_ids.data_ptr<int>(),
+                                             num_tokens_post_pad.data_ptr<int>(), cur_stream()),
+        "batched_moe_align_block_size");
+}
+
+Tensor reorder_mxfp_scales(const Tensor& A_scales, const Tensor& rows_per_expert,
+                           int64_t total_padded_rows) {
+  TORCH_CHECK(A_scales.dim() == 2, "A_scales must be 2D [total_rows, scale_k]");
+  TORCH_CHECK(A_scales.scalar_type() == at::kFloat8_e8m0fnu, "A_scales must be float8_e8m0fnu");
+  TORCH_CHECK(A_scales.is_contiguous(), "A_scales must be contiguous");
+  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt, "rows_per_expert must be int32");
+  TORCH_CHECK(rows_per_expert.is_contiguous(), "rows_per_expert must be contiguous");
+  c10::cuda::CUDAGuard guard(A_scales.device());
+  Tensor out = at::empty({total_padded_rows, A_scales.size(1)}, A_scales.options());
+  check(b200moe_reorder_mxfp_scales(reinterpret_cast<const uint8_t*>(A_scales.data_ptr()),
+                                    rows_per_expert.data_ptr<int>(), rows_per_expert.size(0),
+                                    A_scales.size(1), total_padded_rows,
+                                    reinterpret_cast<uint8_t*>(out.data_ptr()), cur_stream()),
+        "reorder_mxfp_scales");
+  return out;
 }
 
 void init_expert_map(Tensor expert_map, int64_t num_experts, int64_t ep_rank, int64_t ep_size) {
@@ -560,6 +644,16 @@ TORCH_LIBRARY(B200MOE_NS_MOE_C, m) {
       "unpermuted_row_to_permuted_row, int num_experts) -> ()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
   m.def(
+      "batched_moe_align_block_size(int max_tokens_per_batch, int block_size, Tensor "
+      "expert_num_tokens, Tensor! sorted_token_ids, Tensor! experts_ids, Tensor! "
+      "num_tokens_post_pad) -> ()");
+  m.def(
+      "topk_softplus_sqrt(Tensor! topk_weights, Tensor! topk_indices, Tensor! "
+      "token_expert_indices, Tensor gating_output, bool renormalize, float routed_scaling_factor, "
+      "Tensor? correction_bias=None, Tensor? input_ids=None, Tensor? tid2eid=None, Tensor? "
+      "is_padding=None) -> ()");
+  m.def("reorder_mxfp_scales(Tensor A_scales, Tensor rows_per_expert, int total_padded_rows) -> Tensor");
+  m.def(
       "remap_hidden_states(Tensor hidden_states, Tensor? hidden_states_scales, Tensor "
       "remapped_hidden_states, Tensor? remapped_hidden_states_scales, Tensor? expert_map, Tensor "
       "rows_per_expert, Tensor unpermuted_row_to_permuted_row, Tensor topk_ids, int "
@@ -574,6 +668,9 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_MOE_C, CUDA, m) {
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
   m.impl("init_expert_map", &init_expert_map);
+  m.impl("batched_moe_align_block_size", &batched_moe_align_block_size);
+  m.impl("topk_softplus_sqrt", &topk_softplus_sqrt);
+  m.impl("reorder_mxfp_scales", &reorder_mxfp_scales);
   m.impl("remap_hidden_states", &remap_hidden_states);
 }
 

@@ -74,6 +74,14 @@ SIGNATURES = {
                                         c_void_p]),
     "b200moe_grouped_gemm_check": (c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_device_status": (c_int, [c_void_p, POINTER(c_int)]),
+    "b200moe_selftest_wait_timeout": (c_int, [ctypes.c_longlong, c_void_p]),
+    "b200moe_topk_softplus_sqrt": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_void_p, c_void_p]),
+    "b200moe_batched_moe_align_block_size": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                     c_void_p, c_void_p]),
+    "b200moe_reorder_mxfp_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p,
+                                            c_void_p]),
     "b200moe_ep_put_counts": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "b200moe_ep_offsets": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_int64, c_void_p]),
