@@ -46,6 +46,13 @@ extern "C" {
 #define B200MOE_B_LAYOUT_KN 0
 #define B200MOE_B_LAYOUT_NK 1
 
+/* layout of the per-token-group-128 activation scales of an e4m3 A */
+#define B200MOE_A_SCALE_ROW_MAJOR 0    /* [R, K/128], what per_token_group_fp8_quant writes   */
+#define B200MOE_A_SCALE_KBLOCK_MAJOR 1 /* [K/128, R]: also selects the decode-regime kernel
+                                          (weights on the M side of the MMA, 32 tokens per
+                                          tile); FP8_BLOCK recipe, EPI_STORE / EPI_SILU_MUL,
+                                          16-bit output                                      */
+
 /* epilogues of the grouped GEMM */
 #define B200MOE_EPI_STORE 0        /* D = acc (+bias), dtype of D                       */
 #define B200MOE_EPI_SILU_MUL 1     /* D[:, j] = silu(acc[:, j]) * acc[:, N/2 + j]       */
@@ -257,6 +264,7 @@ typedef struct b200moe_gemm_args {
                         that address (N elements) instead of D + r*N.  The
                         addresses may be peer-mapped memory of other GPUs: this
                         is how the expert-parallel combine leaves the GEMM.      */
+  int a_scale_layout; /* B200MOE_A_SCALE_*                                       */
 } b200moe_gemm_args;
 
 /* cutlass_grouped_gemm_interface (csrc/xpu/torch_bindings.cpp:58-67,

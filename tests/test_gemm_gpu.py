@@ -183,6 +183,31 @@ def test_fp8_fused_silu_quant_epilogue(ops, E, avg, K, N, pair, monkeypatch):
     assert ((deq - gact).abs() <= 0.07 * gact.abs() + 2e-3 * rs.unsqueeze(-1) + 1e-6).all()
 
 
+@pytest.mark.parametrize("epi", [EPI_STORE, EPI_SILU])
+@pytest.mark.parametrize("E,max_rows,K,N", [(4, 5, 256, 512), (16, 70, 512, 1024), (64, 33, 1024, 256),
+                                            (3, 1, 7168, 512)])
+def test_fp8_decode_kernel(ops, epi, E, max_rows, K, N):
+    """Few rows per expert: weights on the M side of the MMA, 32 tokens per tile,
+    activation scales K-block-major ([K/128, R])."""
+    g = torch.Generator().manual_seed(E * 7 + K)
+    rows = torch.randint(0, max_rows + 1, (E,), generator=g).to(torch.int32)
+    rows[0] = max_rows
+    R = int(rows.sum())
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    Aq, As = O.per_token_group_fp8_quant(x, 128)
+    Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / K ** 0.5) for _ in range(E)])
+    Bq, Bs = torch.stack(Bq), torch.stack(Bs) * (1.0 + 0.25 * torch.rand(E, K // 128, N // 128, generator=g))
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(torch.bfloat16)
+    ref = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As), Bq, Bs, bias, rows, torch.float32)
+    if epi == EPI_SILU:
+        ref = O.silu_mul_fp32(ref)
+    D = torch.full((R + 3, ref.shape[1]), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.t().contiguous().to(DEV), Bq.to(DEV), Bs.to(DEV), bias.to(DEV),
+                                 D, rows.to(DEV), N, K, E, epi, KN, 1.702, 7.0, None, None, 1)
+    close(D[:R], ref)
+    assert (D[R:] == 9.0).all()
+
+
 def test_fp8_weights_with_16bit_activations(ops):
     # what the reference kernel does natively: weights expanded, activations untouched
     E, K, N = 3, 256, 384

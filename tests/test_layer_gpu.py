@@ -63,9 +63,11 @@ def test_c0_full(ops):
     check(out, ref, 2e-2)
 
 
-@pytest.mark.parametrize("name,T,E_limit,tol", [("c1", 96, None, 5e-2), ("c2", 160, 24, 2e-2),
-                                                ("c3", 48, 20, 5e-2)])
-def test_reduced_configs(ops, name, T, E_limit, tol):
+@pytest.mark.parametrize("name,T,E_limit,tol,decode", [("c1", 96, None, 5e-2, "0"), ("c2", 160, 24, 2e-2, "0"),
+                                                       ("c3", 48, 20, 5e-2, "0"), ("c1", 24, None, 5e-2, "1"),
+                                                       ("c3", 40, 20, 5e-2, "1")])
+def test_reduced_configs(ops, name, T, E_limit, tol, decode, monkeypatch):
+    monkeypatch.setenv("B200MOE_DECODE_PATH", decode)   # "1": the weight-streaming kernels
     """Real H/I/E of the config, few tokens.  Only the first E_limit experts'
     weights are built, and the routing is steered onto them with an expert_map
     that marks the rest non-local (the layer's own expert-parallel masking), so

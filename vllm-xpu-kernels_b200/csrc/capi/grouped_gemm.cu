@@ -872,6 +872,8 @@ __global__ void dequant_mxfp4_kernel(const uint8_t* __restrict__ w, const uint8_
   }
 }
 
+#include "grouped_gemm_decode.cuh"
+
 }  // namespace
 }  // namespace b200moe
 
@@ -967,6 +969,7 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   const bool wide = want_wide_tile(a);
   const bool pair = want_pair(a, wide);
 
+  if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR) return grouped_gemm_decode(a, st);
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3) {
     if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
     if (a.epilogue == B200MOE_EPI_SILU_MUL && (a.N / 2) % 128 != 0) return B200MOE_UNSUPPORTED;

@@ -483,7 +483,7 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
                          const OptTensor& D_scale = std::nullopt,
-                         const OptTensor& D_row_ptr = std::nullopt) {
+                         const OptTensor& D_row_ptr = std::nullopt, int64_t a_scale_layout = 0) {
   const char* op = "cutlass_grouped_gemm_interface";
   TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && D.is_contiguous(), op, ": A, B and D must be contiguous");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
@@ -497,6 +497,7 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
   a.A = A.data_ptr();
   a.B = B.data_ptr();
   a.b_layout = static_cast<int>(b_layout);
+  a.a_scale_layout = static_cast<int>(a_scale_layout);
   a.D = D.data_ptr();
   if (D_scale.has_value()) {
     TORCH_CHECK(D_scale->scalar_type() == at::kFloat && D_scale->is_contiguous(), op,
@@ -565,9 +566,10 @@ Tensor b200_grouped_gemm(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const OptTensor& B_scale, const OptTensor& bias, Tensor D,
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
-                         const OptTensor& D_scale, const OptTensor& D_row_ptr) {
+                         const OptTensor& D_scale, const OptTensor& D_row_ptr,
+                         int64_t a_scale_layout) {
   return grouped_gemm_impl(A, A_scale, B, B_scale, bias, D, rows_per_expert, N, K, num_experts,
-                           epilogue, b_layout, alpha, limit, D_scale, D_row_ptr);
+                           epilogue, b_layout, alpha, limit, D_scale, D_row_ptr, a_scale_layout);
 }
 
 Tensor b200_grouped_gemm_check(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
@@ -710,8 +712,8 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
   m.def(
       "b200_grouped_gemm(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? bias, "
       "Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, int "
-      "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None, Tensor? D_row_ptr=None) "
-      "-> Tensor");
+      "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None, Tensor? D_row_ptr=None, int "
+      "a_scale_layout=0) -> Tensor");
   m.def(
       "b200_grouped_gemm_check(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? "
       "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "

@@ -23,6 +23,7 @@ class GemmArgs(Structure):
         ("b_scale", c_void_p), ("bias", c_void_p), ("bias_dtype", c_int), ("D", c_void_p),
         ("d_scale", c_void_p), ("rows_per_expert", c_void_p), ("R", c_int64), ("N", c_int),
         ("K", c_int), ("E", c_int), ("alpha", c_float), ("limit", c_float), ("d_row_ptr", c_void_p),
+        ("a_scale_layout", c_int),
     ]
 
 

@@ -185,6 +185,10 @@ class XpuFusedMoe:
         if num_rows == 0:
             return
 
+        if (self.is_block_fp8 and row_destinations is None and self._decode_regime(num_rows * k)
+                and self.activation == "silu" and not (self.gemm1_clamp_limit or 0) > 0):
+            return self._apply_decode(output, hidden_states, topk_weights, topk_ids, expert_map,
+                                      a1q_scale)
         if self.is_block_fp8 and a1q_scale is None:
             # dynamic per-token-group-128 quantisation, once per token (not per routed row)
             from .moe_utils import quant_fp8_block_act
@@ -271,6 +275,51 @@ class XpuFusedMoe:
         with self._stage("gather"):
             torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
                                         self.num_experts)
+
+    def _decode_regime(self, routed_rows: int) -> bool:
+        """Opt-in (B200MOE_DECODE_PATH=1): run the GEMMs with the weights on the M side of the
+        MMA, 32 tokens per tile.  Measured no faster than the default kernels at 1..256
+        tokens on the DeepSeek-V3 shape, so it is not selected automatically."""
+        return os.environ.get("B200MOE_DECODE_PATH") == "1"
+
+    def _apply_decode(self, output, hidden_states, topk_weights, topk_ids, expert_map, a1q_scale):
+        from .moe_utils import dequant_fp8_block_act
+        T, H = hidden_states.shape
+        k = topk_ids.shape[1]
+        R, I, E = T * k, self.inter_size, self.num_experts
+        dev = hidden_states.device
+        if a1q_scale is not None:  # rare here: bring the few rows back to 16 bit first
+            hidden_states = dequant_fp8_block_act(hidden_states, a1q_scale).to(output.dtype)
+        if expert_map is None and self.ep_size > 1:
+            expert_map = self.expert_map
+        remapped = torch.empty((R, H), dtype=hidden_states.dtype, device=dev)
+        rows_per_expert = torch.zeros((E,), dtype=torch.int32, device=dev)
+        row_map = torch.empty((T, k), dtype=torch.int32, device=dev)
+        with self._stage("remap"):
+            torch.ops._moe_C.remap_hidden_states(hidden_states, None, remapped, None, expert_map,
+                                                 rows_per_expert, row_map, topk_ids,
+                                                 self.total_experts_num, self.local_experts_num)
+
+        def quant_kblock_major(x):
+            q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=dev)
+            s = torch.empty((x.shape[1] // 128, x.shape[0]), dtype=torch.float32, device=dev)
+            torch.ops._C.per_token_group_fp8_quant(x, q, s.t(), 128, 1e-10, -448.0, 448.0, False,
+                                                   False, False)
+            return q, s
+
+        gemm = torch.ops._xpu_C.b200_grouped_gemm
+        xq, xs = quant_kblock_major(remapped)
+        act = torch.empty((R, I), dtype=output.dtype, device=dev)
+        with self._stage("gemm1"):
+            gemm(xq, xs, self.w13, self.gemm1_wei_scales, self.w13_bias, act, rows_per_expert, 2 * I,
+                 H, E, EPI_SILU_MUL, B_LAYOUT_KN, 1.702, 7.0, None, None, 1)
+        aq, as_ = quant_kblock_major(act)
+        gemm2_out = torch.empty((R, H), dtype=output.dtype, device=dev)
+        with self._stage("gemm2"):
+            gemm(aq, as_, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out, rows_per_expert, H,
+                 I, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None, None, 1)
+        with self._stage("gather"):
+            torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
 
     def _clamp(self, gemm1_out):
         lim = self.gemm1_clamp_limit
