@@ -305,37 +305,39 @@ int b200moe_device_status(void* stream, int* status_host);
  * rank.  All four only enqueue kernels that write; the device-wide barriers
  * between them are the caller's. */
 
-/* Writes my per-destination row counts into row `my_rank` of every rank's i32
- * [world, world] matrix at `counts_offset`. */
-int b200moe_ep_put_counts(const int32_t* send_counts, const int64_t* peer_bases_host,
-                          int64_t counts_offset, int my_rank, int world, void* stream);
+/* Writes my rows-per-global-expert (i32 [num_counts], num_counts = world *
+ * experts_per_rank) into row `my_rank` of every rank's i32 [world, num_counts]
+ * matrix at `counts_offset`. */
+int b200moe_ep_put_counts(const int32_t* send_counts, int num_counts,
+                          const int64_t* peer_bases_host, int64_t counts_offset,
+                          int my_rank, int world, void* stream);
 
-/* From the complete matrix (local copy): send_base i32 [world+1] (prefix of my
- * row), dst_base i32 [world] (my first row inside each destination's receive
- * buffer), recv_base i32 [world+1] (first row of each source in mine).  Rows
- * [recv_base[world], capacity) of recv_expert are set to -1. */
-int b200moe_ep_offsets(const int32_t* counts, int my_rank, int world, int32_t* send_base,
-                       int32_t* dst_base, int32_t* recv_base, int32_t* recv_expert,
-                       int64_t capacity, void* stream);
+/* From the complete matrix (local copy): my_prefix i32 [E+1] (prefix of my own
+ * counts = my send order), dst_start i32 [E] (first row of my rows for expert e
+ * inside its owner's expert-grouped receive buffer), rows_per_expert i32
+ * [experts_per_rank] (what each of my experts receives; feed it to the grouped
+ * GEMMs), recv_total i32 [1]. */
+int b200moe_ep_offsets(const int32_t* counts, int my_rank, int world,
+                       int experts_per_rank, int32_t* my_prefix, int32_t* dst_start,
+                       int32_t* rows_per_expert, int32_t* recv_total, void* stream);
 
-/* Stores my send rows (grouped by destination, as remap_hidden_states with an
- * expert->rank map leaves them), their scale rows and local expert ids into the
- * destinations' receive buffers. */
-int b200moe_ep_push(const void* send_rows, const void* send_scales,
-                    const int32_t* send_expert, int64_t num_rows, int64_t row_bytes,
-                    int64_t scale_row_bytes, int world, const int32_t* send_base,
-                    const int32_t* dst_base, const int64_t* peer_bases_host,
-                    int64_t rows_offset, int64_t scales_offset, int64_t expert_offset,
+/* Stores my send rows (grouped by global expert, as remap_hidden_states with no
+ * expert map leaves them) and their scale rows at their final place in the
+ * owners' receive buffers, and per row an i64 (my_rank << 32 | row) at
+ * meta_offset. */
+int b200moe_ep_push(const void* send_rows, const void* send_scales, int64_t num_rows,
+                    int64_t row_bytes, int64_t scale_row_bytes, int my_rank, int world,
+                    int experts_per_rank, const int32_t* my_prefix,
+                    const int32_t* dst_start, const int64_t* peer_bases_host,
+                    int64_t rows_offset, int64_t scales_offset, int64_t meta_offset,
                     int64_t capacity, void* stream);
 
-/* dst_addr[row_map[j]] = address, in the return buffer of the rank that sent
- * received row j, of the slot that row came from; feed it to
- * b200moe_gemm_args.d_row_ptr of the second grouped GEMM. */
-int b200moe_ep_return_table(const int32_t* row_map, const int32_t* recv_base,
-                            const int32_t* counts, int my_rank, int world,
+/* dst_addr[j] = address, in the return buffer of the rank that sent received row
+ * j, of the row it came from; feed it to b200moe_gemm_args.d_row_ptr of the
+ * second grouped GEMM. */
+int b200moe_ep_return_table(const int64_t* meta, const int32_t* recv_total, int world,
                             const int64_t* peer_bases_host, int64_t return_offset,
-                            int64_t row_bytes, int64_t capacity, int64_t* dst_addr,
-                            void* stream);
+                            int64_t row_bytes, int64_t* dst_addr, void* stream);
 
 #ifdef __cplusplus
 }

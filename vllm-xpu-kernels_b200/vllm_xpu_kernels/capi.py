@@ -83,14 +83,14 @@ SIGNATURES = {
                                                      c_void_p, c_void_p]),
     "b200moe_reorder_mxfp_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p,
                                             c_void_p]),
-    "b200moe_ep_put_counts": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
-    "b200moe_ep_offsets": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                   c_int64, c_void_p]),
-    "b200moe_ep_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+    "b200moe_ep_put_counts": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "b200moe_ep_offsets": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p]),
+    "b200moe_ep_push": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                                 c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                 c_void_p]),
-    "b200moe_ep_return_table": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int64,
-                                        c_int64, c_int64, c_void_p, c_void_p]),
+    "b200moe_ep_return_table": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
+                                        c_void_p, c_void_p]),
 }
 
 _lib = None

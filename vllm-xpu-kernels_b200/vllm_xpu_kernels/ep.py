@@ -136,15 +136,17 @@ class PeerExpertParallel:
     """Expert-parallel layer call whose dispatch and combine are stores into other GPUs'
     memory from this library's own kernels (see csrc/capi/ep.cu):
 
-      pack (remap_hidden_states by destination rank) -> put_counts -> barrier -> offsets ->
-      push rows/scales/expert ids into the destinations' receive buffers -> barrier ->
-      local layer, whose second grouped GEMM stores every result row straight into the
-      return buffer of the rank the token came from -> barrier -> weighted sum (moe_gather).
+      group my rows by global expert (remap_hidden_states) -> put_counts -> barrier ->
+      offsets -> push every row to its final place in its owner's expert-grouped receive
+      buffer -> barrier -> the two grouped GEMMs straight on the receive buffer; the second
+      one stores every result row into the return buffer of the rank the token came from
+      -> barrier -> weighted sum (moe_gather).
 
-    Receive buffers are sized for the worst case (every routed row of every rank lands
-    here); rows nobody writes carry expert id -1 and cost nothing in the GEMMs, whose row
-    counts live on the device.  The three barriers are device-side (symmetric-memory
-    signal pads), stream-ordered, about 7 us each on NVSwitch.
+    The receiving side runs no permutation: senders place rows where the grouped GEMM wants
+    them.  Receive buffers are sized for the worst case (every routed row of every rank
+    lands here); unused rows cost nothing in the GEMMs, whose row counts live on the
+    device.  The three barriers are device-side (symmetric-memory signal pads),
+    stream-ordered, about 7 us each on NVSwitch; there is no host synchronisation.
     """
 
     def __init__(self, group, moe, tokens_per_rank: int, topk: int, hidden: int, row_bytes: int,
@@ -154,39 +156,40 @@ class PeerExpertParallel:
         import torch.distributed._symmetric_memory as symm_mem
 
         from . import capi
-        self.lib, self.capi, self.ct = capi.lib(), capi, ctypes
+        self.lib, self.capi = capi.lib(), capi
         self.group, self.moe = group, moe
         self.G = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.T, self.k, self.H = tokens_per_rank, topk, hidden
         self.row_bytes, self.scale_row_bytes = row_bytes, scale_row_bytes
-        self.experts_per_rank, self.dev, self.out_dtype = experts_per_rank, device, out_dtype
+        self.E_loc, self.dev, self.out_dtype = experts_per_rank, device, out_dtype
         G, R = self.G, tokens_per_rank * topk
+        self.E = G * experts_per_rank
         self.R, self.cap = R, G * R
         self.ret_row_bytes = hidden * torch.empty((), dtype=out_dtype).element_size()
         off = 0
-        self.off_counts = off; off = _align(off + G * G * 4)
+        self.off_counts = off; off = _align(off + G * self.E * 4)
         self.off_rows = off; off = _align(off + self.cap * row_bytes)
         self.off_scales = off; off = _align(off + self.cap * max(scale_row_bytes, 4))
-        self.off_expert = off; off = _align(off + self.cap * 4)
+        self.off_meta = off; off = _align(off + self.cap * 8)
         self.off_ret = off; off = _align(off + R * self.ret_row_bytes)
         self.buf = symm_mem.empty(off, dtype=torch.uint8, device=device)
         self.hdl = symm_mem.rendezvous(self.buf, group.group_name)
         self.buf.zero_()
         self.peer_bases = (ctypes.c_int64 * G)(*[int(p) for p in self.hdl.buffer_ptrs])
         b = self.buf
-        self.counts = b[self.off_counts: self.off_counts + G * G * 4].view(torch.int32)
+        self.counts = b[self.off_counts: self.off_counts + G * self.E * 4].view(torch.int32)
         self.recv_rows = b[self.off_rows: self.off_rows + self.cap * row_bytes]
         self.recv_scales = (b[self.off_scales: self.off_scales + self.cap * scale_row_bytes]
                             if scale_row_bytes else None)
-        self.recv_expert = b[self.off_expert: self.off_expert + self.cap * 4].view(torch.int32)
+        self.meta = b[self.off_meta: self.off_meta + self.cap * 8].view(torch.int64)
         self.ret = b[self.off_ret: self.off_ret + R * self.ret_row_bytes].view(out_dtype).view(R, hidden)
-        self.send_base = torch.zeros(G + 1, dtype=torch.int32, device=device)
-        self.dst_base = torch.zeros(G, dtype=torch.int32, device=device)
-        self.recv_base = torch.zeros(G + 1, dtype=torch.int32, device=device)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.my_prefix = torch.zeros(self.E + 1, **i32)
+        self.dst_start = torch.zeros(self.E, **i32)
+        self.rows_per_expert = torch.zeros(experts_per_rank, **i32)
+        self.recv_total = torch.zeros(1, **i32)
         self.dst_addr = torch.zeros(self.cap, dtype=torch.int64, device=device)
-        self.dummy_out = torch.empty((0, hidden), dtype=out_dtype, device=device)
-        self.ones = torch.ones((self.cap, 1), dtype=torch.float32, device=device)
         self.hdl.barrier(channel=0)
 
     def _check(self, rc, what):
@@ -195,32 +198,36 @@ class PeerExpertParallel:
 
     def apply(self, output, hidden, topk_weights, topk_ids, scales=None):
         lib, G, me = self.lib, self.G, self.rank
+        T, k = topk_ids.shape
+        dev = hidden.device
         st = torch.cuda.current_stream().cuda_stream
-        plan = cuda_plan(hidden, scales, topk_ids, self.experts_per_rank, G)
-        self._check(lib.b200moe_ep_put_counts(plan.send_counts.data_ptr(), self.peer_bases,
+        # my rows grouped by global expert (stable), and how many go to each expert
+        send_rows = torch.empty((T * k, hidden.shape[1]), dtype=hidden.dtype, device=dev)
+        send_scales = (torch.empty((T * k, scales.shape[1]), dtype=scales.dtype, device=dev)
+                       if scales is not None else None)
+        send_counts = torch.zeros(self.E, dtype=torch.int32, device=dev)
+        row_map = torch.empty((T, k), dtype=torch.int32, device=dev)
+        torch.ops._moe_C.remap_hidden_states(hidden, scales, send_rows, send_scales, None, send_counts,
+                                             row_map, topk_ids, self.E, self.E)
+        self._check(lib.b200moe_ep_put_counts(send_counts.data_ptr(), self.E, self.peer_bases,
                                               self.off_counts, me, G, st), "ep_put_counts")
         self.hdl.barrier(channel=0)
-        self._check(lib.b200moe_ep_offsets(self.counts.data_ptr(), me, G, self.send_base.data_ptr(),
-                                           self.dst_base.data_ptr(), self.recv_base.data_ptr(),
-                                           self.recv_expert.data_ptr(), self.cap, st), "ep_offsets")
+        self._check(lib.b200moe_ep_offsets(self.counts.data_ptr(), me, G, self.E_loc,
+                                           self.my_prefix.data_ptr(), self.dst_start.data_ptr(),
+                                           self.rows_per_expert.data_ptr(), self.recv_total.data_ptr(),
+                                           st), "ep_offsets")
         self._check(lib.b200moe_ep_push(
-            plan.send_rows.data_ptr(), plan.send_scales.data_ptr() if plan.send_scales is not None else None,
-            plan.send_expert.data_ptr(), self.R, self.row_bytes, self.scale_row_bytes, G,
-            self.send_base.data_ptr(), self.dst_base.data_ptr(), self.peer_bases, self.off_rows,
-            self.off_scales, self.off_expert, self.cap, st), "ep_push")
+            send_rows.data_ptr(), send_scales.data_ptr() if send_scales is not None else None, T * k,
+            self.row_bytes, self.scale_row_bytes, me, G, self.E_loc, self.my_prefix.data_ptr(),
+            self.dst_start.data_ptr(), self.peer_bases, self.off_rows, self.off_scales, self.off_meta,
+            self.cap, st), "ep_push")
         self.hdl.barrier(channel=1)
-
-        def destinations(row_map):
-            self._check(lib.b200moe_ep_return_table(
-                row_map.data_ptr(), self.recv_base.data_ptr(), self.counts.data_ptr(), me, G,
-                self.peer_bases, self.off_ret, self.ret_row_bytes, self.cap, self.dst_addr.data_ptr(),
-                st), "ep_return_table")
-            return self.dst_addr
-
+        self._check(lib.b200moe_ep_return_table(self.meta.data_ptr(), self.recv_total.data_ptr(), G,
+                                                self.peer_bases, self.off_ret, self.ret_row_bytes,
+                                                self.dst_addr.data_ptr(), st), "ep_return_table")
         rows = self.recv_rows.view(hidden.dtype).view(self.cap, -1)
-        rscales = (self.recv_scales.view(scales.dtype).view(self.cap, -1) if scales is not None else None)
-        self.moe.apply(self.dummy_out, rows, self.ones, self.recv_expert.view(self.cap, 1),
-                       a1q_scale=rscales, row_destinations=destinations)
+        rscales = self.recv_scales.view(scales.dtype).view(self.cap, -1) if scales is not None else None
+        self.moe.run_experts(rows, rscales, self.rows_per_expert, self.out_dtype, self.dst_addr)
         self.hdl.barrier(channel=2)
-        torch.ops._moe_C.moe_gather(output, self.ret, topk_weights, plan.row_map, 0)
+        torch.ops._moe_C.moe_gather(output, self.ret, topk_weights, row_map, 0)
         return output

@@ -209,6 +209,23 @@ class XpuFusedMoe:
                                                  self.local_experts_num)
 
         row_ptr = row_destinations(row_map) if row_destinations is not None else None
+        gemm2_out = self.run_experts(remapped, remapped_scales, rows_per_expert, output.dtype, row_ptr)
+        if row_ptr is not None:
+            return
+        with self._stage("gather"):
+            torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
+                                        self.num_experts)
+
+    def run_experts(self, rows, row_scales, rows_per_expert, out_dtype, row_ptr=None):
+        """The two grouped GEMMs with the activation between them on rows that are already
+        grouped by local expert (``rows_per_expert`` int32 on the device, experts back to
+        back).  Returns the ``[R, H]`` result in the same row order, or, with ``row_ptr``
+        (int64 address per row), stores each result row at its address and returns a
+        placeholder.  Not part of the reference class; ``apply`` and the expert-parallel
+        exchange both end here."""
+        R, hidden_size = rows.shape
+        dev = rows.device
+        remapped, remapped_scales = rows, row_scales
         I, E = self.inter_size, self.num_experts
         oai = _is_swigluoai(self.activation)
         gemm = torch.ops._xpu_C.b200_grouped_gemm
@@ -223,13 +240,13 @@ class XpuFusedMoe:
                          act_q, rows_per_expert, 2 * I, hidden_size, E, EPI_SILU_MUL, B_LAYOUT_KN,
                          1.702, 7.0, act_s)
             else:
-                gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
+                gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
                 with self._stage("gemm1"):
                     gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
                          gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
                 self._clamp(gemm1_out)
                 if oai:
-                    act = torch.empty((R, I), dtype=output.dtype, device=dev)
+                    act = torch.empty((R, I), dtype=out_dtype, device=dev)
                     torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
                     from .moe_utils import quant_fp8_block_act
                     act_q, act_s = quant_fp8_block_act(act)
@@ -238,7 +255,7 @@ class XpuFusedMoe:
                     act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
                     with self._stage("act_quant"):
                         torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
-            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=output.dtype,
+            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=out_dtype,
                                     device=dev)
             with self._stage("gemm2"):
                 gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
@@ -249,9 +266,9 @@ class XpuFusedMoe:
                 w13, w2, layout = self._w13_16, self._w2_16, B_LAYOUT_NK
             else:
                 w13, w2, layout = self.w13, self.w2, B_LAYOUT_KN
-            act = torch.empty((R, I), dtype=output.dtype, device=dev)
+            act = torch.empty((R, I), dtype=out_dtype, device=dev)
             if self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0:
-                gemm1_out = torch.empty((R, 2 * I), dtype=output.dtype, device=dev)
+                gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
                 gemm(remapped, None, w13, None, self.w13_bias, gemm1_out, rows_per_expert, 2 * I,
                      hidden_size, E, EPI_STORE, layout)
                 self._clamp(gemm1_out)
@@ -264,17 +281,12 @@ class XpuFusedMoe:
                     gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
                          hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702,
                          7.0)
-            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=output.dtype,
+            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=out_dtype,
                                     device=dev)
             with self._stage("gemm2"):
                 gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, I,
                      E, EPI_STORE, layout, 1.702, 7.0, None, row_ptr)
-
-        if row_ptr is not None:
-            return
-        with self._stage("gather"):
-            torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
-                                        self.num_experts)
+        return gemm2_out
 
     def _decode_regime(self, routed_rows: int) -> bool:
         """Opt-in (B200MOE_DECODE_PATH=1): run the GEMMs with the weights on the M side of the
