@@ -46,6 +46,7 @@ constexpr int BM = 128;
 constexpr int kStageRowBytes = 128;  // one swizzle row: 64 bf16 or 128 fp8 along the box's inner dim
 constexpr int kMaxExpertsSmem = 1024;
 constexpr int kSwizzleGroupM = 8;
+constexpr int kMaxKBlocks = 160;  // K <= 20480 for the FP8 block-scaled recipe
 
 enum : int { KIND_F16 = 0, KIND_F8 = 1 };
 
@@ -417,6 +418,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ float xchg[2][256];  // group-amax exchange of the quantising epilogue, by tile parity
+  __shared__ float sb_smem[2][2 * kMaxKBlocks];  // weight scales of the tile's two column blocks
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -555,23 +557,44 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int64_t grow = static_cast<int64_t>(tc.row_start) + rank * BM + row_in_tile;
       float acc[CPT];
       float ta[32], tb[32];
-      // weight-scale blocks of the first / second half of this thread's columns
-      int nb0 = 0, nb1 = 0;
+      // Scales.  The tile touches at most two 128-column weight-scale blocks; their K/128
+      // values are staged in shared memory once per tile (one round trip to L2/DRAM instead
+      // of one on the critical path of every K block).  The row's activation scales are
+      // contiguous in K and are fetched four K blocks at a time, four ahead of use.
+      int sel0 = 0, sel1 = 0;
       const float* sa_ptr = nullptr;
-      const float* sb_ptr = nullptr;
-      float sa_n = 0.f, sb0_n = 0.f, sb1_n = 0.f;
+      float4 sa_cur = make_float4(0.f, 0.f, 0.f, 0.f), sa_next = sa_cur;
+      const bool sa_vec = (num_kb & 3) == 0;
+      const float* sbs = sb_smem[tile_parity];
+      auto load_sa4 = [&](int ph0) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (!row_ok || ph0 >= num_kb) return v;
+        if (sa_vec) return *reinterpret_cast<const float4*>(sa_ptr + ph0);
+        v.x = sa_ptr[ph0];
+        if (ph0 + 1 < num_kb) v.y = sa_ptr[ph0 + 1];
+        if (ph0 + 2 < num_kb) v.z = sa_ptr[ph0 + 2];
+        if (ph0 + 3 < num_kb) v.w = sa_ptr[ph0 + 3];
+        return v;
+      };
       if constexpr (C::PROMOTE) {
 #pragma unroll
         for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
-        nb0 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, 0), p.N) / 128;
-        nb1 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, NCH / 2), p.N) / 128;
-        nb0 = nb0 < nb_count ? nb0 : nb_count - 1;
-        nb1 = nb1 < nb_count ? nb1 : nb_count - 1;
+        int nb_lo = problem_col<C>(tc.n_tile, 0, p.N) / 128;
+        int nb_hi = problem_col<C>(tc.n_tile, C::BN - 1, p.N) / 128;
+        nb_lo = nb_lo < nb_count ? nb_lo : nb_count - 1;
+        nb_hi = nb_hi < nb_count ? nb_hi : nb_count - 1;
+        int nb0 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, 0), p.N) / 128;
+        int nb1 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, NCH / 2), p.N) / 128;
+        sel0 = nb0 >= nb_hi ? 1 : 0;   // both halves fall in one of the two blocks
+        sel1 = nb1 >= nb_hi ? 1 : 0;
+        const float* sb_ptr = p.b_scale + static_cast<int64_t>(tc.expert) * num_kb * nb_count;
+        float* dst = sb_smem[tile_parity];
+        for (int i = threadIdx.x - 128; i < 2 * num_kb; i += C::EPI_WARPS * 32)
+          dst[i] = sb_ptr[(i >> 1) * nb_count + ((i & 1) ? nb_hi : nb_lo)];
         sa_ptr = p.a_scale + grow * num_kb;
-        sb_ptr = p.b_scale + static_cast<int64_t>(tc.expert) * num_kb * nb_count;
-        sa_n = row_ok ? sa_ptr[0] : 0.f;
-        sb0_n = sb_ptr[nb0];
-        sb1_n = sb_ptr[nb1];
+        sa_cur = load_sa4(0);
+        sa_next = load_sa4(4);
+        asm volatile("bar.sync 5, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
       }
       // first two loads of the tile
       ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
@@ -585,13 +608,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
         float s0 = 1.f, s1 = 1.f;
         if constexpr (C::PROMOTE) {
-          s0 = sa_n * sb0_n;
-          s1 = sa_n * sb1_n;
-          if (ph + 1 < phases_per_tile) {  // scales of the next K block, ahead of use
-            sa_n = row_ok ? sa_ptr[ph + 1] : 0.f;
-            sb0_n = sb_ptr[(ph + 1) * nb_count + nb0];
-            sb1_n = sb_ptr[(ph + 1) * nb_count + nb1];
+          const int w = ph & 3;
+          if (w == 0 && ph > 0) {
+            sa_cur = sa_next;
+            sa_next = load_sa4(ph + 4);
           }
+          const float sa = w == 0 ? sa_cur.x : (w == 1 ? sa_cur.y : (w == 2 ? sa_cur.z : sa_cur.w));
+          s0 = sa * sbs[2 * ph + sel0];
+          s1 = sa * sbs[2 * ph + sel1];
         }
         int cur_buf = buf;
 #pragma unroll
@@ -972,6 +996,7 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR) return grouped_gemm_decode(a, st);
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3) {
     if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
+    if (a.K / 128 > kMaxKBlocks) return B200MOE_UNSUPPORTED;
     if (a.epilogue == B200MOE_EPI_SILU_MUL && (a.N / 2) % 128 != 0) return B200MOE_UNSUPPORTED;
     if (pair) return launch_epi<KIND_F8, true, true, 256, 6, true>(a, a.B, B200MOE_E4M3, st);
     if (wide || a.epilogue == B200MOE_EPI_SILU_MUL)
@@ -1019,9 +1044,7 @@ extern "C" int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* s
 // written, kernel returns) without involving tensor memory or TMA.
 __global__ void wait_timeout_selftest_kernel(long long budget_cycles) {
   __shared__ uint64_t bar;
-  __shared__ int abort_flag;
   if (threadIdx.x == 0) {
-    abort_flag = 0;
     b200moe::sm100::mbar_init(&bar, 1);
     b200moe::sm100::mbar_fence_init();
   }
@@ -1030,10 +1053,7 @@ __global__ void wait_timeout_selftest_kernel(long long budget_cycles) {
     const long long t0 = clock64();
     bool done = false;
     while (!done && clock64() - t0 < budget_cycles) done = b200moe::sm100::mbar_try_wait(&bar, 0);
-    if (!done) {
-      abort_flag = 1;
-      atomicExch(&b200moe::g_device_status, B200MOE_TIMEOUT);
-    }
+    if (!done) atomicExch(&b200moe::g_device_status, B200MOE_TIMEOUT);
   }
   __syncthreads();
 }
