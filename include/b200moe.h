@@ -37,11 +37,17 @@ extern "C" {
 #define B200MOE_U32 6
 #define B200MOE_U8 7
 #define B200MOE_E2M1X2 8 /* two e2m1 per byte, low nibble = even element */
+#define B200MOE_E5M2 9
 
 /* weight recipes of the grouped GEMM */
 #define B200MOE_RECIPE_BF16 0     /* B [E,K,N] bf16/f16, no scales                     */
 #define B200MOE_RECIPE_FP8_BLOCK 1 /* B [E,K,N] e4m3, scales f32 [E,K/128,N/128]        */
 #define B200MOE_RECIPE_MXFP4 2    /* B [E,N,K/2] e2m1x2, scales e8m0 u8 [E,N,K/32]     */
+/* 16-bit-activation recipes, taken by b200moe_expand_weights only: */
+#define B200MOE_RECIPE_FP8_TENSOR 3 /* B [E,K,N] e4m3|e5m2, one f32 scale per expert [E] */
+#define B200MOE_RECIPE_MXFP8 4      /* B [E,K,N] e4m3|e5m2, scales e8m0 u8 [E,K/32,N]    */
+#define B200MOE_RECIPE_INT4 5       /* B [E,N,K/2] u8 (value = nibble - 8, low nibble =
+                                       even k), scales bf16|f16|f32 [E,N,K/group]         */
 
 #define B200MOE_B_LAYOUT_KN 0
 #define B200MOE_B_LAYOUT_NK 1
@@ -204,6 +210,27 @@ int b200moe_silu_and_mul(void* out, const void* in, int dtype, int64_t R, int d,
 int b200moe_swigluoai_and_mul(void* out, const void* in, int dtype, int64_t R,
                               int d, float alpha, float limit, void* stream);
 
+/* The remaining activations the layer can be built with
+ * (vllm_xpu_kernels/fused_moe_interface.py:133-154): gelu_and_mul,
+ * gelu_tanh_and_mul (csrc/torch_bindings.cpp:112-116, csrc/activation.cpp:51-72),
+ * swiglustep_and_mul(limit = param0) (:202-206, activation.cpp:297-311),
+ * situ_and_mul(beta = param0, linear_beta = param1; <= 0 leaves `up` linear)
+ * (:118-121, activation.cpp:313-323, argument checks :777-780),
+ * relu2_no_mul (:198-200, activation.cpp:44-49).  Gated forms: in [R,2d] ->
+ * out [R,d], gate = first half.  RELU2_NO_MUL: in [R,d] -> out [R,d].
+ * clamp_limit > 0 first clamps gate to <= limit and up to [-limit, limit], the
+ * layer's gemm1_clamp_limit (fused_moe_interface.py:436-441) without a pass of
+ * its own; for RELU2_NO_MUL the first d/2 columns count as gate. */
+#define B200MOE_ACT_SILU 0
+#define B200MOE_ACT_GELU 1
+#define B200MOE_ACT_GELU_TANH 2
+#define B200MOE_ACT_SWIGLUSTEP 3
+#define B200MOE_ACT_SITU 4
+#define B200MOE_ACT_RELU2_NO_MUL 5
+int b200moe_act_and_mul(void* out, const void* in, int dtype, int64_t R, int d,
+                        int act, float param0, float param1, float clamp_limit,
+                        void* stream);
+
 /* per_token_group_fp8_quant (csrc/torch_bindings.cpp:175-182,
  * csrc/quantization/fp8/fp8_quant.cpp:724-849).  scales f32, element (r, g) at
  * r*scale_stride_row + g*scale_stride_group. */
@@ -281,6 +308,20 @@ int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspace,
  * csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:399-483. */
 int b200moe_dequant_weights(int recipe, const void* B, const void* b_scale,
                             void* out_bf16, int E, int N, int K, void* stream);
+
+/* One-time widening of the weight formats the reference runs with 16-bit
+ * activations (W8A16 per-tensor FP8 and MXFP8, W4A16 INT4; recipe detection in
+ * vllm_xpu_kernels/fused_moe_interface.py:48-83, dequantisation rules in
+ * vllm_xpu_kernels/moe_utils.py:206-217 and tests/fused_moe/test_fused_moe.py:37-50):
+ * out = round_to_out_dtype(value * scale), bf16 or f16, in the layout of the
+ * input ([E,K,N] for the FP8 forms, [E,N,K] for INT4).  The result is the B
+ * operand of a B200MOE_RECIPE_BF16 grouped GEMM.  Stands in for the in-kernel
+ * up-conversion of csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:368-523;
+ * tcgen05 needs both operands in one element width. */
+int b200moe_expand_weights(int recipe, const void* B, int b_dtype,
+                           const void* b_scale, int scale_dtype, int group_size,
+                           void* out, int out_dtype, int E, int N, int K,
+                           void* stream);
 
 /* Plain CUDA-core evaluation of the same contract, one thread per output
  * element, for checking the tensor-core path on sizes a CPU cannot reach. */

@@ -318,6 +318,55 @@ def swigluoai_and_mul(x, alpha=1.702, limit=7.0):
     return (u + 1) * (g * torch.sigmoid(g * alpha))
 
 
+def gelu_and_mul(x, approximate="none"):
+    """gelu(first half) * second half (tests/ops/activation_op.py:83-86)."""
+    d = x.shape[-1] // 2
+    return torch.nn.functional.gelu(x[..., :d], approximate=approximate) * x[..., d:]
+
+
+def relu2_no_mul(x):
+    """relu(x)^2 over every column (tests/ops/activation_op.py:188-190)."""
+    return torch.square(torch.relu(x))
+
+
+def swiglustep_and_mul(x, limit=7.0):
+    """min(silu(gate), limit) * clamp(up, +-limit), fp32 inside
+    (csrc/activation.cpp:297-311; tests/ops/swiglustep_and_mul_op.py)."""
+    d = x.shape[-1] // 2
+    g, u = x[..., :d].float(), x[..., d:].float()
+    return (torch.nn.functional.silu(g).clamp(max=limit) * u.clamp(-limit, limit)).to(x.dtype)
+
+
+def situ_and_mul(x, beta, linear_beta=-1.0):
+    """beta*tanh(gate/beta)*sigmoid(gate) * (linear_beta*tanh(up/linear_beta) or up), fp32
+    inside (tests/test_activation.py:98-103)."""
+    g, u = x.float().chunk(2, dim=-1)
+    g = beta * torch.tanh(g / beta) * torch.sigmoid(g)
+    if linear_beta > 0:
+        u = linear_beta * torch.tanh(u / linear_beta)
+    return (g * u).to(x.dtype)
+
+
+def layer_activation(h, activation, situ_beta=None, situ_linear_beta=None):
+    """fp32 activation step of the layer oracle, by the names XpuFusedMoe takes
+    (vllm_xpu_kernels/fused_moe_interface.py:133-154 and :452-464 for the situ arguments)."""
+    if activation == "silu":
+        return silu_mul_fp32(h)
+    if "swigluoai" in str(activation).lower():
+        return swigluoai_and_mul(h)
+    if activation == "gelu":
+        return gelu_and_mul(h)
+    if activation == "gelu_tanh":
+        return gelu_and_mul(h, "tanh")
+    if activation == "relu2_no_mul":
+        return relu2_no_mul(h)
+    if activation == "swiglustep":
+        return swiglustep_and_mul(h, 7.0)
+    if activation == "situ":
+        return situ_and_mul(h, situ_beta, -1.0 if situ_linear_beta is None else situ_linear_beta)
+    raise ValueError(activation)
+
+
 def per_token_group_fp8_quant(x, group_size=128, eps=1e-10, scale_ue8m0=False,
                               divide=False):
     """scale = max(max(eps, amax)/448, 1/(448*512)), optionally rounded up to a
@@ -469,7 +518,42 @@ def dequant_expert_weight(recipe, w_e, s_e):
         return dequant_fp8_block(w_e, s_e)
     if recipe == "mxfp4":
         return dequant_mxfp4(w_e.view(torch.uint8), s_e.view(torch.uint8)).t()
+    if recipe == "fp8":      # one scale per expert (vllm_xpu_kernels/moe_utils.py:214-215)
+        return w_e.float() * s_e.float()
+    if recipe == "mxfp8":    # e8m0 per 32 of K, [K/32, N] (moe_utils.py:77-80)
+        return w_e.float() * e8m0_to_f32(s_e.view(torch.uint8)).repeat_interleave(32, dim=0)
+    if recipe == "int4":     # [N, K/2] nibbles - 8, scale [N, K/group] (test_fused_moe.py:37-50)
+        return dequant_int4(w_e, s_e).t()
     raise ValueError(recipe)
+
+
+def dequant_int4(w_u8, scale):
+    """[N, K/2] packed (low nibble = even k) -> fp32 [N, K], value (nibble - 8) * scale."""
+    lo = (w_u8 & 0xF).to(torch.int32) - 8
+    hi = (w_u8 >> 4).to(torch.int32) - 8
+    q = torch.stack([lo, hi], dim=-1).reshape(w_u8.shape[0], -1).float()
+    group = q.shape[1] // scale.shape[1]
+    return q * scale.float().repeat_interleave(group, dim=1)
+
+
+def quant_mxfp8_weight(w: torch.Tensor):
+    """fp32 [K, N] -> (e4m3 [K, N], e8m0 u8 [K/32, N]); scale 2^ceil(log2(amax/448)) per 32 of K."""
+    K, N = w.shape
+    g = w.reshape(K // 32, 32, N)
+    amax = g.abs().amax(1).clamp_min(2.0 ** -120)
+    e = torch.ceil(torch.log2(amax / 448.0)).clamp(-127, 127)
+    q = (g / torch.exp2(e).unsqueeze(1)).clamp(-448, 448).reshape(K, N).to(torch.float8_e4m3fn)
+    return q, (e + 127).to(torch.uint8)
+
+
+def quant_int4_weight(w: torch.Tensor, group=128, scale_dtype=torch.bfloat16):
+    """fp32 [N, K] -> (u8 [N, K/2], scale [N, K/group]); symmetric, zero point 8."""
+    N, K = w.shape
+    g = w.reshape(N, K // group, group)
+    scale = (g.abs().amax(-1) / 7.0).clamp_min(1e-8).to(scale_dtype)
+    q = torch.round(g / scale.float().unsqueeze(-1)).clamp(-8, 7).to(torch.int32).reshape(N, K) + 8
+    packed = (q[:, 0::2] | (q[:, 1::2] << 4)).to(torch.uint8)
+    return packed, scale
 
 
 def grouped_gemm(recipe, A, B, B_scale, bias, rows_per_expert, out_dtype=None):
@@ -509,7 +593,7 @@ def qdq_act(recipe, x):
 def fused_moe(recipe, x, w13, w13_scale, w13_bias, w2, w2_scale, w2_bias,
               topk_weights, topk_ids, activation="silu", expert_map=None,
               num_local_experts=None, quant_act=True, out_dtype=None,
-              gemm1_clamp_limit=None):
+              gemm1_clamp_limit=None, situ_beta=None, situ_linear_beta=None):
     """Layer oracle: permute, per-expert dequantise-then-fp32 matmuls with the
     activation between them, weighted un-permute
     (tests/fused_moe/test_fused_moe.py:93-166 for the structure,
@@ -524,12 +608,7 @@ def fused_moe(recipe, x, w13, w13_scale, w13_bias, w2, w2_scale, w2_bias,
         d = h.shape[1] // 2
         h[:, :d].clamp_(max=gemm1_clamp_limit)
         h[:, d:].clamp_(min=-gemm1_clamp_limit, max=gemm1_clamp_limit)
-    if activation == "silu":
-        a = silu_mul_fp32(h)
-    elif "swigluoai" in str(activation).lower():
-        a = swigluoai_and_mul(h)
-    else:
-        raise ValueError(activation)
+    a = layer_activation(h, activation, situ_beta, situ_linear_beta)
     if quant_act:
         a = qdq_act(recipe, a)
     y = grouped_gemm(recipe, a, w2, w2_scale, w2_bias, rows, torch.float32)

@@ -137,6 +137,24 @@ def main(root):
     x = torch.randn(24, 512, generator=g).to(torch.bfloat16) * 3
     save("act", x=x, silu=SiluAndMul().forward_native(x),
          oai=SwigluOAIAndMul().forward_native(x))
+    from tests.ops.activation_op import GeluAndMul, Relu2NoMul
+    from tests.ops.swiglustep_and_mul_op import SwigluStepAndMul
+    xs = {"bf16": x, "f16": x.to(torch.float16), "f32": x.float()}
+    arrays = {}
+    for tag, xx in xs.items():
+        arrays["x_" + tag] = xx
+        arrays["gelu_" + tag] = GeluAndMul("none").forward_native(xx)
+        arrays["gelu_tanh_" + tag] = GeluAndMul("tanh").forward_native(xx)
+        arrays["relu2_" + tag] = Relu2NoMul.forward_native(None, xx)  # its constructor wants the native op
+        arrays["swiglustep_" + tag] = SwigluStepAndMul().forward_native(xx)
+        # the situ oracle is inline in the reference's test (tests/test_activation.py:98-103)
+        for lb in (-1.0, 2.0):
+            gate, up = xx.float().chunk(2, dim=-1)
+            gate = 1.7 * torch.tanh(gate / 1.7) * torch.sigmoid(gate)
+            if lb > 0:
+                up = lb * torch.tanh(up / lb)
+            arrays[f"situ_{'lin' if lb > 0 else 'raw'}_{tag}"] = (gate * up).to(xx.dtype)
+    save("act_more", **arrays)
     x = torch.randn(16, 512, generator=g) * 2
     q, s = ref_per_block_quant(x, 1, 128)
     save("fp8_group", x=x, q=q, s=s)

@@ -82,6 +82,39 @@ def test_activations_match_reference():
     assert torch.equal(O.swigluoai_and_mul(x).view(torch.int16), g["oai"])
 
 
+def test_other_activations_match_reference():
+    """gelu / gelu_tanh / relu2 / swiglustep / situ restatements against the reference's
+    torch oracles in all three dtypes."""
+    g = load_golden("act_more")
+    for tag, view in (("bf16", as_bf16), ("f16", lambda t: t), ("f32", lambda t: t)):
+        x = view(g["x_" + tag])
+        get = lambda k: view(g[k + "_" + tag])
+        assert torch.equal(O.gelu_and_mul(x), get("gelu"))
+        assert torch.equal(O.gelu_and_mul(x, "tanh"), get("gelu_tanh"))
+        assert torch.equal(O.relu2_no_mul(x), get("relu2"))
+        assert torch.equal(O.situ_and_mul(x, 1.7, -1.0), get("situ_raw"))
+        assert torch.equal(O.situ_and_mul(x, 1.7, 2.0), get("situ_lin"))
+        # the reference's python oracle rounds silu(gate) to the input dtype before the
+        # product; its kernel (and this restatement) keep fp32: a few ulps apart
+        atol, rtol = {"bf16": (1e-3, 1.6e-2), "f16": (1e-3, 1e-3), "f32": (1e-5, 1.3e-6)}[tag]
+        torch.testing.assert_close(O.swiglustep_and_mul(x), get("swiglustep"), atol=atol, rtol=rtol)
+
+
+def test_weight_recipe_restatements_round_trip():
+    """MXFP8 and INT4 quantise -> dequantise stays within half a quantisation step."""
+    g = torch.Generator().manual_seed(4)
+    w = torch.randn(128, 96, generator=g)
+    q, s = O.quant_mxfp8_weight(w)
+    d = O.dequant_expert_weight("mxfp8", q, s)
+    assert ((d - w).abs() <= 2.0 ** -3 * w.abs() + 1e-6).all()
+    q4, s4 = O.quant_int4_weight(w.t().contiguous(), group=32, scale_dtype=torch.float32)
+    d4 = O.dequant_expert_weight("int4", q4, s4)
+    step = s4.repeat_interleave(32, dim=1).t()
+    assert ((d4 - w).abs() <= 0.5 * step + 1e-6).all()
+    assert torch.equal(O.dequant_expert_weight("fp8", w.to(torch.float8_e4m3fn), torch.tensor(0.5)),
+                       w.to(torch.float8_e4m3fn).float() * 0.5)
+
+
 def test_fp8_group_quant_matches_reference():
     g = load_golden("fp8_group")
     # the reference test oracle divides by the scale and has no lower clamp on

@@ -68,6 +68,90 @@ __global__ void __launch_bounds__(256) swigluoai_kernel(T* __restrict__ out,
   }
 }
 
+// ---- the other activations of the fused-MoE layer -----------------------------
+// One kernel for every "act(first half) * second half" flavour, with the optional
+// clamp the layer applies to the first GEMM's output (gate <= limit, |up| <= limit)
+// folded in, so the clamp is not a separate pass over [R, 2d].
+//   SILU, GELU, GELU_TANH  act(gate) is rounded to T before the product (the reference
+//                          evaluates act in T and multiplies in T)
+//   SWIGLUSTEP, SITU       fp32 throughout, one rounding
+//   RELU2_NO_MUL           not gated: out[r, c] = relu(in[r, c])^2 over all `d` columns
+template <typename T>
+__device__ __forceinline__ float gated_act(int act, float g, float u, float p0, float p1) {
+  switch (act) {
+    case B200MOE_ACT_SILU:
+      return round_through<T>(silu_f32(g)) * u;
+    case B200MOE_ACT_GELU:
+      return round_through<T>(g * 0.5f * (1.0f + erff(g * 0.70710678118654752440f))) * u;
+    case B200MOE_ACT_GELU_TANH: {
+      const float inner = 0.79788456080286535588f * (g + 0.044715f * (g * g * g));
+      return round_through<T>(0.5f * g * (1.0f + tanhf(inner))) * u;
+    }
+    case B200MOE_ACT_SWIGLUSTEP: {
+      const float sg = fminf(silu_f32(g), p0);
+      return sg * fmaxf(fminf(u, p0), -p0);
+    }
+    case B200MOE_ACT_SITU: {
+      const float ag = p0 * tanhf(g / p0) / (1.0f + expf(-g));
+      const float au = p1 > 0.0f ? p1 * tanhf(u / p1) : u;
+      return ag * au;
+    }
+    default:
+      return 0.0f;
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256) act_and_mul_kernel(T* __restrict__ out,
+                                                          const T* __restrict__ in, int64_t R,
+                                                          int d, int act, float p0, float p1,
+                                                          float clamp) {
+  const int64_t chunks_per_row = d / V;
+  const int64_t total = R * chunks_per_row;
+  for (int64_t c = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; c < total;
+       c += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = c / chunks_per_row, col = (c % chunks_per_row) * V;
+    float g[V], u[V], o[V];
+    load_f32<T, V>(in + r * 2 * d + col, g);
+    load_f32<T, V>(in + r * 2 * d + d + col, u);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      if (clamp > 0.0f) {
+        g[i] = round_through<T>(fminf(g[i], clamp));
+        u[i] = round_through<T>(fmaxf(fminf(u[i], clamp), -clamp));
+      }
+      o[i] = gated_act<T>(act, g[i], u[i], p0, p1);
+    }
+    store_f32<T, V>(out + r * d + col, o);
+  }
+}
+
+// relu(x)^2 over [R, d]; columns below `split` take the gate clamp, the rest the up clamp.
+template <typename T, int V>
+__global__ void __launch_bounds__(256) relu2_kernel(T* __restrict__ out, const T* __restrict__ in,
+                                                    int64_t R, int d, float clamp, int split) {
+  const int64_t chunks_per_row = d / V;
+  const int64_t total = R * chunks_per_row;
+  for (int64_t c = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; c < total;
+       c += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = c / chunks_per_row, col = (c % chunks_per_row) * V;
+    float x[V], o[V];
+    load_f32<T, V>(in + r * d + col, x);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float v = x[i];
+      if (clamp > 0.0f) {
+        v = fminf(v, clamp);
+        if (col + i >= split) v = fmaxf(v, -clamp);
+        v = round_through<T>(v);
+      }
+      const float rl = v > 0.0f ? v : 0.0f;
+      o[i] = rl * rl;
+    }
+    store_f32<T, V>(out + r * d + col, o);
+  }
+}
+
 // ---- group quantisation ---------------------------------------------------
 
 __device__ __forceinline__ float round_up_pow2(float s) {
@@ -239,6 +323,37 @@ extern "C" int b200moe_swigluoai_and_mul(void* out, const void* in, int dtype, i
     swigluoai_kernel<scalar_t><<<stream_grid(R * d, 256), 256, 0, as_stream(stream)>>>(
         reinterpret_cast<scalar_t*>(out), reinterpret_cast<const scalar_t*>(in), R, d, alpha, limit);
     return launch_status("swigluoai_kernel");
+  });
+}
+
+extern "C" int b200moe_act_and_mul(void* out, const void* in, int dtype, int64_t R, int d, int act,
+                                   float param0, float param1, float clamp_limit, void* stream) {
+  if (R < 0 || d <= 0 || act < B200MOE_ACT_SILU || act > B200MOE_ACT_RELU2_NO_MUL)
+    return B200MOE_INVALID_ARG;
+  if (act == B200MOE_ACT_SITU && !(isfinite(param0) && param0 > 0.0f && isfinite(param1)))
+    return B200MOE_INVALID_ARG;  // beta finite and > 0, linear_beta finite
+  if (R == 0) return B200MOE_OK;
+  if (!out || !in) return B200MOE_INVALID_ARG;
+  const float clamp = clamp_limit > 0.0f ? clamp_limit : 0.0f;
+  return B200MOE_DISPATCH_FLOAT(dtype, [&] {
+    constexpr int V = 16 / sizeof(scalar_t);
+    cudaStream_t st = as_stream(stream);
+    scalar_t* o = reinterpret_cast<scalar_t*>(out);
+    const scalar_t* x = reinterpret_cast<const scalar_t*>(in);
+    if (act == B200MOE_ACT_RELU2_NO_MUL) {
+      if (d % V == 0)
+        relu2_kernel<scalar_t, V><<<stream_grid(R * (d / V), 256), 256, 0, st>>>(o, x, R, d, clamp, d / 2);
+      else
+        relu2_kernel<scalar_t, 1><<<stream_grid(R * d, 256), 256, 0, st>>>(o, x, R, d, clamp, d / 2);
+      return launch_status("relu2_kernel");
+    }
+    if (d % V == 0)
+      act_and_mul_kernel<scalar_t, V><<<stream_grid(R * (d / V), 256), 256, 0, st>>>(
+          o, x, R, d, act, param0, param1, clamp);
+    else
+      act_and_mul_kernel<scalar_t, 1><<<stream_grid(R * d, 256), 256, 0, st>>>(
+          o, x, R, d, act, param0, param1, clamp);
+    return launch_status("act_and_mul_kernel");
   });
 }
 

@@ -386,6 +386,60 @@ void swigluoai_and_mul(Tensor& out, const Tensor& input, double alpha, double li
         "swigluoai_and_mul");
 }
 
+// Shared body of the other activations; `name` prefixes the error texts.
+void act_and_mul_common(Tensor& out, const Tensor& input, int act, double p0, double p1,
+                        double clamp_limit, const char* name) {
+  TORCH_CHECK(input.dim() >= 1, name, " input must have at least one dimension");
+  const bool gated = act != B200MOE_ACT_RELU2_NO_MUL;
+  if (gated)
+    TORCH_CHECK(input.size(-1) > 0 && input.size(-1) % 2 == 0, name,
+                " input last dimension must be positive and even");
+  TORCH_CHECK(input.is_contiguous(), name, " input must be contiguous");
+  TORCH_CHECK(out.is_contiguous(), name, " output must be contiguous");
+  TORCH_CHECK(out.device() == input.device(), name, " input and output must be on the same device");
+  TORCH_CHECK(out.scalar_type() == input.scalar_type(), name,
+              " input and output must have the same dtype");
+  TORCH_CHECK(out.dim() == input.dim(), name,
+              " input and output must have the same number of dimensions");
+  for (int64_t dim = 0; dim < input.dim() - 1; ++dim)
+    TORCH_CHECK(out.size(dim) == input.size(dim), name,
+                " input and output leading dimensions must match");
+  const int64_t d = gated ? input.size(-1) / 2 : input.size(-1);
+  TORCH_CHECK(out.size(-1) == d, name,
+              gated ? " output last dimension must be half the input last dimension"
+                    : " output must have the input's shape");
+  if (input.numel() == 0) return;
+  c10::cuda::CUDAGuard guard(input.device());
+  check(b200moe_act_and_mul(out.data_ptr(), input.data_ptr(), float_code(input, name),
+                            input.numel() / input.size(-1), d, act, static_cast<float>(p0),
+                            static_cast<float>(p1), static_cast<float>(clamp_limit), cur_stream()),
+        name);
+}
+
+void gelu_and_mul(Tensor& out, const Tensor& input) {
+  act_and_mul_common(out, input, B200MOE_ACT_GELU, 0, 0, 0, "gelu_and_mul:");
+}
+void gelu_tanh_and_mul(Tensor& out, const Tensor& input) {
+  act_and_mul_common(out, input, B200MOE_ACT_GELU_TANH, 0, 0, 0, "gelu_tanh_and_mul:");
+}
+void relu2_no_mul(Tensor& out, Tensor& input) {
+  act_and_mul_common(out, input, B200MOE_ACT_RELU2_NO_MUL, 0, 0, 0, "relu2_no_mul:");
+}
+void swiglustep_and_mul(Tensor& out, const Tensor& input, double limit) {
+  act_and_mul_common(out, input, B200MOE_ACT_SWIGLUSTEP, limit, 0, 0, "swiglustep_and_mul:");
+}
+void situ_and_mul(Tensor& out, const Tensor& input, double beta, double linear_beta) {
+  // same argument checks and texts as csrc/activation.cpp:777-780 of the reference
+  TORCH_CHECK(std::isfinite(beta) && beta > 0.0, "SITU beta must be finite and greater than zero");
+  TORCH_CHECK(std::isfinite(linear_beta), "SITU linear_beta must be finite");
+  act_and_mul_common(out, input, B200MOE_ACT_SITU, beta, linear_beta, 0, "SITU");
+}
+// Extended: any of the activations with the layer's gemm1 clamp folded in.
+void b200_act_and_mul(Tensor& out, const Tensor& input, int64_t act, double p0, double p1,
+                      double clamp_limit) {
+  act_and_mul_common(out, input, static_cast<int>(act), p0, p1, clamp_limit, "b200_act_and_mul:");
+}
+
 void scale_strides(const Tensor& s, int64_t rows, int64_t groups, int64_t* sr, int64_t* sg) {
   TORCH_CHECK(s.scalar_type() == at::kFloat, "group quant: scales must be float32");
   TORCH_CHECK(s.numel() == rows * groups, "group quant: scales must have one entry per group");
@@ -617,6 +671,59 @@ Tensor b200_dequant_weights(const Tensor& B, const Tensor& B_scale) {
   return out;
 }
 
+// recipe: "fp8" (per-expert f32 scale [E]), "mxfp8" (u8/e8m0 scale [E,K/32,N]) or "int4"
+// (u8 [E,N,K/2], 16-bit/f32 scale [E,N,K/group]).  out_dtype: bf16 or f16.
+Tensor b200_expand_weights(const Tensor& B, const Tensor& B_scale, const std::string& recipe,
+                           at::ScalarType out_dtype) {
+  TORCH_CHECK(B.dim() == 3 && B.is_contiguous() && B_scale.is_contiguous(),
+              "b200_expand_weights: contiguous [E, ., .] weights expected");
+  TORCH_CHECK(out_dtype == at::kBFloat16 || out_dtype == at::kHalf,
+              "b200_expand_weights: bf16 or f16 output");
+  c10::cuda::CUDAGuard guard(B.device());
+  const int odt = out_dtype == at::kBFloat16 ? B200MOE_BF16 : B200MOE_F16;
+  const int E = B.size(0);
+  Tensor out;
+  int rc;
+  if (recipe == "int4") {
+    TORCH_CHECK(B.scalar_type() == at::kByte, "b200_expand_weights: int4 weights are uint8 pairs");
+    const int N = B.size(1), K = B.size(2) * 2;
+    TORCH_CHECK(B_scale.dim() == 3 && B_scale.size(0) == E && B_scale.size(1) == N && B_scale.size(2) > 0 &&
+                    K % B_scale.size(2) == 0,
+                "b200_expand_weights: int4 scales must be [E, N, K/group]");
+    const int sdt = B_scale.scalar_type() == at::kBFloat16 ? B200MOE_BF16
+                    : B_scale.scalar_type() == at::kHalf   ? B200MOE_F16
+                                                           : B200MOE_F32;
+    TORCH_CHECK(sdt != B200MOE_F32 || B_scale.scalar_type() == at::kFloat,
+                "b200_expand_weights: int4 scales must be bf16, f16 or f32");
+    out = at::empty({E, N, K}, B.options().dtype(out_dtype));
+    rc = b200moe_expand_weights(B200MOE_RECIPE_INT4, B.data_ptr(), B200MOE_U8, B_scale.data_ptr(), sdt,
+                                K / B_scale.size(2), out.data_ptr(), odt, E, N, K, cur_stream());
+  } else {
+    const bool e5 = B.scalar_type() == at::kFloat8_e5m2;
+    TORCH_CHECK(e5 || B.scalar_type() == at::kFloat8_e4m3fn, "b200_expand_weights: FP8 weights expected");
+    const int K = B.size(1), N = B.size(2);
+    out = at::empty({E, K, N}, B.options().dtype(out_dtype));
+    if (recipe == "fp8") {
+      TORCH_CHECK(B_scale.scalar_type() == at::kFloat && B_scale.numel() == E,
+                  "b200_expand_weights: per-tensor FP8 takes one float32 scale per expert");
+      rc = b200moe_expand_weights(B200MOE_RECIPE_FP8_TENSOR, B.data_ptr(), e5 ? B200MOE_E5M2 : B200MOE_E4M3,
+                                  B_scale.data_ptr(), B200MOE_F32, 0, out.data_ptr(), odt, E, N, K,
+                                  cur_stream());
+    } else if (recipe == "mxfp8") {
+      TORCH_CHECK(B_scale.element_size() == 1 && B_scale.dim() == 3 && B_scale.size(1) * 32 == K &&
+                      B_scale.size(2) == N,
+                  "b200_expand_weights: MXFP8 scales must be e8m0 [E, K/32, N]");
+      rc = b200moe_expand_weights(B200MOE_RECIPE_MXFP8, B.data_ptr(), e5 ? B200MOE_E5M2 : B200MOE_E4M3,
+                                  B_scale.data_ptr(), B200MOE_U8, 32, out.data_ptr(), odt, E, N, K,
+                                  cur_stream());
+    } else {
+      TORCH_CHECK(false, "b200_expand_weights: unknown recipe ", recipe);
+    }
+  }
+  check(rc, "b200_expand_weights");
+  return out;
+}
+
 int64_t b200_device_status() {
   int st = 0;
   check(b200moe_device_status(cur_stream(), &st), "b200_device_status");
@@ -679,6 +786,14 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_MOE_C, CUDA, m) {
 TORCH_LIBRARY(B200MOE_NS_C, m) {
   m.def("silu_and_mul(Tensor! result, Tensor input) -> ()");
   m.def("swigluoai_and_mul(Tensor! out, Tensor input, float alpha=1.702, float limit=7.0) -> ()");
+  m.def("gelu_and_mul(Tensor! out, Tensor input) -> ()");
+  m.def("gelu_tanh_and_mul(Tensor! out, Tensor input) -> ()");
+  m.def("situ_and_mul(Tensor! out, Tensor input, float beta=1.0, float linear_beta=-1.0) -> ()");
+  m.def("relu2_no_mul(Tensor! out, Tensor! input) -> ()");
+  m.def("swiglustep_and_mul(Tensor! out, Tensor input, float limit=7.0) -> ()");
+  m.def(
+      "b200_act_and_mul(Tensor! out, Tensor input, int act, float param0=0.0, float param1=0.0, "
+      "float clamp_limit=0.0) -> ()");
   m.def(
       "per_token_group_fp8_quant(Tensor input, Tensor! output_q, Tensor! output_s, int group_size, "
       "float eps, float fp8_min, float fp8_max, bool scale_ue8m0, bool dummy_is_scale_transposed, "
@@ -697,6 +812,12 @@ TORCH_LIBRARY(B200MOE_NS_C, m) {
 TORCH_LIBRARY_IMPL(B200MOE_NS_C, CUDA, m) {
   m.impl("silu_and_mul", &silu_and_mul);
   m.impl("swigluoai_and_mul", &swigluoai_and_mul);
+  m.impl("gelu_and_mul", &gelu_and_mul);
+  m.impl("gelu_tanh_and_mul", &gelu_tanh_and_mul);
+  m.impl("situ_and_mul", &situ_and_mul);
+  m.impl("relu2_no_mul", &relu2_no_mul);
+  m.impl("swiglustep_and_mul", &swiglustep_and_mul);
+  m.impl("b200_act_and_mul", &b200_act_and_mul);
   m.impl("per_token_group_fp8_quant", &per_token_group_fp8_quant);
   m.impl("per_token_group_quant_mxfp4", &per_token_group_quant_mxfp4);
   m.impl("silu_and_mul_per_block_quant", &silu_and_mul_per_block_quant);
@@ -719,6 +840,7 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
       "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "
       "Tensor");
   m.def("b200_dequant_weights(Tensor B, Tensor B_scale) -> Tensor");
+  m.def("b200_expand_weights(Tensor B, Tensor B_scale, str recipe, ScalarType out_dtype) -> Tensor");
   m.def("b200_device_status() -> int");
 }
 
@@ -727,6 +849,7 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CUDA, m) {
   m.impl("b200_grouped_gemm", &b200_grouped_gemm);
   m.impl("b200_grouped_gemm_check", &b200_grouped_gemm_check);
   m.impl("b200_dequant_weights", &b200_dequant_weights);
+  m.impl("b200_expand_weights", &b200_expand_weights);
 }
 
 TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CompositeExplicitAutograd, m) {

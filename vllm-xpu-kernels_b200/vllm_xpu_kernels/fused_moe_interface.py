@@ -25,6 +25,7 @@ Recipes, detected from the weight dtypes as the reference does
   W4A16 arithmetic of the reference kernel.
 """
 import contextlib
+import math
 import os
 from typing import Optional
 
@@ -70,6 +71,11 @@ def _get_recipe(is_fp8, is_mxfp8, is_mxfp4, is_int4, is_block_fp8):
     return "bf16"
 
 
+# activation name -> code of b200_act_and_mul (swigluoai has an op of its own)
+_ACT_CODES = {"silu": 0, "gelu": 1, "gelu_tanh": 2, "swiglustep": 3, "situ": 4, "relu2_no_mul": 5,
+              "swigluoai": -1}
+
+
 def _is_swigluoai(activation) -> bool:
     return activation == "swigluoai" or "SWIGLUOAI" in str(activation)
 
@@ -102,18 +108,31 @@ class XpuFusedMoe:
         self.is_fp8, self.is_int4, self.is_mxfp4, self.is_mxfp8, self.is_block_fp8 = flags
         self.recipe = _get_recipe(self.is_fp8, self.is_mxfp8, self.is_mxfp4, self.is_int4,
                                   self.is_block_fp8)
-        if self.recipe in ("int4", "mxfp8", "fp8"):
-            raise NotImplementedError(
-                f"recipe {self.recipe} is not part of the B200 fused-MoE path "
-                "(supported: bf16/fp16, block-FP8, MXFP4)")
-        if activation != "silu" and not _is_swigluoai(activation):
+        if self.recipe == "mxfp4_fp8":
+            raise NotImplementedError("the mxfp4 x fp8-activation recipe is not part of the B200 path")
+        self._act_code = _ACT_CODES.get("swigluoai" if _is_swigluoai(activation) else activation)
+        if self._act_code is None:
             raise ValueError(f"Unsupported FusedMoe activation: {activation}.")
+        self.activation_situ_beta = activation_situ_beta
+        self.activation_situ_linear_beta = activation_situ_linear_beta
+        if activation == "situ":
+            # same checks and texts as fused_moe_interface.py:253-262 of the reference
+            if activation_situ_beta is None:
+                raise ValueError("SITU requires activation_situ_beta")
+            if not math.isfinite(activation_situ_beta):
+                raise ValueError("SITU activation_situ_beta must be finite")
+            if activation_situ_beta <= 0:
+                raise ValueError("SITU activation_situ_beta must be positive")
+        # relu2_no_mul is not gated: the second GEMM contracts over all 2*inter columns
+        self.inter_size_scale = 2 if activation == "relu2_no_mul" else 1
 
         # 4-bit weights are [E, N, K/2]; everything else is [E, K, N].
-        self.inter_size = (w13.shape[-2] if self.is_mxfp4 else w13.shape[-1]) // 2
+        self.inter_size = (w13.shape[-2] if (self.is_mxfp4 or self.is_int4) else w13.shape[-1]) // 2
         self.w13, self.w2 = w13, w2
         self.gemm1_wei_scales = w13_scales if self.recipe != "bf16" else None
         self.gemm2_wei_scales = w2_scales if self.recipe != "bf16" else None
+        # W8A16 / W4A16 recipes: widened once per activation dtype, on first use
+        self._expanded = {}
         self.w13_bias, self.w2_bias = w13_bias, w2_bias
         self.n_experts_per_token = n_experts_per_token
         self.activation = activation
@@ -229,9 +248,11 @@ class XpuFusedMoe:
         I, E = self.inter_size, self.num_experts
         oai = _is_swigluoai(self.activation)
         gemm = torch.ops._xpu_C.b200_grouped_gemm
+        clamp = self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0
         if self.is_block_fp8:
-            clamp = self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0
-            if not oai and not clamp and I % 128 == 0 and not os.environ.get("B200MOE_UNFUSED_ACT"):
+            K2 = I * self.inter_size_scale
+            if (self.activation == "silu" and not clamp and I % 128 == 0
+                    and not os.environ.get("B200MOE_UNFUSED_ACT")):
                 # SiLU*mul and the group-128 re-quantisation run in the GEMM's epilogue
                 act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
                 act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
@@ -244,47 +265,42 @@ class XpuFusedMoe:
                 with self._stage("gemm1"):
                     gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
                          gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
-                self._clamp(gemm1_out)
-                if oai:
-                    act = torch.empty((R, I), dtype=out_dtype, device=dev)
-                    torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
-                    from .moe_utils import quant_fp8_block_act
-                    act_q, act_s = quant_fp8_block_act(act)
-                else:
-                    act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
-                    act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
-                    with self._stage("act_quant"):
+                act_q = torch.empty((R, K2), dtype=torch.float8_e4m3fn, device=dev)
+                act_s = torch.empty((R, K2 // 128), dtype=torch.float32, device=dev)
+                with self._stage("act_quant"):
+                    if self.activation == "silu" and not clamp:
                         torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
+                    else:
+                        act = self._activate(gemm1_out)
+                        torch.ops._C.per_token_group_fp8_quant(act, act_q, act_s, 128, 1e-10, -448.0,
+                                                               448.0, False, False, False)
             gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=out_dtype,
                                     device=dev)
             with self._stage("gemm2"):
                 gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
-                     rows_per_expert, hidden_size, I, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None,
+                     rows_per_expert, hidden_size, K2, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None,
                      row_ptr)
         else:
-            if self.is_mxfp4:
-                w13, w2, layout = self._w13_16, self._w2_16, B_LAYOUT_NK
-            else:
-                w13, w2, layout = self.w13, self.w2, B_LAYOUT_KN
-            act = torch.empty((R, I), dtype=out_dtype, device=dev)
-            if self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0:
-                gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
-                gemm(remapped, None, w13, None, self.w13_bias, gemm1_out, rows_per_expert, 2 * I,
-                     hidden_size, E, EPI_STORE, layout)
-                self._clamp(gemm1_out)
-                if oai:
-                    torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
-                else:
-                    torch.ops._C.silu_and_mul(act, gemm1_out)
-            else:
+            w13, w2, layout = self._weights_16(out_dtype)
+            K2 = I * self.inter_size_scale
+            fused_epi = (self.activation == "silu" or oai) and not clamp
+            if fused_epi:
+                act = torch.empty((R, I), dtype=out_dtype, device=dev)
                 with self._stage("gemm1"):
                     gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
                          hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702,
                          7.0)
+            else:
+                gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
+                with self._stage("gemm1"):
+                    gemm(remapped, None, w13, None, self.w13_bias, gemm1_out, rows_per_expert,
+                         2 * I, hidden_size, E, EPI_STORE, layout)
+                with self._stage("act"):
+                    act = self._activate(gemm1_out)
             gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=out_dtype,
                                     device=dev)
             with self._stage("gemm2"):
-                gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, I,
+                gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, K2,
                      E, EPI_STORE, layout, 1.702, 7.0, None, row_ptr)
         return gemm2_out
 
@@ -333,9 +349,43 @@ class XpuFusedMoe:
         with self._stage("gather"):
             torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
 
-    def _clamp(self, gemm1_out):
-        lim = self.gemm1_clamp_limit
-        if lim is not None and lim > 0:
-            # first half / second half, as fused_moe_interface.py:436-441 of the reference
-            gemm1_out[:, :self.inter_size].clamp_(max=lim)
-            gemm1_out[:, self.inter_size:].clamp_(min=-lim, max=lim)
+    def _weights_16(self, dtype):
+        """(w13, w2, layout) as 16-bit operands of the grouped GEMM."""
+        if self.recipe == "bf16":
+            return self.w13, self.w2, B_LAYOUT_KN
+        if self.is_mxfp4:
+            return self._w13_16, self._w2_16, B_LAYOUT_NK
+        if dtype not in self._expanded:
+            expand = torch.ops._xpu_C.b200_expand_weights
+            s13, s2 = self.gemm1_wei_scales, self.gemm2_wei_scales
+            if self.recipe == "fp8":
+                s13, s2 = (t.to(torch.float32).reshape(-1).contiguous() for t in (s13, s2))
+            elif self.recipe == "mxfp8":
+                s13, s2 = (t.view(torch.uint8) for t in (s13, s2))
+            self._expanded[dtype] = (expand(self.w13, s13, self.recipe, dtype),
+                                     expand(self.w2, s2, self.recipe, dtype))
+        w13, w2 = self._expanded[dtype]
+        return w13, w2, (B_LAYOUT_NK if self.is_int4 else B_LAYOUT_KN)
+
+    def _activate(self, gemm1_out):
+        """Activation as a pass of its own over the first GEMM's output, with the layer's
+        clamp (gate <= limit, |up| <= limit; fused_moe_interface.py:436-441 of the reference)
+        folded into the same kernel."""
+        R = gemm1_out.shape[0]
+        lim = self.gemm1_clamp_limit if (self.gemm1_clamp_limit or 0) > 0 else 0.0
+        act = torch.empty((R, self.inter_size * self.inter_size_scale), dtype=gemm1_out.dtype,
+                          device=gemm1_out.device)
+        if self._act_code < 0:  # swigluoai: interleaved gate/up, limit of its own
+            if lim:
+                gemm1_out[:, :self.inter_size].clamp_(max=lim)
+                gemm1_out[:, self.inter_size:].clamp_(min=-lim, max=lim)
+            torch.ops._C.swigluoai_and_mul(act, gemm1_out, 1.702, 7.0)
+            return act
+        p0 = p1 = 0.0
+        if self.activation == "swiglustep":
+            p0 = 7.0
+        elif self.activation == "situ":
+            p0 = self.activation_situ_beta
+            p1 = -1.0 if self.activation_situ_linear_beta is None else self.activation_situ_linear_beta
+        torch.ops._C.b200_act_and_mul(act, gemm1_out, self._act_code, p0, p1, lim)
+        return act
