@@ -201,6 +201,24 @@ int b200moe_moe_sum(const void* in, void* out, int dtype, int T, int k, int H,
                     const void* topk_ids, int ids_dtype,
                     const int32_t* expert_map, void* stream);
 
+/* moe_lora_align_block_size (csrc/moe/torch_bindings.cpp:36-50,
+ * csrc/moe/moe_align_sum_kernels.cpp:1374-1549; slot guards :806-812): one
+ * alignment per LoRA adapter slot.  For every entry s of lora_ids[max_loras+1]
+ * that is in [0, max_loras) and has adapter_enabled[s] != 0, the tokens t with
+ * token_lora_mapping[t] == s are grouped by expert exactly like
+ * moe_align_block_size into row s of sorted_token_ids [max_loras,
+ * max_num_tokens_padded] (padding value num_tokens*topk), expert_ids
+ * [max_loras, max_num_m_blocks] (-1 after the last used block) and
+ * num_tokens_post_pad [max_loras].  Rows of other slots are not written.
+ * expert_map, when given, maps the id before grouping (-1 drops the entry). */
+int b200moe_moe_lora_align_block_size(
+    const void* topk_ids, int ids_dtype, int64_t num_tokens, int topk,
+    const int32_t* token_lora_mapping, int num_experts, int block_size,
+    int max_loras, int64_t max_num_tokens_padded, int64_t max_num_m_blocks,
+    int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_pad,
+    const int32_t* adapter_enabled, const int32_t* lora_ids,
+    const int32_t* expert_map, void* stream);
+
 /* ---- gated activations and activation quantisation --------------------- */
 
 /* silu_and_mul (csrc/torch_bindings.cpp:80-81, csrc/activation.cpp:546-553). in [R,2d] -> out [R,d]. */

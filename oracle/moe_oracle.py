@@ -203,6 +203,43 @@ def moe_align_block_size(topk_ids, block_size, num_experts, expert_map=None,
     return sorted_ids, expert_ids, total
 
 
+def moe_lora_align_block_size(topk_ids, token_lora_mapping, num_experts, block_size, max_loras,
+                              max_num_tokens_padded, max_num_m_blocks, sorted_token_ids,
+                              expert_ids, num_tokens_post_pad, adapter_enabled, lora_ids,
+                              expert_map=None):
+    """One alignment per enabled adapter slot, written into that slot's rows of the
+    caller's (pre-filled) flat outputs; other rows stay as they are
+    (csrc/moe/moe_align_sum_kernels.cpp:803-848 for the slot guards and the token mask,
+    :136-277 for the alignment with inactive blocks labelled -1).  With an expert_map the
+    entries are grouped by the mapped id.  Inside an expert the order is ascending flat
+    index (the reference's is whatever its atomics give; its test checks membership only)."""
+    numel = topk_ids.numel()
+    k = topk_ids.shape[1]
+    sorted_token_ids = sorted_token_ids.clone().view(max_loras, -1)
+    expert_ids = expert_ids.clone().view(max_loras, -1)
+    num_tokens_post_pad = num_tokens_post_pad.clone()
+    for s in lora_ids[: max_loras + 1].tolist():
+        if s < 0 or s >= max_loras or int(adapter_enabled[s]) == 0:
+            continue
+        ids = topk_ids.to(torch.int64).clone()
+        if expert_map is not None:
+            ok = (ids >= 0) & (ids < num_experts)
+            mapped = expert_map.to(torch.int64)[ids.clamp(0, num_experts - 1)]
+            ids = torch.where(ok & (mapped >= 0), mapped, torch.full_like(ids, num_experts))
+        ids[token_lora_mapping != s] = num_experts          # ignored by the alignment
+        srt, eid, tot = moe_align_block_size(ids, block_size, num_experts)
+        n = min(srt.numel(), max_num_tokens_padded)
+        row = torch.full((max_num_tokens_padded,), numel, dtype=torch.int32)
+        row[:n] = srt[:n]
+        sorted_token_ids[s, :max_num_tokens_padded] = row
+        used = int(tot) // block_size
+        blocks = torch.full((max_num_m_blocks,), -1, dtype=torch.int32)
+        blocks[:used] = eid[:used]
+        expert_ids[s, :max_num_m_blocks] = blocks
+        num_tokens_post_pad[s] = int(tot)
+    return sorted_token_ids.flatten(), expert_ids.flatten(), num_tokens_post_pad
+
+
 def batched_moe_align_block_size(max_tokens_per_batch, block_size, expert_num_tokens):
     """Batch b owns token slots [b*max, b*max + n_b); runs padded to the block size, sentinel
     B*max, unused blocks -1 (tests/test_moe_align_block_size.py:346-392)."""

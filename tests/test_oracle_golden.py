@@ -115,6 +115,32 @@ def test_weight_recipe_restatements_round_trip():
                        w.to(torch.float8_e4m3fn).float() * 0.5)
 
 
+def test_lora_align_restatement_has_the_reference_test_property():
+    """Every block of every enabled slot holds entries of one expert and of that slot's
+    tokens; a disabled slot keeps the caller's pre-fill."""
+    g = torch.Generator().manual_seed(8)
+    T, k, E, bs, L = 100, 6, 64, 16, 3
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    slot = torch.randint(0, L, (T,), generator=g, dtype=torch.int32)
+    n = (T * k + E * (bs - 1) + bs - 1) // bs * bs
+    nb = n // bs
+    srt = torch.full((L * n,), -7, dtype=torch.int32)
+    eid = torch.full((L * nb,), -2, dtype=torch.int32)
+    npad = torch.full((L,), -13, dtype=torch.int32)
+    enabled = torch.tensor([1, 0, 1, 1], dtype=torch.int32)
+    srt, eid, npad = O.moe_lora_align_block_size(ids, slot, E, bs, L, n, nb, srt, eid, npad, enabled,
+                                                 torch.tensor([0, 1, 2, -1], dtype=torch.int32))
+    srt, eid = srt.view(L, nb, bs), eid.view(L, nb)
+    assert int(npad[1]) == -13 and (srt[1] == -7).all() and (eid[1] == -2).all()
+    for s in (0, 2):
+        real = srt[s] != T * k
+        assert int(real.sum()) == int((slot == s).sum()) * k
+        for b in real.any(1).nonzero().flatten().tolist():
+            idx = srt[s, b][real[b]].long()
+            assert (ids.flatten()[idx] == eid[s, b]).all() and (slot[idx // k] == s).all()
+        assert (eid[s, int(npad[s]) // bs:] == -1).all()
+
+
 def test_fp8_group_quant_matches_reference():
     g = load_golden("fp8_group")
     # the reference test oracle divides by the scale and has no lower clamp on

@@ -36,11 +36,16 @@ struct GroupParams {
   const int32_t* map;  // optional id -> key (remap) or id -> keep? (align)
   int map_is_filter;   // 1: map only decides validity (align); 0: map gives the key (remap)
   int block_size;      // padding unit of each group's run (1 = none)
+  // optional per-token filter (multi-LoRA): only tokens with token_tag[i / topk] == tag count
+  const int32_t* token_tag = nullptr;
+  int tag = 0;
+  int topk = 1;
 };
 
 __device__ __forceinline__ int key_of(const GroupParams& p, int64_t i) {
   const int64_t id = load_index(p.ids, p.ids_dtype, i);
   if (id < 0 || id >= p.id_limit) return -1;
+  if (p.token_tag && p.token_tag[i / p.topk] != p.tag) return -1;
   if (p.map) {
     const int m = p.map[id];
     if (m < 0) return -1;
@@ -162,6 +167,7 @@ struct AlignOut {
   int64_t blocks_capacity;
   int32_t* total;
   const int32_t* expert_map;
+  int32_t tail_label = 0;  // expert_ids value of the blocks after the last used one
 };
 
 __device__ __forceinline__ void write_align_meta(const AlignOut& o, int num_keys, int block_size,
@@ -175,7 +181,7 @@ __device__ __forceinline__ void write_align_meta(const AlignOut& o, int num_keys
       if (b0 + b < o.blocks_capacity) o.expert_ids[b0 + b] = label;
   }
   for (int64_t b = grand_total / block_size + threadIdx.x; b < o.blocks_capacity; b += kThreads)
-    o.expert_ids[b] = 0;
+    o.expert_ids[b] = o.tail_label;
   if (threadIdx.x == 0) o.total[0] = grand_total;
 }
 
@@ -271,6 +277,50 @@ __global__ void __launch_bounds__(kThreads) fused_small_kernel(GroupParams p, Al
       row_map[idx] = pos;
     }
   });
+}
+
+// Multi-LoRA alignment: CTA x handles the adapter slot lora_ids[x] and builds that slot's
+// own (sorted_token_ids, expert_ids, num_tokens_post_pad) from the tokens mapped to it.
+// Slots that are -1, out of range or disabled are left untouched.  One CTA walks the whole
+// index list twice (count, then place chunk by chunk in index order), so the order inside
+// an expert's run is ascending flat index.
+__global__ void __launch_bounds__(kThreads) lora_align_kernel(
+    GroupParams p, const int32_t* __restrict__ lora_ids,
+    const int32_t* __restrict__ adapter_enabled, int max_loras, int32_t* __restrict__ sorted_ids,
+    int64_t max_padded, int32_t* __restrict__ expert_ids, int64_t max_blocks,
+    int32_t* __restrict__ post_pad) {
+  extern __shared__ int smem[];
+  __shared__ int total[kMaxExperts];
+  __shared__ int start[kMaxExperts];
+  __shared__ int grand;
+  const int lora_id = lora_ids[blockIdx.x];
+  if (lora_id < 0 || lora_id >= max_loras || adapter_enabled[lora_id] == 0) return;
+  p.tag = lora_id;
+  int* warp_off = smem;
+  for (int e = threadIdx.x; e < p.num_keys; e += kThreads) total[e] = 0;
+  __syncthreads();
+  for (int64_t i = threadIdx.x; i < p.numel; i += kThreads) {
+    const int key = key_of(p, i);
+    if (key >= 0) atomicAdd(&total[key], 1);
+  }
+  __syncthreads();
+  scan_keys(p.num_keys, p.block_size, total, start, &grand);
+  AlignOut ao{sorted_ids + lora_id * max_padded, max_padded, expert_ids + lora_id * max_blocks,
+              max_blocks, post_pad + lora_id, nullptr, -1};
+  write_align_meta(ao, p.num_keys, p.block_size, total, start, grand);
+  for (int64_t i = threadIdx.x; i < max_padded; i += kThreads)
+    ao.sorted_ids[i] = static_cast<int32_t>(p.numel);
+  __syncthreads();
+  for (int64_t base = 0; base < p.numel; base += kChunk) {
+    chunk_place(p, base, start, warp_off, [&](int64_t idx, int, int pos) {
+      if (pos < max_padded) ao.sorted_ids[pos] = static_cast<int32_t>(idx);
+    });
+    __syncthreads();
+    // the last warp's cursors now stand behind everything this chunk placed
+    for (int e = threadIdx.x; e < p.num_keys; e += kThreads)
+      start[e] = warp_off[(kWarps - 1) * p.num_keys + e];
+    __syncthreads();
+  }
 }
 
 int run_grouping(const GroupParams& p, const AlignOut& ao, int32_t* rows_per_key,
@@ -599,4 +649,26 @@ extern "C" int b200moe_reorder_mxfp_scales(const uint8_t* scales, const int32_t*
   reorder_scales_kernel<<<static_cast<int>(blocks), 256, 0, as_stream(stream)>>>(
       scales, out, rows_per_expert, num_experts, scale_k, total_padded_rows);
   return launch_status("reorder_scales_kernel");
+}
+
+extern "C" int b200moe_moe_lora_align_block_size(
+    const void* topk_ids, int ids_dtype, int64_t num_tokens, int topk,
+    const int32_t* token_lora_mapping, int num_experts, int block_size, int max_loras,
+    int64_t max_num_tokens_padded, int64_t max_num_m_blocks, int32_t* sorted_token_ids,
+    int32_t* expert_ids, int32_t* num_tokens_post_pad, const int32_t* adapter_enabled,
+    const int32_t* lora_ids, const int32_t* expert_map, void* stream) {
+  if (num_tokens < 0 || topk <= 0 || num_experts <= 0 || block_size <= 0 || max_loras <= 0 ||
+      max_num_tokens_padded < 0 || max_num_m_blocks < 0 || !is_index_dtype(ids_dtype) ||
+      !token_lora_mapping || !sorted_token_ids || !expert_ids || !num_tokens_post_pad ||
+      !adapter_enabled || !lora_ids || (num_tokens > 0 && !topk_ids))
+    return B200MOE_INVALID_ARG;
+  if (num_experts > kMaxExperts || num_tokens * topk >= (1ll << 31)) return B200MOE_UNSUPPORTED;
+  GroupParams p{topk_ids, ids_dtype, num_tokens * topk, num_experts, num_experts, expert_map, 0,
+                block_size, token_lora_mapping, 0, topk};
+  // lora_ids has max_loras + 1 entries: the real slots and a possible -1 for base-model tokens
+  lora_align_kernel<<<max_loras + 1, kThreads, num_experts * kWarps * sizeof(int),
+                      as_stream(stream)>>>(p, lora_ids, adapter_enabled, max_loras,
+                                           sorted_token_ids, max_num_tokens_padded, expert_ids,
+                                           max_num_m_blocks, num_tokens_post_pad);
+  return launch_status("lora_align_kernel");
 }

@@ -238,6 +238,40 @@ void batched_moe_align_block_size(int64_t max_tokens_per_batch, int64_t block_si
         "batched_moe_align_block_size");
 }
 
+void moe_lora_align_block_size(const Tensor& topk_ids, const Tensor& token_lora_mapping,
+                               int64_t num_experts, int64_t block_size, int64_t max_loras,
+                               int64_t max_num_tokens_padded, int64_t max_num_m_blocks,
+                               Tensor& sorted_token_ids, Tensor& expert_ids,
+                               Tensor& num_tokens_post_pad, Tensor& adapter_enabled,
+                               Tensor& lora_ids, const std::optional<Tensor>& maybe_expert_map) {
+  const char* op = "moe_lora_align_block_size";
+  TORCH_CHECK(block_size > 0, "block_size should be greater than 0. ");
+  TORCH_CHECK(topk_ids.dim() == 2 && topk_ids.is_contiguous(), op, ": topk_ids must be contiguous [T, k]");
+  TORCH_CHECK(num_experts <= 1024, op, ": at most 1024 experts");
+  const Tensor* int_tensors[] = {&token_lora_mapping, &sorted_token_ids, &expert_ids,
+                                 &num_tokens_post_pad, &adapter_enabled, &lora_ids};
+  for (const Tensor* t : int_tensors)
+    TORCH_CHECK(t->scalar_type() == at::kInt && t->is_contiguous(), op, ": int32 contiguous tensors expected");
+  TORCH_CHECK(token_lora_mapping.numel() == topk_ids.size(0), op, ": one adapter slot per token");
+  TORCH_CHECK(sorted_token_ids.numel() >= max_loras * max_num_tokens_padded &&
+                  expert_ids.numel() >= max_loras * max_num_m_blocks &&
+                  num_tokens_post_pad.numel() >= max_loras && adapter_enabled.numel() >= max_loras &&
+                  lora_ids.numel() >= max_loras + 1,
+              op, ": output / slot tensors are too small for max_loras");
+  if (maybe_expert_map)
+    TORCH_CHECK(maybe_expert_map->scalar_type() == at::kInt && maybe_expert_map->numel() >= num_experts,
+                op, ": expert_map must be int32 [num_experts]");
+  c10::cuda::CUDAGuard guard(topk_ids.device());
+  check(b200moe_moe_lora_align_block_size(
+            topk_ids.data_ptr(), index_code(topk_ids, op), topk_ids.size(0), topk_ids.size(1),
+            token_lora_mapping.data_ptr<int>(), num_experts, block_size, max_loras,
+            max_num_tokens_padded, max_num_m_blocks, sorted_token_ids.data_ptr<int>(),
+            expert_ids.data_ptr<int>(), num_tokens_post_pad.data_ptr<int>(),
+            adapter_enabled.data_ptr<int>(), lora_ids.data_ptr<int>(),
+            reinterpret_cast<const int32_t*>(opt_ptr(maybe_expert_map)), cur_stream()),
+        op);
+}
+
 Tensor reorder_mxfp_scales(const Tensor& A_scales, const Tensor& rows_per_expert,
                            int64_t total_padded_rows) {
   TORCH_CHECK(A_scales.dim() == 2, "A_scales must be 2D [total_rows, scale_k]");
@@ -753,6 +787,11 @@ TORCH_LIBRARY(B200MOE_NS_MOE_C, m) {
       "unpermuted_row_to_permuted_row, int num_experts) -> ()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
   m.def(
+      "moe_lora_align_block_size(Tensor topk_ids, Tensor token_lora_mapping, int num_experts, int "
+      "block_size, int max_loras, int max_num_tokens_padded, int max_num_m_blocks, Tensor! "
+      "sorted_token_ids, Tensor! experts_ids, Tensor! num_tokens_post_pad, Tensor! adapter_enabled, "
+      "Tensor! lora_ids, Tensor? maybe_expert_map) -> ()");
+  m.def(
       "batched_moe_align_block_size(int max_tokens_per_batch, int block_size, Tensor "
       "expert_num_tokens, Tensor! sorted_token_ids, Tensor! experts_ids, Tensor! "
       "num_tokens_post_pad) -> ()");
@@ -778,6 +817,7 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_MOE_C, CUDA, m) {
   m.impl("moe_gather", &moe_gather);
   m.impl("init_expert_map", &init_expert_map);
   m.impl("batched_moe_align_block_size", &batched_moe_align_block_size);
+  m.impl("moe_lora_align_block_size", &moe_lora_align_block_size);
   m.impl("topk_softplus_sqrt", &topk_softplus_sqrt);
   m.impl("reorder_mxfp_scales", &reorder_mxfp_scales);
   m.impl("remap_hidden_states", &remap_hidden_states);

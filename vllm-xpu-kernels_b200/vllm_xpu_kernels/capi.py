@@ -56,6 +56,10 @@ SIGNATURES = {
                                    c_int, c_void_p]),
     "b200moe_moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                 c_void_p, c_void_p]),
+    "b200moe_moe_lora_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int,
+                                                  c_int, c_int, c_int64, c_int64, c_void_p,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p,
+                                                  c_void_p, c_void_p]),
     "b200moe_act_and_mul": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_float,
                                     c_float, c_float, c_void_p]),
     "b200moe_expand_weights": (c_int, [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
