@@ -233,6 +233,25 @@ class Layer:
         return 1 + (1 if self.cfg["recipe"] == "fp8block" else 0) + self.moe.launches_per_apply(self.T)
 
 
+def same_dtype_probe(dev, n=8192, iters=10):
+    """TFLOP/s of one unscaled e4m3 x e4m3 GEMM of n^3 on the library's own tcgen05 pipeline."""
+    a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+    b = torch.randn(1, n, n, device=dev).to(torch.float8_e4m3fn)
+    d = torch.empty(n, n, dtype=torch.bfloat16, device=dev)
+    rows = torch.tensor([n], dtype=torch.int32, device=dev)
+    run = lambda: torch.ops._xpu_C.b200_grouped_gemm(a, None, b, None, None, d, rows, n, n, 1, 0, 0)
+    for _ in range(3):
+        run()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    for _ in range(iters):
+        run()
+    e.record()
+    torch.cuda.synchronize()
+    return 2.0 * n ** 3 / (s.elapsed_time(e) / iters * 1e-3) / 1e12
+
+
 def flops_per_token(cfg):
     return 6.0 * cfg["k"] * cfg["H"] * cfg["I"]
 
@@ -367,6 +386,15 @@ def main():
     with ClockSampler(local) as clk:
         ms = timed_region(lambda: layer.step(x, logits), args.steps)
 
+        # the same step sequence once more with an event pair around every stage: the
+        # dominant kernel's own duration, under the conditions of the timed region above
+        layer.moe.stage_timer = gemm_ms
+        for _ in range(args.steps):
+            flush.fill_(1)
+            layer.step(x, logits)
+        torch.cuda.synchronize()
+        layer.moe.stage_timer = None
+
         def e2e_region(steps):
             """K steps through the public calls from pinned host buffers: each step's x and
             logits are copied in, its [T, H] result is copied out.  Copies run on their own
@@ -411,13 +439,6 @@ def main():
         e2e_region(2)
         ms_e2e = e2e_region(args.steps)
 
-        # the dominant kernel alone, inside the same step sequence
-        layer.moe.stage_timer = gemm_ms
-        for _ in range(args.steps):
-            flush.fill_(1)
-            layer.step(x, logits)
-        torch.cuda.synchronize()
-        layer.moe.stage_timer = None
     gemm1 = [s.elapsed_time(e) for name, s, e in gemm_ms if name == "gemm1"]
     gemm1_ms = sum(gemm1) / max(len(gemm1), 1)
     stages = {}
@@ -472,6 +493,16 @@ def main():
             "clocks": clk.summary(),
             "stages_ms": stages, "active_experts": active,
         }
+        nominal = 4500.0 if fp8 else 2250.0   # dense TFLOP/s of the part's data sheet
+        line["roofline"]["frac_of_nominal"] = achieved / nominal
+        line["roofline"]["nominal_peak"] = nominal
+        if fp8 and world == 1 and not decode:
+            # Same-dtype ceiling measured in this run: one plain e4m3 x e4m3 problem of 8192^3
+            # (unit scales, so no per-K-block promotion) through the same kernel family.
+            probe = same_dtype_probe(dev)
+            line["roofline"]["same_dtype_probe"] = {
+                "tflops": probe, "what": "plain tcgen05 e4m3 GEMM, M=N=K=8192, unit scales, bf16 out"}
+            line["roofline"]["frac_of_probe"] = achieved / probe if probe > 0 else None
         if decode and gemm1_ms > 0:
             gbs = gemm1_bytes / (gemm1_ms * 1e-3) / 1e9
             line["roofline"] = {"bound": "hbm", "kernel": "grouped_gemm_kernel (w13), weight streaming",

@@ -42,6 +42,8 @@ extern "C" {
 /* weight recipes of the grouped GEMM */
 #define B200MOE_RECIPE_BF16 0     /* B [E,K,N] bf16/f16, no scales                     */
 #define B200MOE_RECIPE_FP8_BLOCK 1 /* B [E,K,N] e4m3, scales f32 [E,K/128,N/128]        */
+                                   /* (a_scale and b_scale both NULL: unit scales, a plain
+                                      e4m3 x e4m3 contraction; store epilogue only)      */
 #define B200MOE_RECIPE_MXFP4 2    /* B [E,N,K/2] e2m1x2, scales e8m0 u8 [E,N,K/32]     */
 /* 16-bit-activation recipes, taken by b200moe_expand_weights only: */
 #define B200MOE_RECIPE_FP8_TENSOR 3 /* B [E,K,N] e4m3|e5m2, one f32 scale per expert [E] */

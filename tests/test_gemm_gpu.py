@@ -118,6 +118,27 @@ def test_fp8_block(ops, E, avg, K, N):
     close(D, ref)
 
 
+@pytest.mark.parametrize("pair", ["0", "1"])
+@pytest.mark.parametrize("E,avg,K,N", [(1, 300, 512, 256), (3, 700, 1024, 512)])
+def test_fp8_unit_scales(ops, E, avg, K, N, pair, monkeypatch):
+    """No scales at all: the plain e4m3 x e4m3 contraction (one accumulation phase per tile)
+    that the benchmark uses as its same-dtype ceiling.  Exact products, fp32 sums."""
+    monkeypatch.setenv("B200MOE_PAIR", pair)
+    monkeypatch.setenv("B200MOE_TILE_N", "256")
+    rows = ragged_rows(E, avg, K)
+    if int(rows.sum()) == 0:
+        rows[0] = 1
+    R = int(rows.sum())
+    g = torch.Generator().manual_seed(K)
+    A = torch.randn(R, K, generator=g).to(torch.float8_e4m3fn)
+    B = (torch.randn(E, K, N, generator=g) / K ** 0.5).to(torch.float8_e4m3fn)
+    ref = O.grouped_gemm("bf16", A.float(), B.float(), None, None, rows, torch.float32)
+    D = torch.zeros(R, N, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(A.to(DEV), None, B.to(DEV), None, None, D, rows.to(DEV), N, K, E,
+                                 EPI_STORE, KN)
+    close(D, ref)
+
+
 @pytest.mark.parametrize("tile_n,pair", [("128", "0"), ("256", "0"), ("256", "1")])
 @pytest.mark.parametrize("kind", ["bf16_kn", "bf16_nk", "fp8"])
 def test_every_tile_shape(ops, tile_n, pair, kind, monkeypatch):

@@ -994,6 +994,14 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   const bool pair = want_pair(a, wide);
 
   if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR) return grouped_gemm_decode(a, st);
+  if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3 && !a.a_scale && !a.b_scale) {
+    // Unit scales: a plain e4m3 x e4m3 contraction with one accumulation phase per tile.
+    // No recipe of the layer uses it; it is the same-dtype ceiling the block-scaled
+    // kernel is measured against.
+    if (a.K % 128 || a.N % 128 || quant_out || a.epilogue != B200MOE_EPI_STORE) return B200MOE_UNSUPPORTED;
+    if (pair) return launch_config<Config<KIND_F8, true, false, 256, B200MOE_EPI_STORE, 6, true>>(a, a.B, B200MOE_E4M3, st);
+    return launch_config<Config<KIND_F8, true, false, 256, B200MOE_EPI_STORE, 4>>(a, a.B, B200MOE_E4M3, st);
+  }
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3) {
     if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
     if (a.K / 128 > kMaxKBlocks) return B200MOE_UNSUPPORTED;

@@ -606,7 +606,12 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
   a.alpha = static_cast<float>(alpha);
   a.limit = static_cast<float>(limit);
   const auto bt = B.scalar_type();
-  if (bt == at::kFloat8_e4m3fn) {
+  if (bt == at::kFloat8_e4m3fn && !B_scale.has_value() && !A_scale.has_value() &&
+      a.a_dtype == B200MOE_E4M3) {
+    // unit scales: the plain e4m3 x e4m3 contraction (throughput probe of the extended op)
+    TORCH_CHECK(K % 128 == 0 && N % 128 == 0, op, ": FP8 needs K and N to be multiples of 128");
+    a.recipe = B200MOE_RECIPE_FP8_BLOCK;
+  } else if (bt == at::kFloat8_e4m3fn) {
     TORCH_CHECK(B_scale.has_value() && B_scale->scalar_type() == at::kFloat && B_scale->dim() == 3,
                 op, ": float8 weights need float32 block scales [E, K/128, N/128]");
     TORCH_CHECK(B_scale->is_contiguous(), op, ": weight scales must be contiguous");
