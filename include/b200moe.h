@@ -393,12 +393,44 @@ int b200moe_ep_push(const void* send_rows, const void* send_scales, int64_t num_
                     int64_t rows_offset, int64_t scales_offset, int64_t meta_offset,
                     int64_t capacity, void* stream);
 
+/* The same placement straight from the token-major inputs, without a local
+ * copy grouped by expert: for every (token t, slot s) with row_map[t,s] = i >= 0
+ * and expert e = topk_ids[t,s], row t of `hidden` (and of `scales`) goes to row
+ * dst_start[e] + (i - my_prefix[e]) of e's owner.  row_map and the per-expert
+ * counts behind my_prefix come from b200moe_remap_hidden_states called with
+ * hidden = NULL.  Rows travel as bulk asynchronous copies. */
+int b200moe_ep_dispatch(const void* hidden, const void* scales, int64_t row_bytes,
+                        int64_t scale_row_bytes, const void* topk_ids, int ids_dtype,
+                        const int32_t* row_map, int num_tokens, int topk, int my_rank,
+                        int world, int experts_per_rank, const int32_t* my_prefix,
+                        const int32_t* dst_start, const int64_t* peer_bases_host,
+                        int64_t rows_offset, int64_t scales_offset, int64_t meta_offset,
+                        int64_t capacity, void* stream);
+
 /* dst_addr[j] = address, in the return buffer of the rank that sent received row
  * j, of the row it came from; feed it to b200moe_gemm_args.d_row_ptr of the
  * second grouped GEMM. */
 int b200moe_ep_return_table(const int64_t* meta, const int32_t* recv_total, int world,
                             const int64_t* peer_bases_host, int64_t return_offset,
                             int64_t row_bytes, int64_t* dst_addr, void* stream);
+
+/* The other way round ("pull" combine): src_addr[i] = address, in the output
+ * buffer of the rank that owns send row i's expert, where that rank's second
+ * grouped GEMM leaves the row's result (row j of the buffer at out_offset, j as
+ * in b200moe_ep_push; 0 if j is beyond capacity). */
+int b200moe_ep_source_table(const int32_t* my_prefix, const int32_t* dst_start,
+                            int64_t num_rows, int world, int experts_per_rank,
+                            const int64_t* peer_bases_host, int64_t out_offset,
+                            int64_t row_bytes, int64_t capacity, int64_t* src_addr,
+                            void* stream);
+
+/* moe_gather (csrc/moe/torch_bindings.cpp:81-85) over rows that live in peers'
+ * memory: out[t] = sum_j weights[t,j] * row at src_addr[row_map[t,j]], fp32
+ * accumulation in slot order, entries with row_map < 0 or a null address
+ * skipped.  Call after a barrier that follows every rank's second GEMM. */
+int b200moe_ep_gather(void* out, int dtype, const float* weights,
+                      const int32_t* row_map, const int64_t* src_addr, int T, int k,
+                      int H, void* stream);
 
 #ifdef __cplusplus
 }

@@ -35,11 +35,12 @@ def _worker(rank, world, port, recipe, backend, result):
     d = lambda t: None if t is None else t[sl].to(dev)  # noqa: E731
     moe = XpuFusedMoe(d(layer["w13"]), d(layer["w13_scale"]), None, d(layer["w2"]), d(layer["w2_scale"]),
                       None, cfg["k"], "silu", per)
-    if backend == "peer":
+    if backend.startswith("peer"):
         from vllm_xpu_kernels.ep import PeerExpertParallel
         fp8 = recipe == "fp8block"
         ep = PeerExpertParallel(dist.group.WORLD, moe, cfg["T"], cfg["k"], cfg["H"],
-                                cfg["H"] * (1 if fp8 else 2), (cfg["H"] // 128) * 4 if fp8 else 0, per, dev)
+                                cfg["H"] * (1 if fp8 else 2), (cfg["H"] // 128) * 4 if fp8 else 0, per, dev,
+                                combine=backend.split("-")[1])
     else:
         ep = ExpertParallel(dist.group.WORLD, per, make_local_fn(moe))
     ok = True
@@ -64,14 +65,16 @@ def _worker(rank, world, port, recipe, backend, result):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("backend", ["nccl", "peer"])
+@pytest.mark.parametrize("backend", ["nccl", "peer-pull", "peer-push"])
 @pytest.mark.parametrize("recipe", ["bf16", "fp8block"])
 def test_expert_parallel_two_gpus(recipe, backend):
-    """backend 'nccl': all-to-all-v through torch.distributed; 'peer': this library's kernels
-    storing into the other GPU's memory, the second GEMM's epilogue included."""
+    """backend 'nccl': all-to-all-v through torch.distributed; 'peer-*': this library's kernels
+    storing into the other GPU's memory for the dispatch, and for the combine either the
+    token's owner reading the result rows from the peers ('pull') or the second GEMM's
+    epilogue storing them into the sender's memory ('push')."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    port = 29621 + 2 * (recipe != "bf16") + (backend == "peer")
+    port = 29621 + 3 * (recipe != "bf16") + ["nccl", "peer-pull", "peer-push"].index(backend)
     with mp.Manager() as m:
         result = m.dict()
         mp.spawn(_worker, args=(2, port, recipe, backend, result), nprocs=2, join=True)

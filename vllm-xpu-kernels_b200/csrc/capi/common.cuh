@@ -15,6 +15,9 @@ namespace b200moe {
 constexpr int kNumSMs = 148;  // B200: two dies of 74 SMs
 
 void set_last_error(const char* what, cudaError_t err);
+// Device address of the status word that kernels raise when a bounded wait runs out
+// (read and cleared by b200moe_device_status); null if it cannot be resolved.
+int* device_status_word();
 
 // Checks the launch that was just enqueued and maps a failure to a status.
 inline int launch_status(const char* what) {

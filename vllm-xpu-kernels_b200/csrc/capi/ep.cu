@@ -18,7 +18,14 @@
 //                                                         (then a device barrier)
 //   return_table (rank, row) of every received row -> the address of that row
 //                in the sender's return buffer; the second grouped GEMM takes
-//                this table and its epilogue stores straight to the peers.
+//                this table and its epilogue stores straight to the peers
+//                ("push" combine), or
+//   source_table for every row I sent, the address its result will have in the
+//                owner's output buffer, and
+//   gather       out[t] = sum_j w[t,j] * row at source_table[row_map[t,j]]: the
+//                token's owner reads the k result rows from the peers and does
+//                the weighted sum in the same pass ("pull" combine; the
+//                second GEMM then stores locally at full speed).
 //
 // The receive buffer is already in the order the grouped GEMM wants, so the
 // receiving side runs no permutation at all.
@@ -26,6 +33,7 @@
 // The barriers between the steps are issued by the caller on the same stream.
 // Every kernel here only writes; nothing spins on remote data.
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace b200moe {
 namespace {
@@ -132,6 +140,234 @@ __global__ void ep_return_table_kernel(const int64_t* __restrict__ meta,
   }
 }
 
+// Where the result of each of my send rows will sit: row i goes to expert e's owner at
+// row j of its receive buffer (the same arithmetic as the push), and the owner's second
+// GEMM leaves the result at row j of its output buffer.
+__global__ void ep_source_table_kernel(const int32_t* __restrict__ my_prefix,
+                                       const int32_t* __restrict__ dst_start, int E, int E_loc,
+                                       PeerPtrs peers, int64_t out_off, int64_t row_bytes,
+                                       int64_t capacity, int64_t* __restrict__ src_addr) {
+  const int64_t total = my_prefix[E];
+  for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    int lo = 0, hi = E;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (my_prefix[mid] <= i) lo = mid; else hi = mid;
+    }
+    const int64_t j = dst_start[lo] + (i - my_prefix[lo]);
+    src_addr[i] = j < capacity ? reinterpret_cast<int64_t>(peers.base[lo / E_loc] + out_off + j * row_bytes)
+                               : 0;
+  }
+}
+
+// One CTA per token.  The k source rows live in other GPUs' memory: each thread first issues
+// the 16-byte loads of up to 8 rows, then accumulates them in slot order (fp32), so that
+// several NVLink round trips are in flight per thread.  Sum order and rounding are those of
+// moe_gather.
+template <typename T>
+__global__ void __launch_bounds__(256) ep_gather_kernel(T* __restrict__ out,
+                                                        const float* __restrict__ weights,
+                                                        const int32_t* __restrict__ row_map,
+                                                        const int64_t* __restrict__ src_addr, int k,
+                                                        int H) {
+  constexpr int V = 16 / sizeof(T);
+  constexpr int kBatch = 8;
+  constexpr int kMaxTopK = 64;
+  const int64_t t = blockIdx.x;
+  __shared__ const T* rows[kMaxTopK];
+  __shared__ float w[kMaxTopK];
+  for (int j = threadIdx.x; j < k; j += blockDim.x) {
+    const int r = row_map[t * k + j];
+    rows[j] = r < 0 ? nullptr : reinterpret_cast<const T*>(src_addr[r]);
+    w[j] = weights[t * k + j];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
+    float acc[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    for (int j0 = 0; j0 < k; j0 += kBatch) {
+      Vec<T, V> raw[kBatch];
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const T* p = j0 + b < k ? rows[j0 + b] : nullptr;
+        if (p) raw[b] = *reinterpret_cast<const Vec<T, V>*>(p + c);
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        if (j0 + b < k && rows[j0 + b]) {
+          const float wj = w[j0 + b];
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] += wj * Elem<T>::to_f32(raw[b].v[i]);
+        }
+      }
+    }
+    store_f32<T, V>(out + t * H + c, acc);
+  }
+}
+
+// The same sum with the rows brought over by bulk async copies (TMA, no tensor map, no
+// multicast): thread 0 issues one copy per source row -- a few KB each, which crosses
+// NVLink as full-size requests -- into a two-stage shared-memory ring; all threads then add
+// the k staged rows.  A work item is (token, column chunk); CTAs are persistent.  Every wait
+// is bounded: on a timeout the CTA raises the status word and leaves after giving copies in
+// flight time to land.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          sm100::smem_u32(smem_dst)),
+      "l"(gsrc), "r"(bytes), "r"(sm100::smem_u32(bar))
+      : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) ep_gather_bulk_kernel(
+    T* __restrict__ out, const float* __restrict__ weights, const int32_t* __restrict__ row_map,
+    const int64_t* __restrict__ src_addr, int num_tokens, int k, int H, int chunk_elems,
+    int n_chunks, int* __restrict__ status) {
+  constexpr int V = 16 / sizeof(T);
+  extern __shared__ __align__(128) uint8_t stage_smem[];
+  __shared__ uint64_t full[2];
+  __shared__ float w_s[2][64];
+  __shared__ int ok_s[2][64];
+  __shared__ int abort_flag;
+  const int chunk_bytes = chunk_elems * static_cast<int>(sizeof(T));
+  const int64_t items = static_cast<int64_t>(num_tokens) * n_chunks;
+  if (threadIdx.x == 0) {
+    sm100::mbar_init(&full[0], 1);
+    sm100::mbar_init(&full[1], 1);
+    sm100::mbar_fence_init();
+    abort_flag = 0;
+  }
+  __syncthreads();
+
+  auto issue = [&](int64_t item, int s) {  // thread 0 only
+    const int64_t t = item / n_chunks;
+    const int col0 = static_cast<int>(item % n_chunks) * chunk_elems;
+    const int cols = H - col0 < chunk_elems ? H - col0 : chunk_elems;
+    const uint32_t bytes = static_cast<uint32_t>(cols) * sizeof(T);
+    int valid = 0;
+    for (int j = 0; j < k; ++j) {
+      const int r = row_map[t * k + j];
+      const int64_t a = r < 0 ? 0 : src_addr[r];
+      ok_s[s][j] = a != 0;
+      w_s[s][j] = weights[t * k + j];
+      valid += a != 0;
+    }
+    sm100::mbar_arrive_expect_tx(&full[s], valid * bytes);
+    for (int j = 0; j < k; ++j) {
+      if (!ok_s[s][j]) continue;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(src_addr[row_map[t * k + j]]) +
+                           static_cast<int64_t>(col0) * sizeof(T);
+      bulk_load(stage_smem + (static_cast<size_t>(s) * k + j) * chunk_bytes, src, bytes, &full[s]);
+    }
+  };
+
+  int64_t item = blockIdx.x;
+  if (threadIdx.x == 0 && item < items) issue(item, 0);
+  __syncthreads();
+  for (int i = 0; item < items; ++i, item += gridDim.x) {
+    const int s = i & 1;
+    if (threadIdx.x == 0 && item + gridDim.x < items) issue(item + gridDim.x, s ^ 1);
+    const bool got = sm100::mbar_wait(&full[s], (i >> 1) & 1, &abort_flag);
+    if (__syncthreads_or(!got)) {
+      if (threadIdx.x == 0) atomicExch(status, B200MOE_TIMEOUT);
+      for (int n = 0; n < 64; ++n) __nanosleep(10000);  // let copies in flight land
+      break;
+    }
+    const int64_t t = item / n_chunks;
+    const int col0 = static_cast<int>(item % n_chunks) * chunk_elems;
+    const int cols = H - col0 < chunk_elems ? H - col0 : chunk_elems;
+    const uint8_t* base = stage_smem + static_cast<size_t>(s) * k * chunk_bytes;
+    for (int c = threadIdx.x * V; c < cols; c += blockDim.x * V) {
+      float acc[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[e] = 0.f;
+      for (int j = 0; j < k; ++j) {
+        if (!ok_s[s][j]) continue;
+        const Vec<T, V> raw = *reinterpret_cast<const Vec<T, V>*>(
+            base + static_cast<size_t>(j) * chunk_bytes + static_cast<size_t>(c) * sizeof(T));
+        const float wj = w_s[s][j];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] += wj * Elem<T>::to_f32(raw.v[e]);
+      }
+      store_f32<T, V>(out + t * H + col0 + c, acc);
+    }
+    __syncthreads();  // stage s may be refilled from the next iteration on
+  }
+}
+
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst),
+               "r"(sm100::smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
+// Dispatch without a local staging copy: one warp per (token, slot) pair.  Lane 0 brings the
+// token's row (and its scales) into shared memory with one bulk async copy from local HBM --
+// the k copies of a token hit L2 -- and sends it to its place in the owner's expert-grouped
+// receive buffer with one bulk async store, so a row crosses NVLink as a few full-size
+// writes.  Up to ~30 such warps are resident per SM, each with one row in flight.
+__global__ void __launch_bounds__(32) ep_dispatch_bulk_kernel(
+    const uint8_t* __restrict__ hidden, const uint8_t* __restrict__ scales, int64_t row_bytes,
+    int64_t scale_bytes, const void* __restrict__ ids, int ids_dtype,
+    const int32_t* __restrict__ row_map, int64_t pairs, int k, int E_loc, int me,
+    const int32_t* __restrict__ my_prefix, const int32_t* __restrict__ dst_start, PeerPtrs peers,
+    int64_t rows_off, int64_t scales_off, int64_t meta_off, int64_t capacity,
+    int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t row_smem[];
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  const int lane = threadIdx.x;
+  if (lane == 0) {
+    sm100::mbar_init(&bar, 1);
+    sm100::mbar_fence_init();
+    abort_flag = 0;
+  }
+  __syncwarp();
+  const bool bulk_scales = scales && scale_bytes % 16 == 0;
+  uint32_t parity = 0;
+  for (int64_t p = blockIdx.x; p < pairs; p += gridDim.x) {
+    const int i = row_map[p];
+    if (i < 0) continue;
+    const int e = static_cast<int>(load_index(ids, ids_dtype, p));
+    const int64_t j = dst_start[e] + (i - my_prefix[e]);
+    if (j >= capacity) continue;  // cannot happen with a worst-case capacity
+    const int64_t t = p / k;
+    uint8_t* peer = peers.base[e / E_loc];
+    if (lane == 0) {
+      const uint32_t total = static_cast<uint32_t>(row_bytes + (bulk_scales ? scale_bytes : 0));
+      sm100::mbar_arrive_expect_tx(&bar, total);
+      bulk_load(row_smem, hidden + t * row_bytes, static_cast<uint32_t>(row_bytes), &bar);
+      if (bulk_scales)
+        bulk_load(row_smem + row_bytes, scales + t * scale_bytes, static_cast<uint32_t>(scale_bytes), &bar);
+      if (!sm100::mbar_wait(&bar, parity, &abort_flag)) {
+        atomicExch(status, B200MOE_TIMEOUT);
+        for (int n = 0; n < 64; ++n) __nanosleep(10000);  // let the copies in flight land
+      } else {
+        bulk_store(peer + rows_off + j * row_bytes, row_smem, static_cast<uint32_t>(row_bytes));
+        if (bulk_scales)
+          bulk_store(peer + scales_off + j * scale_bytes, row_smem + row_bytes,
+                     static_cast<uint32_t>(scale_bytes));
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        reinterpret_cast<int64_t*>(peer + meta_off)[j] = (static_cast<int64_t>(me) << 32) | i;
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the buffer is free again
+      }
+    }
+    parity ^= 1u;
+    __syncwarp();
+    if (abort_flag) return;
+    if (scales && !bulk_scales) {  // ragged scale rows: plain 4-byte stores
+      const uint32_t* ss = reinterpret_cast<const uint32_t*>(scales + t * scale_bytes);
+      uint32_t* ds = reinterpret_cast<uint32_t*>(peer + scales_off + j * scale_bytes);
+      for (int64_t v = lane; v < scale_bytes / 4; v += 32) ds[v] = ss[v];
+    }
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 bool load_peers(const int64_t* peer_bases_host, int G, PeerPtrs* out) {
   if (!peer_bases_host || G <= 0 || G > kMaxRanks) return false;
   for (int i = 0; i < kMaxRanks; ++i)
@@ -195,4 +431,108 @@ extern "C" int b200moe_ep_return_table(const int64_t* meta, const int32_t* recv_
   ep_return_table_kernel<<<kNumSMs, 256, 0, as_stream(stream)>>>(meta, recv_total, peers,
                                                                  return_offset, row_bytes, dst_addr);
   return launch_status("ep_return_table_kernel");
+}
+
+extern "C" int b200moe_ep_source_table(const int32_t* my_prefix, const int32_t* dst_start,
+                                       int64_t num_rows, int world, int experts_per_rank,
+                                       const int64_t* peer_bases_host, int64_t out_offset,
+                                       int64_t row_bytes, int64_t capacity, int64_t* src_addr,
+                                       void* stream) {
+  PeerPtrs peers;
+  if (!my_prefix || !dst_start || !src_addr || !load_peers(peer_bases_host, world, &peers) ||
+      experts_per_rank <= 0 || num_rows < 0 || row_bytes <= 0)
+    return B200MOE_INVALID_ARG;
+  if (num_rows == 0) return B200MOE_OK;
+  const int64_t blocks = (num_rows + 255) / 256;
+  ep_source_table_kernel<<<static_cast<unsigned>(blocks < kNumSMs * 4 ? blocks : kNumSMs * 4), 256, 0,
+                           as_stream(stream)>>>(my_prefix, dst_start, world * experts_per_rank,
+                                                experts_per_rank, peers, out_offset, row_bytes,
+                                                capacity, src_addr);
+  return launch_status("ep_source_table_kernel");
+}
+
+extern "C" int b200moe_ep_gather(void* out, int dtype, const float* weights, const int32_t* row_map,
+                                 const int64_t* src_addr, int T, int k, int H, void* stream) {
+  if (T < 0 || k <= 0 || k > 64 || H <= 0) return B200MOE_INVALID_ARG;
+  if (T == 0) return B200MOE_OK;
+  if (!out || !weights || !row_map || !src_addr) return B200MOE_INVALID_ARG;
+  if ((H * dtype_size(dtype)) % 16 != 0) return B200MOE_INVALID_ARG;
+  // B200MOE_EP_GATHER=loads selects the plain-load kernel (kept for comparison).
+  const char* mode = getenv("B200MOE_EP_GATHER");
+  const bool bulk = !(mode && strcmp(mode, "loads") == 0);
+  return B200MOE_DISPATCH_FLOAT(dtype, [&] {
+    constexpr int V = 16 / sizeof(scalar_t);
+    cudaStream_t st = as_stream(stream);
+    if (!bulk) {
+      int threads = (H / V + 31) / 32 * 32;
+      threads = threads > 256 ? 256 : threads;
+      ep_gather_kernel<scalar_t><<<T, threads, 0, st>>>(reinterpret_cast<scalar_t*>(out), weights,
+                                                        row_map, src_addr, k, H);
+      return launch_status("ep_gather_kernel");
+    }
+    // column chunk: k staged rows per stage within 48 KB, two stages, two CTAs per SM
+    const int row_bytes = H * static_cast<int>(sizeof(scalar_t));
+    int cmax = (48 * 1024 / k) / 16 * 16;
+    if (cmax > row_bytes) cmax = row_bytes;
+    const int n_chunks = (row_bytes + cmax - 1) / cmax;
+    const int chunk_bytes = ((row_bytes + n_chunks - 1) / n_chunks + 15) / 16 * 16;
+    const size_t smem = 2 * static_cast<size_t>(k) * chunk_bytes;
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(ep_gather_bulk_kernel<scalar_t>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+      if (e != cudaSuccess) {
+        set_last_error("cudaFuncSetAttribute(ep_gather_bulk_kernel)", e);
+        return static_cast<int>(B200MOE_CUDA_ERROR);
+      }
+      attr_set = true;
+    }
+    int* status = device_status_word();
+    if (!status) return static_cast<int>(B200MOE_CUDA_ERROR);
+    const int64_t items = static_cast<int64_t>(T) * n_chunks;
+    const int grid = static_cast<int>(items < 2 * kNumSMs ? items : 2 * kNumSMs);
+    ep_gather_bulk_kernel<scalar_t><<<grid, 256, smem, st>>>(
+        reinterpret_cast<scalar_t*>(out), weights, row_map, src_addr, T, k, H,
+        chunk_bytes / static_cast<int>(sizeof(scalar_t)), n_chunks, status);
+    return launch_status("ep_gather_bulk_kernel");
+  });
+}
+
+extern "C" int b200moe_ep_dispatch(const void* hidden, const void* scales, int64_t row_bytes,
+                                   int64_t scale_row_bytes, const void* topk_ids, int ids_dtype,
+                                   const int32_t* row_map, int num_tokens, int topk, int my_rank,
+                                   int world, int experts_per_rank, const int32_t* my_prefix,
+                                   const int32_t* dst_start, const int64_t* peer_bases_host,
+                                   int64_t rows_offset, int64_t scales_offset, int64_t meta_offset,
+                                   int64_t capacity, void* stream) {
+  PeerPtrs peers;
+  if (!hidden || !topk_ids || !row_map || !my_prefix || !dst_start || !is_index_dtype(ids_dtype) ||
+      !load_peers(peer_bases_host, world, &peers) || row_bytes <= 0 || row_bytes % 16 != 0 ||
+      scale_row_bytes % 4 != 0 || num_tokens < 0 || topk <= 0 || experts_per_rank <= 0)
+    return B200MOE_INVALID_ARG;
+  if (num_tokens == 0) return B200MOE_OK;
+  const size_t smem = static_cast<size_t>(row_bytes) + (scale_row_bytes % 16 == 0 ? scale_row_bytes : 0);
+  if (smem > 200 * 1024) return B200MOE_UNSUPPORTED;
+  int* status = device_status_word();
+  if (!status) return B200MOE_CUDA_ERROR;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(ep_dispatch_bulk_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) {
+      set_last_error("cudaFuncSetAttribute(ep_dispatch_bulk_kernel)", e);
+      return B200MOE_CUDA_ERROR;
+    }
+    attr_set = true;
+  }
+  int per_sm = static_cast<int>((216 * 1024) / (smem + 1024));
+  per_sm = per_sm > 32 ? 32 : (per_sm < 1 ? 1 : per_sm);
+  const int64_t pairs = static_cast<int64_t>(num_tokens) * topk;
+  const int64_t want = static_cast<int64_t>(kNumSMs) * per_sm;
+  ep_dispatch_bulk_kernel<<<static_cast<unsigned>(pairs < want ? pairs : want), 32, smem,
+                            as_stream(stream)>>>(
+      reinterpret_cast<const uint8_t*>(hidden), reinterpret_cast<const uint8_t*>(scales), row_bytes,
+      scale_row_bytes, topk_ids, ids_dtype, row_map, pairs, topk, experts_per_rank, my_rank,
+      my_prefix, dst_start, peers, rows_offset, scales_offset, meta_offset, capacity, status);
+  return launch_status("ep_dispatch_bulk_kernel");
 }

@@ -1072,6 +1072,13 @@ extern "C" int b200moe_selftest_wait_timeout(long long budget_cycles, void* stre
   return launch_status("wait_timeout_selftest_kernel");
 }
 
+int* b200moe::device_status_word() {
+  // one address per device; looked up each time (a handful of host calls per layer)
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, b200moe::g_device_status) != cudaSuccess) return nullptr;
+  return reinterpret_cast<int*>(p);
+}
+
 extern "C" int b200moe_device_status(void* stream, int* status_host) {
   if (!status_host) return B200MOE_INVALID_ARG;
   cudaStream_t st = as_stream(stream);

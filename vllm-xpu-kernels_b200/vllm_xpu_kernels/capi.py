@@ -97,6 +97,13 @@ SIGNATURES = {
     "b200moe_ep_push": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int,
                                 c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                 c_void_p]),
+    "b200moe_ep_dispatch": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                    c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "b200moe_ep_source_table": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p, c_int64,
+                                        c_int64, c_int64, c_void_p, c_void_p]),
+    "b200moe_ep_gather": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_void_p]),
     "b200moe_ep_return_table": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
                                         c_void_p, c_void_p]),
 }

@@ -20,11 +20,17 @@ Received data always lands in this GPU's own memory (NCCL) before any kernel
 reads it.  Steps 1, 4 and 5 are injected as callables so that the exchange logic
 can be exercised on CPU ranks with torch stand-ins.
 """
+import os
 from dataclasses import dataclass
 from typing import Callable, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+
+# dtype codes of the C interface
+_FLOAT_CODES = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+_INDEX_CODES = {torch.int32: 4, torch.int64: 5}
 
 
 @dataclass
@@ -150,7 +156,8 @@ class PeerExpertParallel:
     """
 
     def __init__(self, group, moe, tokens_per_rank: int, topk: int, hidden: int, row_bytes: int,
-                 scale_row_bytes: int, experts_per_rank: int, device, out_dtype=torch.bfloat16):
+                 scale_row_bytes: int, experts_per_rank: int, device, out_dtype=torch.bfloat16,
+                 combine: str = None):
         import ctypes
 
         import torch.distributed._symmetric_memory as symm_mem
@@ -172,7 +179,20 @@ class PeerExpertParallel:
         self.off_rows = off; off = _align(off + self.cap * row_bytes)
         self.off_scales = off; off = _align(off + self.cap * max(scale_row_bytes, 4))
         self.off_meta = off; off = _align(off + self.cap * 8)
-        self.off_ret = off; off = _align(off + R * self.ret_row_bytes)
+        # "pull": the second GEMM stores locally and the token's owner reads the result rows
+        # from the peers inside the weighted sum.  "push": the second GEMM's epilogue stores
+        # every row into its sender's return buffer.  Measured on 8 GPUs at the DeepSeek-V3
+        # shape, the epilogue's per-lane 16-byte stores reach a fifth of the link rate and
+        # stall the tensor pipeline (second GEMM 12.4 ms against 3.7 ms alone), so pull is
+        # the default.
+        self.combine = combine or os.environ.get("B200MOE_EP_COMBINE", "pull")
+        assert self.combine in ("pull", "push")
+        if self.combine == "push":
+            self.off_ret = off; off = _align(off + R * self.ret_row_bytes)
+            self.off_out = 0
+        else:
+            self.off_out = off; off = _align(off + self.cap * self.ret_row_bytes)
+            self.off_ret = 0
         self.buf = symm_mem.empty(off, dtype=torch.uint8, device=device)
         self.hdl = symm_mem.rendezvous(self.buf, group.group_name)
         self.buf.zero_()
@@ -183,13 +203,19 @@ class PeerExpertParallel:
         self.recv_scales = (b[self.off_scales: self.off_scales + self.cap * scale_row_bytes]
                             if scale_row_bytes else None)
         self.meta = b[self.off_meta: self.off_meta + self.cap * 8].view(torch.int64)
-        self.ret = b[self.off_ret: self.off_ret + R * self.ret_row_bytes].view(out_dtype).view(R, hidden)
+        if self.combine == "push":
+            self.ret = b[self.off_ret: self.off_ret + R * self.ret_row_bytes].view(out_dtype).view(R, hidden)
+            self.dst_addr = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        else:
+            self.out_rows = b[self.off_out: self.off_out + self.cap * self.ret_row_bytes] \
+                .view(out_dtype).view(self.cap, hidden)
+            self.src_addr = torch.zeros(R, dtype=torch.int64, device=device)
         i32 = dict(dtype=torch.int32, device=device)
         self.my_prefix = torch.zeros(self.E + 1, **i32)
         self.dst_start = torch.zeros(self.E, **i32)
         self.rows_per_expert = torch.zeros(experts_per_rank, **i32)
         self.recv_total = torch.zeros(1, **i32)
-        self.dst_addr = torch.zeros(self.cap, dtype=torch.int64, device=device)
+        self._ws = None
         self.hdl.barrier(channel=0)
 
     def _check(self, rc, what):
@@ -201,33 +227,56 @@ class PeerExpertParallel:
         T, k = topk_ids.shape
         dev = hidden.device
         st = torch.cuda.current_stream().cuda_stream
-        # my rows grouped by global expert (stable), and how many go to each expert
-        send_rows = torch.empty((T * k, hidden.shape[1]), dtype=hidden.dtype, device=dev)
-        send_scales = (torch.empty((T * k, scales.shape[1]), dtype=scales.dtype, device=dev)
-                       if scales is not None else None)
+        # where each (token, slot) entry stands in my send order (stable by global expert), and
+        # how many entries go to each expert; the rows themselves are not copied locally
         send_counts = torch.zeros(self.E, dtype=torch.int32, device=dev)
         row_map = torch.empty((T, k), dtype=torch.int32, device=dev)
-        torch.ops._moe_C.remap_hidden_states(hidden, scales, send_rows, send_scales, None, send_counts,
-                                             row_map, topk_ids, self.E, self.E)
-        self._check(lib.b200moe_ep_put_counts(send_counts.data_ptr(), self.E, self.peer_bases,
-                                              self.off_counts, me, G, st), "ep_put_counts")
-        self.hdl.barrier(channel=0)
-        self._check(lib.b200moe_ep_offsets(self.counts.data_ptr(), me, G, self.E_loc,
-                                           self.my_prefix.data_ptr(), self.dst_start.data_ptr(),
-                                           self.rows_per_expert.data_ptr(), self.recv_total.data_ptr(),
-                                           st), "ep_offsets")
-        self._check(lib.b200moe_ep_push(
-            send_rows.data_ptr(), send_scales.data_ptr() if send_scales is not None else None, T * k,
-            self.row_bytes, self.scale_row_bytes, me, G, self.E_loc, self.my_prefix.data_ptr(),
-            self.dst_start.data_ptr(), self.peer_bases, self.off_rows, self.off_scales, self.off_meta,
-            self.cap, st), "ep_push")
-        self.hdl.barrier(channel=1)
-        self._check(lib.b200moe_ep_return_table(self.meta.data_ptr(), self.recv_total.data_ptr(), G,
-                                                self.peer_bases, self.off_ret, self.ret_row_bytes,
-                                                self.dst_addr.data_ptr(), st), "ep_return_table")
+        stage = self.moe._stage
+        ids_code = _INDEX_CODES[topk_ids.dtype]
+        ws_bytes = lib.b200moe_remap_hidden_states_workspace_bytes(T, k, self.E)
+        if self._ws is None or self._ws.numel() < ws_bytes:
+            self._ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        with stage("ep_group"):
+            self._check(lib.b200moe_remap_hidden_states(
+                None, None, None, None, self.row_bytes, self.scale_row_bytes, topk_ids.data_ptr(),
+                ids_code, None, T, k, self.E, self.E, send_counts.data_ptr(), row_map.data_ptr(),
+                self._ws.data_ptr(), self._ws.numel(), st), "remap_hidden_states")
+        with stage("ep_counts"):
+            self._check(lib.b200moe_ep_put_counts(send_counts.data_ptr(), self.E, self.peer_bases,
+                                                  self.off_counts, me, G, st), "ep_put_counts")
+            self.hdl.barrier(channel=0)
+            self._check(lib.b200moe_ep_offsets(self.counts.data_ptr(), me, G, self.E_loc,
+                                               self.my_prefix.data_ptr(), self.dst_start.data_ptr(),
+                                               self.rows_per_expert.data_ptr(),
+                                               self.recv_total.data_ptr(), st), "ep_offsets")
+        with stage("ep_push"):
+            self._check(lib.b200moe_ep_dispatch(
+                hidden.data_ptr(), scales.data_ptr() if scales is not None else None, self.row_bytes,
+                self.scale_row_bytes, topk_ids.data_ptr(), ids_code, row_map.data_ptr(), T, k, me, G,
+                self.E_loc, self.my_prefix.data_ptr(), self.dst_start.data_ptr(), self.peer_bases,
+                self.off_rows, self.off_scales, self.off_meta, self.cap, st), "ep_dispatch")
+            self.hdl.barrier(channel=1)
         rows = self.recv_rows.view(hidden.dtype).view(self.cap, -1)
         rscales = self.recv_scales.view(scales.dtype).view(self.cap, -1) if scales is not None else None
-        self.moe.run_experts(rows, rscales, self.rows_per_expert, self.out_dtype, self.dst_addr)
-        self.hdl.barrier(channel=2)
-        torch.ops._moe_C.moe_gather(output, self.ret, topk_weights, row_map, 0)
+        if self.combine == "push":
+            with stage("ep_table"):
+                self._check(lib.b200moe_ep_return_table(
+                    self.meta.data_ptr(), self.recv_total.data_ptr(), G, self.peer_bases, self.off_ret,
+                    self.ret_row_bytes, self.dst_addr.data_ptr(), st), "ep_return_table")
+            self.moe.run_experts(rows, rscales, self.rows_per_expert, self.out_dtype, self.dst_addr)
+            with stage("ep_combine"):
+                self.hdl.barrier(channel=2)
+                torch.ops._moe_C.moe_gather(output, self.ret, topk_weights, row_map, 0)
+            return output
+        with stage("ep_table"):
+            self._check(lib.b200moe_ep_source_table(
+                self.my_prefix.data_ptr(), self.dst_start.data_ptr(), T * k, G, self.E_loc,
+                self.peer_bases, self.off_out, self.ret_row_bytes, self.cap,
+                self.src_addr.data_ptr(), st), "ep_source_table")
+        self.moe.run_experts(rows, rscales, self.rows_per_expert, self.out_dtype, None, self.out_rows)
+        with stage("ep_combine"):
+            self.hdl.barrier(channel=2)
+            self._check(lib.b200moe_ep_gather(
+                output.data_ptr(), _FLOAT_CODES[output.dtype], topk_weights.data_ptr(),
+                row_map.data_ptr(), self.src_addr.data_ptr(), T, k, self.H, st), "ep_gather")
         return output

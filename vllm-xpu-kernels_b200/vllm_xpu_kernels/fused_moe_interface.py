@@ -235,13 +235,13 @@ class XpuFusedMoe:
             torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
                                         self.num_experts)
 
-    def run_experts(self, rows, row_scales, rows_per_expert, out_dtype, row_ptr=None):
+    def run_experts(self, rows, row_scales, rows_per_expert, out_dtype, row_ptr=None, out=None):
         """The two grouped GEMMs with the activation between them on rows that are already
         grouped by local expert (``rows_per_expert`` int32 on the device, experts back to
         back).  Returns the ``[R, H]`` result in the same row order, or, with ``row_ptr``
         (int64 address per row), stores each result row at its address and returns a
-        placeholder.  Not part of the reference class; ``apply`` and the expert-parallel
-        exchange both end here."""
+        placeholder.  ``out`` (``[R, H]``) is used as the result buffer when given.  Not part
+        of the reference class; ``apply`` and the expert-parallel exchange both end here."""
         R, hidden_size = rows.shape
         dev = rows.device
         remapped, remapped_scales = rows, row_scales
@@ -274,8 +274,8 @@ class XpuFusedMoe:
                         act = self._activate(gemm1_out)
                         torch.ops._C.per_token_group_fp8_quant(act, act_q, act_s, 128, 1e-10, -448.0,
                                                                448.0, False, False, False)
-            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=out_dtype,
-                                    device=dev)
+            gemm2_out = out if out is not None else torch.empty(
+                (R if row_ptr is None else 1, hidden_size), dtype=out_dtype, device=dev)
             with self._stage("gemm2"):
                 gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
                      rows_per_expert, hidden_size, K2, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None,
@@ -297,8 +297,8 @@ class XpuFusedMoe:
                          2 * I, hidden_size, E, EPI_STORE, layout)
                 with self._stage("act"):
                     act = self._activate(gemm1_out)
-            gemm2_out = torch.empty((R if row_ptr is None else 1, hidden_size), dtype=out_dtype,
-                                    device=dev)
+            gemm2_out = out if out is not None else torch.empty(
+                (R if row_ptr is None else 1, hidden_size), dtype=out_dtype, device=dev)
             with self._stage("gemm2"):
                 gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, K2,
                      E, EPI_STORE, layout, 1.702, 7.0, None, row_ptr)
