@@ -151,6 +151,7 @@ class XpuFusedMoe:
         # for each stage, the way the reference's benchmark brackets its stages
         # (benchmark/src/fused_moe_interface_.py:84-168 there).
         self.stage_timer = None
+        self.stage_only = None   # optional set of stage names to restrict the timer to
 
         self.expert_map = expert_map
         if self.expert_map is None and self.ep_size > 1:
@@ -166,7 +167,7 @@ class XpuFusedMoe:
 
     @contextlib.contextmanager
     def _stage(self, name):
-        if self.stage_timer is None:
+        if self.stage_timer is None or (self.stage_only is not None and name not in self.stage_only):
             yield
             return
         start = torch.cuda.Event(enable_timing=True)
