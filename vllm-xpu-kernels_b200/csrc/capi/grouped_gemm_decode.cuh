@@ -123,6 +123,7 @@ struct alignas(8) DecodeBarriers {
   uint64_t empty[8];
   uint64_t tfull[4];
   uint64_t tempty[4];
+  uint64_t sfree, sready;  // hand-over of the staged-scales buffer between tiles (4 reader warps)
 };
 
 // GATED: two weight tiles per stage (gate features f, up features N/2 + f), epilogue
@@ -158,6 +159,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
   const int n_out = GATED ? p.N / 2 : p.N;            // output features
   const int f_tiles = (n_out + kFeat - 1) / kFeat;
   const int num_kb = p.K / kBK;
+  // after the operand stages: this tile's activation scales [K/128][32] and weight scales [K/128][2]
+  float* sa_s = reinterpret_cast<float*>(tiles + C::STAGES * C::STAGE_BYTES);
+  float* sb_s = sa_s + num_kb * kNTok;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -169,6 +173,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
       mbar_init(&bars.tfull[b], 1);
       mbar_init(&bars.tempty[b], 4);
     }
+    mbar_init(&bars.sfree, 4);
+    mbar_init(&bars.sready, 4);
     mbar_fence_init();
     prefetch_tensormap(&map_tok);
     prefetch_tensormap(&map_w);
@@ -249,6 +255,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
     const int nb_count = p.N / 128;
     int buf = 0;
     uint32_t buf_phase = 0;
+    uint32_t tile_parity = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const DecodeTile tc = decode_tile(sched, t);
@@ -263,14 +270,41 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
       const int nb_g = f0 / 128 < nb_count ? f0 / 128 : nb_count - 1;
       const int nb_u = GATED ? ((p.N / 2 + f0) / 128 < nb_count ? (p.N / 2 + f0) / 128 : nb_count - 1) : 0;
       const float* sb_ptr = p.b_scale + static_cast<int64_t>(tc.expert) * num_kb * nb_count;
+      // All scales of the tile go to shared memory first (one round trip to L2 per tile):
+      // a load per K block would put that latency on every step of the readers' chain,
+      // which is what paces this kernel.
+      // (mbarriers with the bounded wait rather than a named barrier: a warp that gave up on
+      // a wait must not leave the others parked)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.sfree);   // this warp is done with the last tile's scales
+      ok = mbar_wait(&bars.sfree, tile_parity, abort_p);
+      if (!ok) break;
+      {
+        const int rt = threadIdx.x - 128;
+        for (int i = rt; i < num_kb * kNTok; i += 128) {
+          const int j = i & (kNTok - 1);
+          sa_s[i] = j < tc.rows_valid
+                        ? p.a_scale_t[static_cast<int64_t>(i / kNTok) * p.R + tc.row_start + j]
+                        : 0.f;
+        }
+        for (int i = rt; i < 2 * num_kb; i += 128)
+          sb_s[i] = sb_ptr[(i >> 1) * nb_count + ((i & 1) ? nb_u : nb_g)];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars.sready);
+      ok = mbar_wait(&bars.sready, tile_parity, abort_p);
+      if (!ok) break;
+      tile_parity ^= 1u;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         // scales of this K block: one per token (same for every lane) and one per weight block
         float sa[kNTok];
-        const float* sa_ptr = p.a_scale_t + static_cast<int64_t>(kb) * p.R + tc.row_start;
 #pragma unroll
-        for (int j = 0; j < kNTok; ++j) sa[j] = j < tc.rows_valid ? sa_ptr[j] : 0.f;
-        const float sbg = sb_ptr[kb * nb_count + nb_g];
-        const float sbu = GATED ? sb_ptr[kb * nb_count + nb_u] : 0.f;
+        for (int j = 0; j < kNTok; j += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(sa_s + kb * kNTok + j);
+          sa[j] = v.x; sa[j + 1] = v.y; sa[j + 2] = v.z; sa[j + 3] = v.w;
+        }
+        const float sbg = sb_s[2 * kb];
+        const float sbu = GATED ? sb_s[2 * kb + 1] : 0.f;
         ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
         if (!ok) break;
         tc_fence_after();
@@ -346,18 +380,21 @@ int launch_decode(const b200moe_gemm_args& a, cudaStream_t st) {
   p.K = a.K;
   p.E = a.E;
   p.ldd = GATED ? a.N / 2 : a.N;
+  constexpr int kMaxDecodeKBlocks = 160;  // K <= 20480: the staged scales fit beside the stages
+  if (a.K / kBK > kMaxDecodeKBlocks) return B200MOE_UNSUPPORTED;
+  const size_t smem = C::SMEM_BYTES + static_cast<size_t>(a.K / kBK) * (kNTok + 2) * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(decode_gemm_kernel<GATED>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(C::SMEM_BYTES));
+    cudaError_t e = cudaFuncSetAttribute(
+        decode_gemm_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        static_cast<int>(C::SMEM_BYTES + kMaxDecodeKBlocks * (kNTok + 2) * sizeof(float)));
     if (e != cudaSuccess) {
       set_last_error("cudaFuncSetAttribute", e);
       return B200MOE_CUDA_ERROR;
     }
     attr_set = true;
   }
-  decode_gemm_kernel<GATED><<<kNumSMs, C::THREADS, C::SMEM_BYTES, st>>>(map_tok, map_w, p);
+  decode_gemm_kernel<GATED><<<kNumSMs, C::THREADS, smem, st>>>(map_tok, map_w, p);
   return launch_status("decode_gemm_kernel");
 }
 
