@@ -1,0 +1,155 @@
+"""The expert-parallel exchange kernels with several ranks emulated on ONE GPU.
+
+None of these kernels waits on another rank (the ordering between steps is the caller's
+barriers), so the ranks' launches can simply run one after the other on one device, each
+rank with its own "symmetric" buffer and the table of all buffers' addresses.  Checked: the
+receive buffers hold exactly the rows the grouped GEMM expects (experts back to back,
+sources in rank order, stable inside a source), scales and tags travel with them, and the
+pull combine (both kernels) and the push return table give the weighted sum of the owners'
+results."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+I32, I64 = 4, 5
+
+
+def _align(n, a=256):
+    return (n + a - 1) // a * a
+
+
+class Rank:
+    def __init__(self, r, G, E_loc, T, k, H, scale_bytes, g):
+        self.r = r
+        E = G * E_loc
+        self.x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(DEV)
+        ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+        ids[torch.rand(T, k, generator=g) < 0.05] = -1          # a few dropped entries
+        self.ids = ids.to(DEV)
+        self.w = torch.rand(T, k, generator=g).to(DEV)
+        self.scales = (torch.randn(T, scale_bytes // 4, generator=g).to(DEV) if scale_bytes else None)
+        cap = G * T * k
+        off = 0
+        self.off_counts = off; off = _align(off + G * E * 4)
+        self.off_rows = off; off = _align(off + cap * H * 2)
+        self.off_scales = off; off = _align(off + cap * max(scale_bytes, 4))
+        self.off_meta = off; off = _align(off + cap * 8)
+        self.off_out = off; off = _align(off + cap * H * 2)
+        self.off_ret = off; off = _align(off + T * k * H * 2)
+        self.buf = torch.zeros(off, dtype=torch.uint8, device=DEV)
+        i32 = dict(dtype=torch.int32, device=DEV)
+        self.send_counts = torch.zeros(E, **i32)
+        self.row_map = torch.empty(T, k, **i32)
+        self.my_prefix = torch.zeros(E + 1, **i32)
+        self.dst_start = torch.zeros(E, **i32)
+        self.rows_per_expert = torch.zeros(E_loc, **i32)
+        self.recv_total = torch.zeros(1, **i32)
+
+    def view(self, off, nbytes, dtype):
+        return self.buf[off: off + nbytes].view(dtype)
+
+
+@pytest.mark.parametrize("G,E_loc,T,k,H,scale_bytes", [(4, 3, 37, 3, 256, 16), (2, 8, 64, 4, 512, 8),
+                                                       (3, 2, 50, 2, 128, 0), (1, 8, 33, 2, 256, 16)])
+@pytest.mark.parametrize("gather", ["bulk", "loads"])
+def test_exchange_with_emulated_ranks(ops, G, E_loc, T, k, H, scale_bytes, gather, monkeypatch):
+    from vllm_xpu_kernels import capi
+    monkeypatch.setenv("B200MOE_EP_GATHER", gather)
+    lib = capi.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(G * 100 + T)
+    E, cap, row_bytes = G * E_loc, G * T * k, H * 2
+    ranks = [Rank(r, G, E_loc, T, k, H, scale_bytes, g) for r in range(G)]
+    bases = (ctypes.c_int64 * G)(*[rk.buf.data_ptr() for rk in ranks])
+
+    def ok(rc):
+        assert rc == 0, (capi.status_string(rc), lib.b200moe_last_error().decode())
+
+    ws = torch.empty(max(lib.b200moe_remap_hidden_states_workspace_bytes(T, k, E), 16), dtype=torch.uint8, device=DEV)
+    for rk in ranks:        # step 1 + 2: rank my entries by global expert, publish the counts
+        ok(lib.b200moe_remap_hidden_states(None, None, None, None, row_bytes, scale_bytes, rk.ids.data_ptr(),
+                                           I32, None, T, k, E, E, rk.send_counts.data_ptr(),
+                                           rk.row_map.data_ptr(), ws.data_ptr(), ws.numel(), st))
+        ok(lib.b200moe_ep_put_counts(rk.send_counts.data_ptr(), E, bases, rk.off_counts, rk.r, G, st))
+    for rk in ranks:        # step 3 + 4: offsets, then rows to their owners
+        counts = rk.view(rk.off_counts, G * E * 4, torch.int32)
+        ok(lib.b200moe_ep_offsets(counts.data_ptr(), rk.r, G, E_loc, rk.my_prefix.data_ptr(),
+                                  rk.dst_start.data_ptr(), rk.rows_per_expert.data_ptr(),
+                                  rk.recv_total.data_ptr(), st))
+        ok(lib.b200moe_ep_dispatch(rk.x.data_ptr(), rk.scales.data_ptr() if scale_bytes else None, row_bytes,
+                                   scale_bytes, rk.ids.data_ptr(), I32, rk.row_map.data_ptr(), T, k, rk.r, G,
+                                   E_loc, rk.my_prefix.data_ptr(), rk.dst_start.data_ptr(), bases,
+                                   rk.off_rows, rk.off_scales, rk.off_meta, cap, st))
+    torch.cuda.synchronize()
+
+    # what every owner must now hold: experts back to back, sources in rank order, stable inside
+    for o, rk in enumerate(ranks):
+        want_rows, want_scales, want_tags, want_counts = [], [], [], []
+        for e in range(o * E_loc, (o + 1) * E_loc):
+            n_e = 0
+            for s in ranks:
+                flat = s.ids.flatten()
+                sel = (flat == e).nonzero().flatten()
+                want_rows.append(s.x[sel // k])
+                if scale_bytes:
+                    want_scales.append(s.scales[sel // k])
+                want_tags.append((s.r << 32) | s.row_map.flatten()[sel].long())
+                n_e += sel.numel()
+            want_counts.append(n_e)
+        want_rows = torch.cat(want_rows)
+        n = want_rows.shape[0]
+        assert int(rk.recv_total) == n and rk.rows_per_expert.tolist() == want_counts
+        got = rk.view(rk.off_rows, cap * row_bytes, torch.bfloat16).view(cap, H)[:n]
+        assert torch.equal(got, want_rows)
+        if scale_bytes:
+            gs = rk.view(rk.off_scales, cap * scale_bytes, torch.float32).view(cap, -1)[:n]
+            assert torch.equal(gs, torch.cat(want_scales))
+        assert torch.equal(rk.view(rk.off_meta, cap * 8, torch.int64)[:n], torch.cat(want_tags))
+        # stand-in for the experts: result row = received row * (1 + local expert index)
+        factor = torch.repeat_interleave(torch.arange(1, E_loc + 1, device=DEV), rk.rows_per_expert.long())
+        out = rk.view(rk.off_out, cap * row_bytes, torch.bfloat16).view(cap, H)
+        out[:n] = (got.float() * factor.unsqueeze(1)).to(torch.bfloat16)
+
+    def expected(rk):
+        e_loc = (rk.ids % E_loc + 1).float()
+        rows = (rk.x.float().unsqueeze(1) * e_loc.unsqueeze(2)).to(torch.bfloat16).float()   # [T, k, H]
+        wgt = torch.where(rk.ids >= 0, rk.w, torch.zeros_like(rk.w))
+        acc = torch.zeros(T, H, device=DEV)
+        for j in range(k):                       # slot order, fp32, as the kernels do
+            acc = acc + wgt[:, j: j + 1] * rows[:, j]
+        return acc.to(torch.bfloat16)
+
+    for rk in ranks:        # pull combine
+        src = torch.zeros(T * k, dtype=torch.int64, device=DEV)
+        ok(lib.b200moe_ep_source_table(rk.my_prefix.data_ptr(), rk.dst_start.data_ptr(), T * k, G, E_loc,
+                                       bases, rk.off_out, row_bytes, cap, src.data_ptr(), st))
+        res = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+        ok(lib.b200moe_ep_gather(res.data_ptr(), 2, rk.w.data_ptr(), rk.row_map.data_ptr(), src.data_ptr(),
+                                 T, k, H, st))
+        torch.cuda.synchronize()
+        torch.testing.assert_close(res.float(), expected(rk).float(), atol=2e-2, rtol=2e-2)
+
+    if gather == "bulk":    # push combine: the return table sends every result row home
+        for rk in ranks:
+            dst = torch.zeros(cap, dtype=torch.int64, device=DEV)
+            ok(lib.b200moe_ep_return_table(rk.view(rk.off_meta, cap * 8, torch.int64).data_ptr(),
+                                           rk.recv_total.data_ptr(), G, bases, rk.off_ret, row_bytes,
+                                           dst.data_ptr(), st))
+            n = int(rk.recv_total)
+            out = rk.view(rk.off_out, cap * row_bytes, torch.bfloat16).view(cap, H)
+            base_of = {int(b): s for b, s in zip(bases, ranks)}
+            for j in range(n):           # what the second GEMM's epilogue does with the table
+                addr = int(dst[j])
+                owner = max((b for b in base_of if b <= addr), key=lambda b: b)
+                s = base_of[owner]
+                row = (addr - owner - s.off_ret) // row_bytes
+                s.view(s.off_ret, T * k * row_bytes, torch.bfloat16).view(T * k, H)[row] = out[j]
+        for rk in ranks:
+            ret = rk.view(rk.off_ret, T * k * row_bytes, torch.bfloat16).view(T * k, H)
+            res = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+            ops._moe_C.moe_gather(res, ret, rk.w, rk.row_map, 0)
+            torch.testing.assert_close(res.float(), expected(rk).float(), atol=2e-2, rtol=2e-2)
+    assert ops._xpu_C.b200_device_status() == 0

@@ -1,10 +1,10 @@
 // Expert-parallel exchange over peer-mapped memory (NVLink / NVSwitch).
 //
 // Each rank owns a slice of the experts and a slice of the tokens.  All buffers
-// that another rank writes live in a symmetric allocation whose per-rank base
-// addresses every rank knows, so the exchange is plain stores to peer
-// addresses from ordinary kernels — no collective library call, no host round
-// trip for sizes:
+// that another rank touches live in a symmetric allocation whose per-rank base
+// addresses every rank knows, so the exchange is stores to and loads from peer
+// addresses issued by this library's own kernels — no collective library call,
+// no host round trip for sizes:
 //
 //   put_counts   my rows per GLOBAL expert -> row `me` of every rank's [G, E]
 //                count matrix                             (then a device barrier)
@@ -12,26 +12,28 @@
 //                start inside its owner's receive buffer (which is grouped by
 //                expert, sources in rank order inside an expert); the rows each
 //                of my own experts receives
-//   push         my send rows (grouped by global expert, as remap_hidden_states
-//                leaves them) + activation scales -> their final place in the
-//                owners' receive buffers, plus (my rank, my row) per row
+//   dispatch     every (token, slot) row + activation scales -> its final place
+//                in the owner's receive buffer, plus (my rank, my row) per row,
+//                as bulk asynchronous copies; `push` is the older form that
+//                takes rows already grouped by expert and plain stores
 //                                                         (then a device barrier)
-//   return_table (rank, row) of every received row -> the address of that row
-//                in the sender's return buffer; the second grouped GEMM takes
-//                this table and its epilogue stores straight to the peers
-//                ("push" combine), or
 //   source_table for every row I sent, the address its result will have in the
 //                owner's output buffer, and
 //   gather       out[t] = sum_j w[t,j] * row at source_table[row_map[t,j]]: the
 //                token's owner reads the k result rows from the peers and does
-//                the weighted sum in the same pass ("pull" combine; the
-//                second GEMM then stores locally at full speed).
+//                the weighted sum in the same pass ("pull" combine; the second
+//                grouped GEMM stores locally at full speed), or
+//   return_table (rank, row) of every received row -> the address of that row
+//                in the sender's return buffer; the second grouped GEMM takes
+//                this table and its epilogue stores straight to the peers
+//                ("push" combine).
 //
 // The receive buffer is already in the order the grouped GEMM wants, so the
 // receiving side runs no permutation at all.
 //
 // The barriers between the steps are issued by the caller on the same stream.
-// Every kernel here only writes; nothing spins on remote data.
+// No kernel here spins on remote data; the bulk-copy kernels wait only on the
+// mbarrier of their own copies, with a cycle budget.
 #include "common.cuh"
 #include "tcgen05.cuh"
 

@@ -139,19 +139,20 @@ def _align(n, a=256):
 
 
 class PeerExpertParallel:
-    """Expert-parallel layer call whose dispatch and combine are stores into other GPUs'
+    """Expert-parallel layer call whose dispatch and combine move rows through other GPUs'
     memory from this library's own kernels (see csrc/capi/ep.cu):
 
-      group my rows by global expert (remap_hidden_states) -> put_counts -> barrier ->
-      offsets -> push every row to its final place in its owner's expert-grouped receive
-      buffer -> barrier -> the two grouped GEMMs straight on the receive buffer; the second
-      one stores every result row into the return buffer of the rank the token came from
-      -> barrier -> weighted sum (moe_gather).
+      rank my (token, slot) entries by global expert (remap_hidden_states, grouping only) ->
+      put_counts -> barrier -> offsets -> dispatch every row to its final place in its owner's
+      expert-grouped receive buffer -> barrier -> the two grouped GEMMs straight on the
+      receive buffer -> barrier -> gather: the token's owner reads its k result rows from the
+      owners' output buffers inside the weighted sum ("pull"; with combine="push" the second
+      GEMM's epilogue stores the rows into the sender's return buffer instead).
 
     The receiving side runs no permutation: senders place rows where the grouped GEMM wants
-    them.  Receive buffers are sized for the worst case (every routed row of every rank
-    lands here); unused rows cost nothing in the GEMMs, whose row counts live on the
-    device.  The three barriers are device-side (symmetric-memory signal pads),
+    them.  Receive and output buffers are sized for the worst case (every routed row of
+    every rank lands here); unused rows cost nothing in the GEMMs, whose row counts live on
+    the device.  The three barriers are device-side (symmetric-memory signal pads),
     stream-ordered, about 7 us each on NVSwitch; there is no host synchronisation.
     """
 
