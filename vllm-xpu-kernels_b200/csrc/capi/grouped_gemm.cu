@@ -300,12 +300,76 @@ __device__ __forceinline__ void accumulate32(float* acc, const float (&t)[32], f
   }
 }
 
+// The same store for a whole warp, coalesced.  Each lane holds NV consecutive columns of
+// its own row (lane = row), so a direct store instruction would touch 32 different rows
+// with 16 bytes each -- 32 separate lines per instruction, which costs the readers about
+// 2 us per 128x256 tile.  Here every 32-column chunk goes through a 2 KB per-warp buffer
+// in shared memory (16-byte pieces XOR-swizzled so that neither side has bank conflicts)
+// and comes back with four lanes per row: a store instruction then writes 8 rows x 64
+// contiguous bytes.  `row_base(rr)` returns the address of element 0 of row rr of this
+// warp's 32 rows (or nullptr to skip the row); all 32 lanes must call this together.
+template <int NV, typename RowBase>
+__device__ __forceinline__ void store_rows_coalesced(uint4* wbuf, int lane, int d_dtype, int col0,
+                                                     const float (&v)[NV], int n_valid,
+                                                     RowBase row_base) {
+  static_assert(NV % 32 == 0, "whole 32-column chunks");
+  uint8_t* rows[4];
+#pragma unroll
+  for (int it = 0; it < 4; ++it) rows[it] = reinterpret_cast<uint8_t*>(row_base(it * 8 + (lane >> 2)));
+  const int qq = lane & 3;
+#pragma unroll
+  for (int c = 0; c < NV / 32; ++c) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t w[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float a = v[c * 32 + q * 8 + 2 * i], b = v[c * 32 + q * 8 + 2 * i + 1];
+        if (d_dtype == B200MOE_BF16) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        } else {
+          const __half2 h = __floats2half2_rn(a, b);
+          w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      }
+      wbuf[lane * 4 + (q ^ ((lane >> 1) & 3))] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int rr = it * 8 + (lane >> 2);
+      const uint4 piece = wbuf[rr * 4 + (qq ^ ((rr >> 1) & 3))];
+      const int col = c * 32 + qq * 8;  // first of the 8 columns this lane stores
+      if (rows[it]) {
+        uint8_t* dst = rows[it] + static_cast<int64_t>(col0 + col) * 2;
+        if (col + 8 <= n_valid) {
+          *reinterpret_cast<uint4*>(dst) = piece;
+        } else {  // ragged right edge: element by element
+          const uint16_t* e = reinterpret_cast<const uint16_t*>(&piece);
+          for (int j = 0; j < 8; ++j)
+            if (col + j < n_valid) reinterpret_cast<uint16_t*>(dst)[j] = e[j];
+        }
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // acc[] -> global memory for one row of one tile.
 template <typename C>
 __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoord& tc, int g,
                                               bool row_ok, int64_t grow, float (&acc)[C::CPT],
-                                              float* xchg) {
+                                              float* xchg, uint4* wbuf) {
   constexpr int CPT = C::CPT;
+  const int lane = threadIdx.x & 31;
+  // rows of this warp: grow - lane .. grow - lane + 31, valid below `warp_rows_valid`
+  const int64_t warp_row0 = grow - lane;
+  const int warp_rows_valid = tc.rows_valid - static_cast<int>(warp_row0 - tc.row_start);
+  auto local_row = [&](int rr) -> void* {  // element 0 of row rr in D
+    if (rr >= warp_rows_valid) return nullptr;
+    return reinterpret_cast<uint8_t*>(p.D) + (warp_row0 + rr) * p.ldd * 2;
+  };
   if (p.bias) {
 #pragma unroll
     for (int c = 0; c < C::NCH; ++c) {
@@ -319,11 +383,14 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
   }
   if constexpr (C::EPI == B200MOE_EPI_STORE) {
     const int col0 = tc.n_tile * C::BN + g * CPT;
-    if (row_ok && col0 < p.N) {
-      if (p.d_row_ptr)  // the row's home may be another GPU's memory
-        store_row16<CPT>(reinterpret_cast<void*>(p.d_row_ptr[grow]), p.d_dtype, col0, acc, p.N - col0);
-      else
-        store_row16<CPT>(p.D, p.d_dtype, grow * p.ldd + col0, acc, p.N - col0);
+    if (col0 < p.N) {
+      if (p.d_row_ptr) {  // the row's home may be another GPU's memory
+        store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, [&](int rr) -> void* {
+          return rr < warp_rows_valid ? reinterpret_cast<void*>(p.d_row_ptr[warp_row0 + rr]) : nullptr;
+        });
+      } else {
+        store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, local_row);
+      }
     }
   } else if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
     constexpr int HALF = CPT / 2;
@@ -364,8 +431,8 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
           *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
-    } else if (row_ok && col0 < half_n) {
-      store_row16<HALF>(p.D, p.d_dtype, grow * p.ldd + col0, o, half_n - col0);
+    } else if (col0 < half_n) {
+      store_rows_coalesced<HALF>(wbuf, lane, p.d_dtype, col0, o, half_n - col0, local_row);
     }
   } else {  // SWIGLU_OAI: (gate, up) pairs are adjacent columns
     const int col0 = tc.n_tile * C::BN + g * CPT;
@@ -373,8 +440,8 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
 #pragma unroll
     for (int j = 0; j < CPT / 2; ++j)
       o[j] = swiglu_oai_f32(acc[2 * j], acc[2 * j + 1], p.alpha, p.limit);
-    if (row_ok && col0 < p.N)
-      store_row16<CPT / 2>(p.D, p.d_dtype, grow * p.ldd + col0 / 2, o, (p.N - col0) / 2);
+    if (col0 < p.N)
+      store_rows_coalesced<CPT / 2>(wbuf, lane, p.d_dtype, col0 / 2, o, (p.N - col0) / 2, local_row);
   }
 }
 
@@ -419,6 +486,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ int abort_flag;
   __shared__ float xchg[2][256];  // group-amax exchange of the quantising epilogue, by tile parity
   __shared__ float sb_smem[2][2 * kMaxKBlocks];  // weight scales of the tile's two column blocks
+  __shared__ uint4 epi_buf[8][128];              // per reader warp: 32 rows x 64 B for coalesced stores
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -653,7 +721,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       if (!ok) break;
-      tile_epilogue<C>(p, tc, g, row_ok, grow, acc, xchg[tile_parity]);
+      tile_epilogue<C>(p, tc, g, row_ok, grow, acc, xchg[tile_parity], epi_buf[ew]);
     }
   }
 
