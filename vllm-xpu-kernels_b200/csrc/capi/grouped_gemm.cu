@@ -261,6 +261,7 @@ struct alignas(8) Barriers {
   uint64_t empty[8];
   uint64_t tfull[4];
   uint64_t tempty[4];
+  uint64_t sready;  // this tile's staged scales are in shared memory (one arrival per reader warp)
 };
 
 // Tensor-memory column (inside one accumulator buffer) of chunk c of a reader
@@ -506,6 +507,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(&bars.tfull[b], 1);
       mbar_init(&bars.tempty[b], C::EPI_WARPS * (C::PAIR ? 2 : 1));  // both CTAs' readers
     }
+    mbar_init(&bars.sready, C::EPI_WARPS);
     mbar_fence_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -662,7 +664,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         sa_ptr = p.a_scale + grow * num_kb;
         sa_cur = load_sa4(0);
         sa_next = load_sa4(4);
-        asm volatile("bar.sync 5, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+        // hand-over of the staged buffer: one arrival per warp and a bounded wait (a warp that
+        // gave up on some wait must not leave the others parked on a plain barrier)
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.sready);
+        ok = mbar_wait(&bars.sready, static_cast<uint32_t>(tile_parity), abort_p);
+        if (!ok) break;
       }
       // first two loads of the tile
       ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
