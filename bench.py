@@ -498,6 +498,18 @@ def main():
             "clocks": clk.summary(),
             "stages_ms": stages, "active_experts": active,
         }
+        # the streaming stages either side of the GEMMs: algorithmic bytes / stage time
+        b_in = 1 if fp8 else 2
+        H = cfg["H"]
+        stream_bytes = {
+            "remap": T * H * b_in + R * H * b_in + (R + T) * (H // 128) * 4 * (1 if fp8 else 0) + T * cfg["k"] * 8,
+            "gather": R * H * 2 + T * H * 2 + T * cfg["k"] * 8,
+        }
+        line["hbm_stages"] = {
+            name: {"gbs": round(stream_bytes[name] / (stages[name] * 1e-3) / 1e9, 1),
+                   "frac_of_measured_copy": round(stream_bytes[name] / (stages[name] * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                   "bytes": stream_bytes[name], "ms": stages[name]}
+            for name in stream_bytes if stages.get(name)}
         nominal = 4500.0 if fp8 else 2250.0   # dense TFLOP/s of the part's data sheet
         line["roofline"]["frac_of_nominal"] = achieved / nominal
         line["roofline"]["nominal_peak"] = nominal
