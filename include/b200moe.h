@@ -59,7 +59,9 @@ extern "C" {
 #define B200MOE_A_SCALE_KBLOCK_MAJOR 1 /* [K/128, R]: also selects the decode-regime kernel
                                           (weights on the M side of the MMA, 32 tokens per
                                           tile); FP8_BLOCK recipe, EPI_STORE / EPI_SILU_MUL,
-                                          16-bit output                                      */
+                                          16-bit output, or e4m3 + d_scale with SILU_MUL     */
+#define B200MOE_A_SCALE_ROW_MAJOR_DECODE 2 /* [R, K/128] as ROW_MAJOR, and the decode-regime
+                                          kernel as KBLOCK_MAJOR                              */
 
 /* epilogues of the grouped GEMM */
 #define B200MOE_EPI_STORE 0        /* D = acc (+bias), dtype of D                       */

@@ -229,6 +229,40 @@ def test_fp8_decode_kernel(ops, epi, E, max_rows, K, N):
     assert (D[R:] == 9.0).all()
 
 
+@pytest.mark.parametrize("E,max_rows,K,N", [(4, 5, 256, 512), (16, 70, 512, 1024), (3, 1, 7168, 512)])
+def test_fp8_decode_kernel_row_major_scales_and_quantised_output(ops, E, max_rows, K, N):
+    """The decode-regime kernel fed like the default one (row-major activation scales) and
+    writing what the default w13 kernel writes: e4m3 [R, N/2] + one f32 scale per token per
+    128 columns."""
+    g = torch.Generator().manual_seed(E * 11 + K)
+    rows = torch.randint(0, max_rows + 1, (E,), generator=g).to(torch.int32)
+    rows[0] = max_rows
+    R = int(rows.sum())
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    Aq, As = O.per_token_group_fp8_quant(x, 128)
+    Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / K ** 0.5) for _ in range(E)])
+    Bq, Bs = torch.stack(Bq), torch.stack(Bs) * (1.0 + 0.25 * torch.rand(E, K // 128, N // 128, generator=g))
+    h = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As), Bq, Bs, None, rows, torch.float32)
+    # 16-bit output with row-major scales
+    D = torch.full((R + 2, N), 9.0, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, D, rows.to(DEV), N, K, E,
+                                 EPI_STORE, KN, 1.702, 7.0, None, None, 2)
+    close(D[:R], h)
+    assert (D[R:] == 9.0).all()
+    # quantised gated output
+    act = O.silu_mul_fp32(h)
+    I = N // 2
+    gact = act.view(R, I // 128, 128)
+    rs = torch.maximum(gact.abs().amax(-1) / 448.0, torch.tensor(O.FP8_MIN_SCALE))
+    Dq = torch.zeros(R, I, dtype=torch.float8_e4m3fn, device=DEV)
+    Ds = torch.zeros(R, I // 128, dtype=torch.float32, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, Dq, rows.to(DEV), N, K, E,
+                                 EPI_SILU, KN, 1.702, 7.0, Ds, None, 2)
+    assert torch.allclose(Ds.cpu(), rs, rtol=1e-3, atol=1e-9)
+    deq = Dq.cpu().float().view(R, -1, 128) * Ds.cpu().unsqueeze(-1)
+    assert ((deq - gact).abs() <= 0.07 * gact.abs() + 2e-3 * rs.unsqueeze(-1) + 1e-6).all()
+
+
 def test_fp8_weights_with_16bit_activations(ops):
     # what the reference kernel does natively: weights expanded, activations untouched
     E, K, N = 3, 256, 384

@@ -162,3 +162,25 @@ def test_cuda_graph_capture_and_replay(ops, name):
         step()
         torch.cuda.synchronize()
         assert torch.equal(replayed, out)
+
+
+@pytest.mark.parametrize("T", [1, 3])
+def test_few_tokens_take_the_decode_kernels(ops, T, monkeypatch):
+    """At most one routed row per expert: apply() picks the decode-regime GEMMs by itself; the
+    result matches the oracle and the default kernels' result within the FP8 bound."""
+    monkeypatch.delenv("B200MOE_DECODE_PATH", raising=False)
+    cfg = dict(O.CONFIGS["c1"], H=512, I=1024)
+    layer = O.make_layer(cfg, T=T)
+    moe = build(cfg, layer)
+    assert moe._decode_regime(T * cfg["k"])
+    w, ids = route_gpu(ops, cfg, layer)
+    rw, rids = O.route(cfg, layer)
+    out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=DEV)
+    moe.apply(out, to_dev(layer["x"]), w, ids)
+    ref = O.fused_moe("fp8block", layer["x"], layer["w13"], layer["w13_scale"], None, layer["w2"],
+                      layer["w2_scale"], None, rw, rids, "silu", out_dtype=torch.float32)
+    check(out, ref, 5e-2)
+    monkeypatch.setenv("B200MOE_DECODE_PATH", "0")
+    out2 = torch.empty_like(out)
+    moe.apply(out2, to_dev(layer["x"]), w, ids)
+    check(out2, ref, 5e-2)

@@ -1068,7 +1068,8 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   const bool wide = want_wide_tile(a);
   const bool pair = want_pair(a, wide);
 
-  if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR) return grouped_gemm_decode(a, st);
+  if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR || a.a_scale_layout == B200MOE_A_SCALE_ROW_MAJOR_DECODE)
+    return grouped_gemm_decode(a, st);
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3 && !a.a_scale && !a.b_scale) {
     // Unit scales: a plain e4m3 x e4m3 contraction with one accumulation phase per tile.
     // No recipe of the layer uses it; it is the same-dtype ceiling the block-scaled

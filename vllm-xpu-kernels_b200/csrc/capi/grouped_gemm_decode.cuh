@@ -8,18 +8,19 @@
 // 4 KB of tokens from L2, so almost every byte in flight is a weight byte, and the tile
 // count (experts x feature tiles x token chunks) is large enough to balance 148 SMs.
 //
-// Measured on the DeepSeek-V3 shape with 1..256 tokens: no faster than the 128-row-tile
-// kernel (both stream weights at 3.3-5.0 TB/s; an L2 prefetch cursor ahead of the loads
-// made either slower), and slower once experts need several 32-token chunks.  It is kept
-// as an explicit option (a_scale_layout = K-block-major), not as the default.
+// Measured on the DeepSeek-V3 shape: with all scales of a tile staged in shared memory and
+// the output quantised in the epilogue, a layer of 1..32 tokens is 4-6 % faster on this
+// kernel than on the 128-row-tile kernel; from about four rows per expert on it is slower
+// (hot experts need several 32-token chunks, each streaming the weights again).  Callers
+// select it with the activation-scale layout code.
 //
 //   accumulator (tensor memory): lanes = output features, columns = tokens
 //   per 128 of K:  acc[f][t] += a_scale[kb][t] * b_scale[kb][f/128] * partial[f][t]
 //   epilogue:      store (+bias) or silu(gate)*up, written token-major so that the 32
 //                  lanes of a warp store 32 neighbouring features of one token.
 //
-// Activation scales are taken K-block-major ([K/128, R]) so that the 32 tokens of a tile
-// are contiguous for each K block.  Warp roles, mbarrier protocol and the bounded waits
+// Activation scales are taken K-block-major ([K/128, R]) or row-major ([R, K/128]); either
+// way they are read once per tile into shared memory.  Warp roles, mbarrier protocol and the bounded waits
 // are those of the prefill kernel (grouped_gemm.cu).
 // (included by grouped_gemm.cu inside its translation-unit-local namespace)
 
@@ -31,7 +32,9 @@ constexpr int kTokBytes = kNTok * 128;
 constexpr int kMaxExperts = 1024;
 
 struct DecodeParams {
-  const float* a_scale_t;  // [K/128, R] K-block-major
+  const float* a_scale_t;  // [K/128, R] K-block-major, or [R, K/128] when a_row_major
+  int a_row_major;
+  float* d_scale;          // [R, N_out/128] when D is e4m3 (gated epilogue only)
   const float* b_scale;    // [E, K/128, N/128]
   const void* bias;
   int bias_dtype;
@@ -124,6 +127,7 @@ struct alignas(8) DecodeBarriers {
   uint64_t tfull[4];
   uint64_t tempty[4];
   uint64_t sfree, sready;  // hand-over of the staged-scales buffer between tiles (4 reader warps)
+  uint64_t qready;         // quantising epilogue: every warp's per-token maxima are in shared memory
 };
 
 // GATED: two weight tiles per stage (gate features f, up features N/2 + f), epilogue
@@ -151,6 +155,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
   __shared__ DecodeBarriers bars;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float qmax[4][kNTok];  // quantising epilogue: per reader warp, per token
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -175,6 +180,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
     }
     mbar_init(&bars.sfree, 4);
     mbar_init(&bars.sready, 4);
+    mbar_init(&bars.qready, 4);
     mbar_fence_init();
     prefetch_tensormap(&map_tok);
     prefetch_tensormap(&map_w);
@@ -256,6 +262,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
     int buf = 0;
     uint32_t buf_phase = 0;
     uint32_t tile_parity = 0;
+    uint32_t quant_parity = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
       const DecodeTile tc = decode_tile(sched, t);
@@ -283,9 +290,10 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
         const int rt = threadIdx.x - 128;
         for (int i = rt; i < num_kb * kNTok; i += 128) {
           const int j = i & (kNTok - 1);
-          sa_s[i] = j < tc.rows_valid
-                        ? p.a_scale_t[static_cast<int64_t>(i / kNTok) * p.R + tc.row_start + j]
-                        : 0.f;
+          const int kb = i / kNTok;
+          sa_s[i] = j >= tc.rows_valid ? 0.f
+                    : p.a_row_major    ? p.a_scale_t[static_cast<int64_t>(tc.row_start + j) * num_kb + kb]
+                                       : p.a_scale_t[static_cast<int64_t>(kb) * p.R + tc.row_start + j];
         }
         for (int i = rt; i < 2 * num_kb; i += 128)
           sb_s[i] = sb_ptr[(i >> 1) * nb_count + ((i & 1) ? nb_u : nb_g)];
@@ -325,23 +333,59 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
       }
       if (!ok) break;
       const int f = f0 + f_local;
-      if (f < n_out) {
-        float bg = 0.f, bu = 0.f;
-        if (p.bias) {
-          bg = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(tc.expert) * p.N + f);
-          if (GATED) bu = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(tc.expert) * p.N + p.N / 2 + f);
+      float bg = 0.f, bu = 0.f;
+      if (p.bias && f < n_out) {
+        bg = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(tc.expert) * p.N + f);
+        if (GATED) bu = load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(tc.expert) * p.N + p.N / 2 + f);
+      }
+#pragma unroll
+      for (int j = 0; j < kNTok; ++j) {
+        float v = accg[j] + bg;
+        if (GATED) {
+          const float u = accu[GATED ? j : 0] + bu;
+          v = v * fast_sigmoid(v) * u;
         }
+        accg[j] = v;
+      }
+      if (GATED && p.d_dtype == B200MOE_E4M3) {
+        // Per-token-group-128 quantisation: the tile's 128 features are one group of each of
+        // its tokens.  Per token: maximum over the warp's 32 features by shuffles, over the
+        // four warps through shared memory, then one e4m3 byte per (token, feature).
 #pragma unroll
         for (int j = 0; j < kNTok; ++j) {
           if (j < tc.rows_valid) {
-            float v = accg[j] + bg;
-            if (GATED) {
-              const float u = accu[GATED ? j : 0] + bu;
-              v = v * fast_sigmoid(v) * u;
-            }
-            store16(p.D, p.d_dtype, static_cast<int64_t>(tc.row_start + j) * p.ldd + f, v);
+            float m = f < n_out ? fabsf(accg[j]) : 0.f;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+            if (lane == 0) qmax[quad][j] = m;
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.qready);
+        ok = mbar_wait(&bars.qready, quant_parity, abort_p);
+        if (!ok) break;
+        quant_parity ^= 1u;
+        uint8_t* out = reinterpret_cast<uint8_t*>(p.D);
+#pragma unroll
+        for (int j = 0; j < kNTok; ++j) {
+          if (j < tc.rows_valid) {
+            const float amax = fmaxf(fmaxf(qmax[0][j], qmax[1][j]), fmaxf(qmax[2][j], qmax[3][j]));
+            const float sc = fmaxf(amax * (1.0f / 448.0f), 1.0f / (448.0f * 512.0f));
+            const int64_t row = tc.row_start + j;
+            if (f < n_out) {
+              const float q = fmaxf(-448.0f, fminf(accg[j] * (1.0f / sc), 448.0f));
+              out[row * p.ldd + f] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3));
+            }
+            if (f_local == 0) p.d_scale[row * (n_out / 128) + tc.f_tile] = sc;
+          }
+        }
+        // qmax is rewritten by the next tile only after every warp passed that tile's
+        // scale hand-over, i.e. after it finished reading here
+      } else if (f < n_out) {
+#pragma unroll
+        for (int j = 0; j < kNTok; ++j)
+          if (j < tc.rows_valid)
+            store16(p.D, p.d_dtype, static_cast<int64_t>(tc.row_start + j) * p.ldd + f, accg[j]);
       }
     }
   }
@@ -369,6 +413,8 @@ int launch_decode(const b200moe_gemm_args& a, cudaStream_t st) {
   if (rc != B200MOE_OK) return rc;
   DecodeParams p;
   p.a_scale_t = a.a_scale;
+  p.a_row_major = a.a_scale_layout == B200MOE_A_SCALE_ROW_MAJOR_DECODE;
+  p.d_scale = a.d_scale;
   p.b_scale = reinterpret_cast<const float*>(a.b_scale);
   p.bias = a.bias;
   p.bias_dtype = a.bias_dtype;
@@ -399,12 +445,14 @@ int launch_decode(const b200moe_gemm_args& a, cudaStream_t st) {
 }
 
 // Entry used by b200moe_grouped_gemm when the caller asks for the decode form
-// (a_scale_layout = K-block-major).
+// (a_scale_layout = K-block-major, or row-major with the decode selector).
 int grouped_gemm_decode(const b200moe_gemm_args& a, cudaStream_t st) {
   if (a.recipe != B200MOE_RECIPE_FP8_BLOCK || a.a_dtype != B200MOE_E4M3 || !a.a_scale || !a.b_scale)
     return B200MOE_UNSUPPORTED;
   if (a.K % 128 || a.N % 128 || a.E > kMaxExperts) return B200MOE_INVALID_ARG;
-  if (a.d_dtype != B200MOE_BF16 && a.d_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
+  const bool quant_out = a.d_dtype == B200MOE_E4M3;
+  if (!quant_out && a.d_dtype != B200MOE_BF16 && a.d_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
+  if (quant_out && (a.epilogue != B200MOE_EPI_SILU_MUL || !a.d_scale)) return B200MOE_UNSUPPORTED;
   if (a.d_row_ptr) return B200MOE_UNSUPPORTED;
   if (a.epilogue == B200MOE_EPI_STORE) return launch_decode<false>(a, st);
   if (a.epilogue == B200MOE_EPI_SILU_MUL) {

@@ -43,6 +43,7 @@ except ImportError as e:  # the class below then raises on construction
 
 EPI_STORE, EPI_SILU_MUL, EPI_SWIGLU_OAI = 0, 1, 2
 B_LAYOUT_KN, B_LAYOUT_NK = 0, 1
+A_SCALE_ROW_MAJOR_DECODE = 2   # row-major activation scales + the decode-regime GEMM kernel
 
 
 def _get_weights_dtype(weight, scales):
@@ -206,7 +207,8 @@ class XpuFusedMoe:
             return
 
         if (self.is_block_fp8 and row_destinations is None and self._decode_regime(num_rows * k)
-                and self.activation == "silu" and not (self.gemm1_clamp_limit or 0) > 0):
+                and self.activation == "silu" and not (self.gemm1_clamp_limit or 0) > 0
+                and self.inter_size % 128 == 0):
             return self._apply_decode(output, hidden_states, topk_weights, topk_ids, expert_map,
                                       a1q_scale)
         if self.is_block_fp8 and a1q_scale is None:
@@ -306,47 +308,48 @@ class XpuFusedMoe:
         return gemm2_out
 
     def _decode_regime(self, routed_rows: int) -> bool:
-        """Opt-in (B200MOE_DECODE_PATH=1): run the GEMMs with the weights on the M side of the
-        MMA, 32 tokens per tile.  Measured no faster than the default kernels at 1..256
-        tokens on the DeepSeek-V3 shape, so it is not selected automatically."""
-        return os.environ.get("B200MOE_DECODE_PATH") == "1"
+        """Whether to run the two GEMMs on the decode-regime kernel (weights on the M side of
+        the MMA, 32 tokens per tile).  With at most about one routed row per local expert it is
+        4-6 % faster end to end on the DeepSeek-V3 shape (1..32 tokens); from a few rows per
+        expert on, hot experts need several 32-token chunks that each stream the weights again,
+        and the 128-row-tile kernel wins.  B200MOE_DECODE_PATH=0/1 overrides."""
+        forced = os.environ.get("B200MOE_DECODE_PATH")
+        if forced is not None:
+            return forced == "1"
+        return routed_rows <= self.num_experts
 
     def _apply_decode(self, output, hidden_states, topk_weights, topk_ids, expert_map, a1q_scale):
-        from .moe_utils import dequant_fp8_block_act
+        """Same sequence of launches as the default path, with the two grouped GEMMs on the
+        decode-regime kernel (weights on the M side of the MMA, 32 tokens per tile); the first
+        one quantises its output per token per 128 columns in its epilogue."""
+        from .moe_utils import quant_fp8_block_act
         T, H = hidden_states.shape
         k = topk_ids.shape[1]
         R, I, E = T * k, self.inter_size, self.num_experts
         dev = hidden_states.device
-        if a1q_scale is not None:  # rare here: bring the few rows back to 16 bit first
-            hidden_states = dequant_fp8_block_act(hidden_states, a1q_scale).to(output.dtype)
+        if a1q_scale is None:
+            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states)
         if expert_map is None and self.ep_size > 1:
             expert_map = self.expert_map
         remapped = torch.empty((R, H), dtype=hidden_states.dtype, device=dev)
+        remapped_scales = torch.empty((R, a1q_scale.shape[1]), dtype=a1q_scale.dtype, device=dev)
         rows_per_expert = torch.zeros((E,), dtype=torch.int32, device=dev)
         row_map = torch.empty((T, k), dtype=torch.int32, device=dev)
         with self._stage("remap"):
-            torch.ops._moe_C.remap_hidden_states(hidden_states, None, remapped, None, expert_map,
-                                                 rows_per_expert, row_map, topk_ids,
+            torch.ops._moe_C.remap_hidden_states(hidden_states, a1q_scale, remapped, remapped_scales,
+                                                 expert_map, rows_per_expert, row_map, topk_ids,
                                                  self.total_experts_num, self.local_experts_num)
-
-        def quant_kblock_major(x):
-            q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=dev)
-            s = torch.empty((x.shape[1] // 128, x.shape[0]), dtype=torch.float32, device=dev)
-            torch.ops._C.per_token_group_fp8_quant(x, q, s.t(), 128, 1e-10, -448.0, 448.0, False,
-                                                   False, False)
-            return q, s
-
         gemm = torch.ops._xpu_C.b200_grouped_gemm
-        xq, xs = quant_kblock_major(remapped)
-        act = torch.empty((R, I), dtype=output.dtype, device=dev)
+        act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
+        act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
         with self._stage("gemm1"):
-            gemm(xq, xs, self.w13, self.gemm1_wei_scales, self.w13_bias, act, rows_per_expert, 2 * I,
-                 H, E, EPI_SILU_MUL, B_LAYOUT_KN, 1.702, 7.0, None, None, 1)
-        aq, as_ = quant_kblock_major(act)
+            gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias, act_q,
+                 rows_per_expert, 2 * I, H, E, EPI_SILU_MUL, B_LAYOUT_KN, 1.702, 7.0, act_s, None,
+                 A_SCALE_ROW_MAJOR_DECODE)
         gemm2_out = torch.empty((R, H), dtype=output.dtype, device=dev)
         with self._stage("gemm2"):
-            gemm(aq, as_, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out, rows_per_expert, H,
-                 I, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None, None, 1)
+            gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out, rows_per_expert,
+                 H, I, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None, None, A_SCALE_ROW_MAJOR_DECODE)
         with self._stage("gather"):
             torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
 
