@@ -33,7 +33,7 @@ import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one w13 GEMM launch, from the ncu capture
 # summarised under profiles/ (captured on a 2-expert slice, scaled by the expert count).
-TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 267.66e6}  # profiles/grouped_gemm_fp8_c1_small.md
+TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 269.44e6}  # profiles/grouped_gemm_fp8_c1_small.md
 
 # The benchmark configurations (shapes of BASELINE.json's configs 0-3).
 CONFIGS = {
