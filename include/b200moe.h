@@ -345,6 +345,55 @@ int b200moe_expand_weights(int recipe, const void* B, int b_dtype,
                            void* out, int out_dtype, int E, int N, int K,
                            void* stream);
 
+/* ---- block-scaled (MX) grouped GEMM -------------------------------------------
+ * The tensor-core form of the reference's MXFP4 weight recipe
+ * (csrc/xpu/grouped_gemm/xe_2/gemm_xe2.hpp:249-504 `xe_gemm_4bits`, scale decode
+ * :426-434; weight layout csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:281-301):
+ * B stays e2m1 [E,N,K/2] in memory; A is MXFP8 (e4m3 with one e8m0 scale per 32
+ * of K, the quantisation vllm_xpu_kernels/moe_utils.py:84-109 applies to
+ * activations: per_token_group_fp8_quant with group 32 and scale_ue8m0); both
+ * scale sets are applied inside tcgen05.mma kind::mxf8f6f4.block_scale. */
+
+/* Bytes of the rearranged weight scales for b200moe_grouped_gemm_mx. */
+size_t b200moe_mx_weight_scales_bytes(int E, int N, int K);
+/* scales: e8m0 bytes [E,N,K/32] as the operator takes them -> `out` in the order
+ * the tensor core reads them (once per layer).  Plays the part of
+ * reorder_mxfp_scales (csrc/moe/reorder_mxfp_scales.cpp:174-234) for the weight
+ * side. */
+int b200moe_mx_prepare_weight_scales(const uint8_t* scales, int E, int N, int K,
+                                     uint8_t* out, void* stream);
+
+/* MXFP8 quantisation of activations: out_q e4m3 [R,N]; out_sf e8m0 bytes, scale
+ * of columns [32g, 32g+32) of row r at out_sf[r*sf_pitch + g] (sf_pitch a multiple
+ * of 16 and >= 16*ceil(N/512); bytes past N/32 are not written).
+ * scale = 2^ceil(log2(max(max(amax,1e-10)/448, 1/(448*512)))), q = e4m3(x / scale):
+ * per_token_group_fp8_quant(group 32, scale_ue8m0) with the scale stored as its
+ * exponent byte (vllm_xpu_kernels/moe_utils.py:84-109). */
+int b200moe_quant_mxfp8(const void* in, int dtype, void* out_q, uint8_t* out_sf,
+                        int64_t R, int N, int64_t sf_pitch, void* stream);
+
+typedef struct b200moe_mx_gemm_args {
+  int epilogue;      /* B200MOE_EPI_STORE or B200MOE_EPI_SWIGLU_OAI                 */
+  int d_dtype;       /* BF16/F16; or E4M3 with d_sf (SWIGLU_OAI only): the result
+                        leaves the GEMM as MXFP8, ready to be the next A          */
+  const void* A;     /* e4m3 [R,K], rows grouped by expert                         */
+  const uint8_t* a_sf; /* e8m0 [R, a_sf_pitch]                                      */
+  int64_t a_sf_pitch;  /* multiple of 16, >= 16*ceil(K/512)                          */
+  const void* B;     /* e2m1 pairs [E,N,K/2], 32-byte aligned                      */
+  const uint8_t* b_sf; /* from b200moe_mx_prepare_weight_scales                      */
+  const void* bias;  /* [E,N] of bias_dtype or NULL                                */
+  int bias_dtype;
+  void* D;           /* [R,N], or [R,N/2] for SWIGLU_OAI                           */
+  uint8_t* d_sf;     /* e8m0 [R, d_sf_pitch] when d_dtype == E4M3                  */
+  int64_t d_sf_pitch;
+  const int32_t* rows_per_expert; /* i32 [E], device                               */
+  int64_t R;
+  int N, K, E;       /* K a multiple of 64, >= 128                                 */
+  float alpha, limit;
+} b200moe_mx_gemm_args;
+
+int b200moe_grouped_gemm_mx(const b200moe_mx_gemm_args* args, void* stream);
+
 /* Plain CUDA-core evaluation of the same contract, one thread per output
  * element, for checking the tensor-core path on sizes a CPU cannot reach. */
 int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* stream);

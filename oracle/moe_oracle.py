@@ -422,6 +422,21 @@ def per_token_group_fp8_quant(x, group_size=128, eps=1e-10, scale_ue8m0=False,
     return q, s
 
 
+def quant_mxfp8_act(x):
+    """MXFP8 activations the way the reference quantises them
+    (vllm_xpu_kernels/moe_utils.py:84-109: per_token_group_fp8_quant with group
+    32 and scale_ue8m0, the scale then cast to e8m0): (e4m3 [M, N], e8m0 bytes
+    u8 [M, N/32])."""
+    q, s = per_token_group_fp8_quant(x, 32, scale_ue8m0=True)
+    return q, (torch.log2(s).round().to(torch.int32) + 127).to(torch.uint8)
+
+
+def dequant_mxfp8_act(q, sf_u8):
+    """(vllm_xpu_kernels/moe_utils.py:71-75) fp32 = e4m3 * 2^(byte - 127) per 32 columns."""
+    M, N = q.shape
+    return (q.float().view(M, N // 32, 32) * e8m0_to_f32(sf_u8[:, :N // 32]).unsqueeze(-1)).view(M, N)
+
+
 def e2m1_code(x: torch.Tensor) -> torch.Tensor:
     """4-bit code of the nearest e2m1 value; a value exactly between two
     code points goes to the smaller magnitude (strict '>' compares,

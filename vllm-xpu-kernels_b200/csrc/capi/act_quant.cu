@@ -282,6 +282,44 @@ __global__ void __launch_bounds__(256) group_quant_mxfp4_kernel(
   }
 }
 
+// MXFP8: e4m3 values with one e8m0 scale per 32 columns (4 lanes of 8 values).  The scale is
+// the smallest power of two >= max(amax, 1e-10) / 448 (not below 1 / (448 * 512)), found on
+// the bits of the float, and stored as its biased exponent.
+template <typename T>
+__global__ void __launch_bounds__(256) quant_mxfp8_kernel(const T* __restrict__ in,
+                                                           uint8_t* __restrict__ out_q,
+                                                           uint8_t* __restrict__ out_sf, int64_t R,
+                                                           int N, int64_t sf_pitch) {
+  const int64_t chunks_per_row = N / kVec;
+  const int64_t total = R * chunks_per_row;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t base = blockIdx.x * static_cast<int64_t>(blockDim.x); base < total; base += stride) {
+    const int64_t c = base + threadIdx.x;
+    const bool live = c < total;
+    const int64_t r = live ? c / chunks_per_row : 0;
+    const int col = live ? static_cast<int>(c % chunks_per_row) * kVec : 0;
+    float x[kVec];
+    float amax = 0.f;
+    if (live) {
+      fetch8<T, false>(in, r, col, N, x);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) amax = fmaxf(amax, fabsf(x[i]));
+    }
+    amax = seg_max<4>(amax);
+    const float s0 = fmaxf(fmaxf(amax, 1e-10f) * (1.0f / 448.0f), 1.0f / (448.0f * 512.0f));
+    uint32_t bits = __float_as_uint(s0);
+    uint32_t e = bits >> 23;
+    if (bits & 0x7FFFFFu) ++e;
+    if (!live) continue;
+    if ((threadIdx.x & 3) == 0) out_sf[r * sf_pitch + col / 32] = static_cast<uint8_t>(e);
+    const float inv = 1.0f / __uint_as_float(e << 23);
+    uint8_t q[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) q[i] = f32_to_e4m3(fmaxf(-448.f, fminf(x[i] * inv, 448.f)));
+    *reinterpret_cast<uint2*>(out_q + r * N + col) = *reinterpret_cast<uint2*>(q);
+  }
+}
+
 inline int stream_grid(int64_t work_items, int threads) {
   int64_t blocks = (work_items + threads - 1) / threads;
   const int64_t cap = static_cast<int64_t>(kNumSMs) * 8;
@@ -426,5 +464,18 @@ extern "C" int b200moe_silu_mul_mxfp4_quant(const void* in, int dtype, uint8_t* 
         <<<stream_grid(R * (d / kVec), 256), 256, 0, as_stream(stream)>>>(
             reinterpret_cast<const scalar_t*>(in), out_q, out_s, R, d, eps, d / 32, 1);
     return launch_status("silu_mul_mxfp4_quant_kernel");
+  });
+}
+
+extern "C" int b200moe_quant_mxfp8(const void* in, int dtype, void* out_q, uint8_t* out_sf,
+                                   int64_t R, int N, int64_t sf_pitch, void* stream) {
+  if (R < 0 || N <= 0 || N % 32 || sf_pitch < N / 32) return B200MOE_INVALID_ARG;
+  if (R == 0) return B200MOE_OK;
+  if (!in || !out_q || !out_sf) return B200MOE_INVALID_ARG;
+  return B200MOE_DISPATCH_FLOAT(dtype, [&] {
+    quant_mxfp8_kernel<scalar_t><<<stream_grid(R * (N / kVec), 256), 256, 0, as_stream(stream)>>>(
+        reinterpret_cast<const scalar_t*>(in), reinterpret_cast<uint8_t*>(out_q), out_sf, R, N,
+        sf_pitch);
+    return launch_status("quant_mxfp8_kernel");
   });
 }

@@ -972,6 +972,7 @@ __global__ void dequant_mxfp4_kernel(const uint8_t* __restrict__ w, const uint8_
 }
 
 #include "grouped_gemm_decode.cuh"
+#include "grouped_gemm_mx.cuh"
 
 }  // namespace
 }  // namespace b200moe
@@ -1112,6 +1113,54 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   if (pair) return launch_epi<KIND_F16, true, false, 256, 6, true>(a, B, a.a_dtype, st);
   if (wide) return launch_epi<KIND_F16, true, false, 256, 4>(a, B, a.a_dtype, st);
   return launch_epi<KIND_F16, true, false, 128, 6>(a, B, a.a_dtype, st);
+}
+
+extern "C" size_t b200moe_mx_weight_scales_bytes(int E, int N, int K) {
+  if (E <= 0 || N <= 0 || K <= 0) return 0;
+  const size_t num_kb = (static_cast<size_t>(K) + kMxBK - 1) / kMxBK;
+  const size_t atoms = (static_cast<size_t>(N) + 127) / 128 + 1;
+  return static_cast<size_t>(E) * num_kb * atoms * kMxAtomBytes;
+}
+
+extern "C" int b200moe_mx_prepare_weight_scales(const uint8_t* scales, int E, int N, int K,
+                                                uint8_t* out, void* stream) {
+  if (!scales || !out || E <= 0 || N <= 0 || K < kMxBK || K % 32) return B200MOE_INVALID_ARG;
+  const int64_t words = static_cast<int64_t>(b200moe_mx_weight_scales_bytes(E, N, K) / 4);
+  int64_t blocks = (words + 255) / 256;
+  if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;
+  mx_prepare_weight_scales_kernel<<<static_cast<int>(blocks), 256, 0, as_stream(stream)>>>(
+      scales, out, E, N, K, words);
+  return launch_status("mx_prepare_weight_scales_kernel");
+}
+
+extern "C" int b200moe_grouped_gemm_mx(const b200moe_mx_gemm_args* a, void* stream) {
+  if (!a) return B200MOE_INVALID_ARG;
+  if (a->R < 0 || a->N <= 0 || a->K < kMxBK || a->E <= 0 || a->E > kMaxExpertsSmem)
+    return B200MOE_INVALID_ARG;
+  if (a->K % 64 || a->N % 8) return B200MOE_UNSUPPORTED;  // packed 4-bit rows: 32-byte pitch
+  if (a->R == 0) return B200MOE_OK;
+  if (a->R >= (1ll << 31)) return B200MOE_UNSUPPORTED;
+  if (!a->A || !a->a_sf || !a->B || !a->b_sf || !a->D || !a->rows_per_expert) return B200MOE_INVALID_ARG;
+  if (reinterpret_cast<uintptr_t>(a->B) % 32 || reinterpret_cast<uintptr_t>(a->A) % 16 ||
+      reinterpret_cast<uintptr_t>(a->a_sf) % 16 || reinterpret_cast<uintptr_t>(a->b_sf) % 16)
+    return B200MOE_INVALID_ARG;
+  const int64_t groups = (a->K + 511) / 512;
+  if (a->a_sf_pitch % 16 || a->a_sf_pitch < groups * 16) return B200MOE_INVALID_ARG;
+  cudaStream_t st = as_stream(stream);
+  if (a->epilogue == B200MOE_EPI_STORE) {
+    if (a->d_dtype != B200MOE_BF16 && a->d_dtype != B200MOE_F16) return B200MOE_UNSUPPORTED;
+    return launch_mx<MxConfig<192, B200MOE_EPI_STORE, 4>>(*a, st);
+  }
+  if (a->epilogue == B200MOE_EPI_SWIGLU_OAI) {
+    if (a->N % 2) return B200MOE_INVALID_ARG;
+    if (a->d_dtype == B200MOE_E4M3) {
+      if (!a->d_sf || (a->N / 2) % 32 || a->d_sf_pitch < (a->N / 2) / 32) return B200MOE_INVALID_ARG;
+    } else if (a->d_dtype != B200MOE_BF16 && a->d_dtype != B200MOE_F16) {
+      return B200MOE_UNSUPPORTED;
+    }
+    return launch_mx<MxConfig<192, B200MOE_EPI_SWIGLU_OAI, 4>>(*a, st);
+  }
+  return B200MOE_UNSUPPORTED;
 }
 
 extern "C" int b200moe_grouped_gemm_check(const b200moe_gemm_args* args, void* stream) {

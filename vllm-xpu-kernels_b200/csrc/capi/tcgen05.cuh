@@ -269,6 +269,71 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
       : "memory");
 }
 
+// ---- block-scaled MMA (kind::mxf8f6f4) ---------------------------------------------------
+// D += (A * SFA) x (B * SFB): one e8m0 scale per row per 32 elements of K, for both
+// operands, applied inside the tensor core.  The scales live in tensor memory: a
+// 128-row operand tile keeps the four scales of one 128-wide K block as the four
+// bytes of a 32-bit word, row r in lane (r % 32) of column (r / 32), and every lane
+// quadrant holds a copy.  tcgen05.cp with the 32x128b.warpx4 shape produces exactly
+// that from 512 bytes of shared memory laid out as byte[(r % 32) * 16 + (r / 32) * 4 + k].
+
+// Instruction descriptor.  a_fmt / b_fmt: 0 = e4m3, 1 = e5m2, 5 = e2m1 (one element per
+// byte container in shared memory).  b_mn_major only for the 8-bit formats.  sf_a / sf_b:
+// which byte of the scale words this instruction uses (the K sub-block inside the stage).
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t a_fmt, uint32_t b_fmt,
+                                                     uint32_t b_mn_major, uint32_t M, uint32_t N,
+                                                     uint32_t sf_a, uint32_t sf_b) {
+  return (sf_b << 4) | (a_fmt << 7) | (b_fmt << 10) | (b_mn_major << 16) | ((N >> 3) << 17) |
+         (1u << 23)  // scale format e8m0
+         | ((M >> 4) << 24) | (sf_a << 29);
+}
+
+__device__ __forceinline__ void mma_mxf8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem),
+        "r"(sfb_tmem)
+      : "memory");
+}
+
+// Shared-memory descriptor without swizzle for rows of 16 bytes stored back to back
+// (8-row groups 128 bytes apart): the source of a scale-factor copy.
+__device__ __forceinline__ uint64_t make_sdesc_rows16(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;  // stride between 8-row groups
+  d |= static_cast<uint64_t>(1) << 46;         // descriptor version
+  return d;
+}
+
+// 32 rows x 16 bytes of shared memory -> 4 columns of tensor memory, lanes 0..31,
+// replicated into all four lane quadrants.  Ordered with the MMAs issued after it by
+// the same thread; completion is covered by the next tcgen05.commit.
+__device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc)
+               : "memory");
+}
+
+// Makes this thread's earlier generic-proxy writes to shared memory visible to the
+// asynchronous proxy (TMA, tcgen05.cp, tcgen05.mma operand reads).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Plain bulk copy global -> shared (no tensor map, no multicast); both addresses and the
+// size are multiples of 16 bytes.  Completion is reported to `bar` as transferred bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                          uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes),
+        "r"(smem_u32(bar))
+      : "memory");
+}
+
 // ---- CTA pairs (cta_group::2) ---------------------------------------------------------
 // Two CTAs of a cluster share one MMA: M = 256 (128 rows from each CTA's shared
 // memory), each CTA supplies half of the N columns of B and receives its 128 rows

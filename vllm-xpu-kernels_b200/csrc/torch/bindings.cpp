@@ -763,6 +763,90 @@ Tensor b200_expand_weights(const Tensor& B, const Tensor& B_scale, const std::st
   return out;
 }
 
+// ---- block-scaled (MX) grouped GEMM ------------------------------------------------
+
+// e8m0 weight scales [E, N, K/32] -> the tensor-core order (one call per layer).
+Tensor b200_mx_prepare_weight_scales(const Tensor& scales, int64_t K) {
+  TORCH_CHECK(scales.dim() == 3 && scales.is_contiguous() && scales.element_size() == 1 &&
+                  scales.size(2) * 32 == K,
+              "b200_mx_prepare_weight_scales: e8m0 scales [E, N, K/32] expected");
+  c10::cuda::CUDAGuard guard(scales.device());
+  const int E = scales.size(0), N = scales.size(1);
+  Tensor out = at::empty({static_cast<int64_t>(b200moe_mx_weight_scales_bytes(E, N, K))},
+                         scales.options().dtype(at::kByte));
+  check(b200moe_mx_prepare_weight_scales(reinterpret_cast<const uint8_t*>(scales.data_ptr()), E, N, K,
+                                         out.data_ptr<uint8_t>(), cur_stream()),
+        "b200_mx_prepare_weight_scales");
+  return out;
+}
+
+// x [R, N] -> (e4m3 [R, N], e8m0 bytes [R, pitch]) with pitch = 16 * ceil(N / 512).
+std::tuple<Tensor, Tensor> b200_quant_mxfp8(const Tensor& x) {
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.size(1) % 32 == 0,
+              "b200_quant_mxfp8: contiguous [R, N] with N a multiple of 32 expected");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t R = x.size(0), N = x.size(1);
+  const int64_t pitch = (N + 511) / 512 * 16;
+  Tensor q = at::empty({R, N}, x.options().dtype(at::kFloat8_e4m3fn));
+  Tensor sf = at::empty({R, pitch}, x.options().dtype(at::kByte));
+  check(b200moe_quant_mxfp8(x.data_ptr(), float_code(x, "b200_quant_mxfp8"), q.data_ptr(),
+                            sf.data_ptr<uint8_t>(), R, N, pitch, cur_stream()),
+        "b200_quant_mxfp8");
+  return {q, sf};
+}
+
+Tensor b200_grouped_gemm_mx(const Tensor& A, const Tensor& A_sf, const Tensor& B, const Tensor& B_sf,
+                            const OptTensor& bias, Tensor D, const OptTensor& D_sf,
+                            const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
+                            int64_t epilogue, double alpha, double limit) {
+  const char* op = "b200_grouped_gemm_mx";
+  TORCH_CHECK(A.is_contiguous() && A_sf.is_contiguous() && B.is_contiguous() && B_sf.is_contiguous() &&
+                  D.is_contiguous(),
+              op, ": contiguous tensors expected");
+  TORCH_CHECK(A.scalar_type() == at::kFloat8_e4m3fn && A.dim() == 2 && A.size(1) == K, op,
+              ": A must be float8_e4m3fn [R, K]");
+  TORCH_CHECK(A_sf.element_size() == 1 && A_sf.dim() == 2 && A_sf.size(0) == A.size(0), op,
+              ": A scales must be e8m0 bytes [R, pitch]");
+  TORCH_CHECK(B.element_size() == 1 && B.numel() == num_experts * N * (K / 2), op,
+              ": B must be packed e2m1 [E, N, K/2]");
+  TORCH_CHECK(B_sf.numel() == static_cast<int64_t>(b200moe_mx_weight_scales_bytes(num_experts, N, K)), op,
+              ": B scales must come from b200_mx_prepare_weight_scales");
+  TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
+                  rows_per_expert.numel() >= num_experts,
+              op, ": rows_per_expert must be int32 [num_experts]");
+  b200moe_mx_gemm_args a{};
+  a.epilogue = static_cast<int>(epilogue);
+  a.d_dtype = act_code(D, op);
+  a.A = A.data_ptr();
+  a.a_sf = reinterpret_cast<const uint8_t*>(A_sf.data_ptr());
+  a.a_sf_pitch = A_sf.size(1);
+  a.B = B.data_ptr();
+  a.b_sf = reinterpret_cast<const uint8_t*>(B_sf.data_ptr());
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->is_contiguous() && bias->numel() == num_experts * N, op, ": bias must be [E, N]");
+    a.bias = bias->data_ptr();
+    a.bias_dtype = float_code(*bias, op);
+  }
+  a.D = D.data_ptr();
+  if (D_sf.has_value()) {
+    TORCH_CHECK(D_sf->element_size() == 1 && D_sf->dim() == 2 && D_sf->is_contiguous() &&
+                    D_sf->size(0) == A.size(0),
+                op, ": output scales must be e8m0 bytes [R, pitch]");
+    a.d_sf = reinterpret_cast<uint8_t*>(D_sf->data_ptr());
+    a.d_sf_pitch = D_sf->size(1);
+  }
+  a.rows_per_expert = rows_per_expert.data_ptr<int>();
+  a.R = A.size(0);
+  a.N = N;
+  a.K = K;
+  a.E = num_experts;
+  a.alpha = static_cast<float>(alpha);
+  a.limit = static_cast<float>(limit);
+  c10::cuda::CUDAGuard guard(A.device());
+  check(b200moe_grouped_gemm_mx(&a, cur_stream()), op);
+  return D;
+}
+
 int64_t b200_device_status() {
   int st = 0;
   check(b200moe_device_status(cur_stream(), &st), "b200_device_status");
@@ -887,6 +971,12 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
   m.def("b200_dequant_weights(Tensor B, Tensor B_scale) -> Tensor");
   m.def("b200_expand_weights(Tensor B, Tensor B_scale, str recipe, ScalarType out_dtype) -> Tensor");
   m.def("b200_device_status() -> int");
+  m.def("b200_mx_prepare_weight_scales(Tensor scales, int K) -> Tensor");
+  m.def("b200_quant_mxfp8(Tensor x) -> (Tensor, Tensor)");
+  m.def(
+      "b200_grouped_gemm_mx(Tensor A, Tensor A_sf, Tensor B, Tensor B_sf, Tensor? bias, Tensor D, "
+      "Tensor? D_sf, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, float "
+      "alpha=1.702, float limit=7.0) -> Tensor");
 }
 
 TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CUDA, m) {
@@ -895,6 +985,9 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CUDA, m) {
   m.impl("b200_grouped_gemm_check", &b200_grouped_gemm_check);
   m.impl("b200_dequant_weights", &b200_dequant_weights);
   m.impl("b200_expand_weights", &b200_expand_weights);
+  m.impl("b200_mx_prepare_weight_scales", &b200_mx_prepare_weight_scales);
+  m.impl("b200_quant_mxfp8", &b200_quant_mxfp8);
+  m.impl("b200_grouped_gemm_mx", &b200_grouped_gemm_mx);
 }
 
 TORCH_LIBRARY_IMPL(B200MOE_NS_XPU_C, CompositeExplicitAutograd, m) {

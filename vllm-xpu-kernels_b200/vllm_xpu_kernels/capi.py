@@ -27,6 +27,16 @@ class GemmArgs(Structure):
     ]
 
 
+class MxGemmArgs(Structure):
+    _fields_ = [
+        ("epilogue", c_int), ("d_dtype", c_int), ("A", c_void_p), ("a_sf", c_void_p),
+        ("a_sf_pitch", c_int64), ("B", c_void_p), ("b_sf", c_void_p), ("bias", c_void_p),
+        ("bias_dtype", c_int), ("D", c_void_p), ("d_sf", c_void_p), ("d_sf_pitch", c_int64),
+        ("rows_per_expert", c_void_p), ("R", c_int64), ("N", c_int), ("K", c_int), ("E", c_int),
+        ("alpha", c_float), ("limit", c_float),
+    ]
+
+
 # name -> (restype, argtypes); must list every symbol include/b200moe.h declares.
 SIGNATURES = {
     "b200moe_version": (c_char_p, []),
@@ -81,6 +91,11 @@ SIGNATURES = {
     "b200moe_grouped_gemm": (c_int, [POINTER(GemmArgs), c_void_p, c_size_t, c_void_p]),
     "b200moe_dequant_weights": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                         c_void_p]),
+    "b200moe_mx_weight_scales_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200moe_mx_prepare_weight_scales": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200moe_quant_mxfp8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64,
+                                    c_void_p]),
+    "b200moe_grouped_gemm_mx": (c_int, [POINTER(MxGemmArgs), c_void_p]),
     "b200moe_grouped_gemm_check": (c_int, [POINTER(GemmArgs), c_void_p]),
     "b200moe_device_status": (c_int, [c_void_p, POINTER(c_int)]),
     "b200moe_selftest_wait_timeout": (c_int, [ctypes.c_longlong, c_void_p]),
