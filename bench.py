@@ -1,19 +1,24 @@
 """Fused-MoE layer benchmark: tokens/s of one layer pass on seeded synthetic data.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config c1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config c3]
 
 One step = routing + activation quantisation + XpuFusedMoe.apply over one batch.
-Default workload: the Mixtral-8x7B-shaped FP8 layer (T=4096, H=4096, I=14336,
-E=8, top-2, 128x128 block scales), the largest configuration that is quoted on
-one GPU.  Prints one JSON line (rank 0).
+Default workload at every N: the DeepSeek-V3-shaped FP8 layer (T=16384 tokens per GPU,
+H=7168, I=2048, 256 routed experts, grouped top-8), the configuration the 1/2/4/8-GPU
+scaling is quoted on; it fits one GPU (11.3 GB of weights), so N=1 runs the same workload
+with all experts local.  With N > 1 the experts are sharded E/N per rank and tokens stay
+data-parallel (weak scaling).  Prints one JSON line (rank 0).
 
 * ``value``  : tokens/s with inputs already in HBM, CUDA-event timed, max over ranks.
 * ``e2e``    : tokens/s through the same public calls with pinned HOST inputs
                copied in and the layer output copied back inside the timed region.
 * ``roofline``: the w13 grouped GEMM, FLOPs of one launch / its mean duration
                (CUDA events around that launch inside the timed steps).
+* ``parity`` : after the timed region, 16 tokens of rank 0 checked against the CPU oracle.
 * ``cpu_baseline``: the CPU oracle (a port of the reference's torch path) on a
-               bounded token sample, on this host's cores.
+               bounded token sample, on this host's cores (N=1 only).
+* ``other_configs`` / ``decode`` (N=1 only): short runs of the Mixtral-shaped FP8 layer,
+  the gpt-oss-shaped MXFP4 layer and the decode sweep (T = 1..256, Zipf-skewed routing).
 
 ``--impl reference`` times only that CPU path (rank 0; other ranks exit).
 """
@@ -31,11 +36,13 @@ sys.path.insert(0, os.path.join(ROOT, "vllm-xpu-kernels_b200"))
 
 import torch  # noqa: E402
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one w13 GEMM launch, from the ncu capture
-# summarised under profiles/ (captured on a 2-expert slice, scaled by the expert count).
-TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 269.44e6}  # profiles/grouped_gemm_fp8_c1_small.md
+# dram__bytes_read.sum + dram__bytes_write.sum of one w13 GEMM launch: measured with ncu on
+# a slice of the experts and scaled by the expert count (traffic grows with the experts
+# touched; every expert's weights are streamed once).
+TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 269.44e6}
 
-# The benchmark configurations (shapes of BASELINE.json's configs 0-3).
+# The benchmark configurations (shapes of the four layer configurations; the fifth, the
+# decode sweep, is c3 with few tokens and skewed routing).
 CONFIGS = {
     "c0": dict(T=64, H=1024, I=2048, E=8, k=2, recipe="bf16", routing="softmax", activation="silu",
                bias=False, name="tiny bf16 layer"),
@@ -45,13 +52,15 @@ CONFIGS = {
                     "per-token-group-128 FP8 activations, softmax top-2"),
     "c2": dict(T=8192, H=2880, I=2880, E=128, k=4, recipe="mxfp4", routing="softmax",
                activation="swigluoai", bias=True,
-               name="gpt-oss-120b-shaped layer, MXFP4 weights (expanded to bf16 once, W4A16), bf16 "
-                    "biases, SwigluOAI, softmax top-4"),
+               name="gpt-oss-120b-shaped layer, MXFP4 weights kept 4-bit (e2m1 + e8m0 per 32), MXFP8 "
+                    "activations, block-scaled tcgen05 MMA, bf16 biases, SwigluOAI, softmax top-4"),
     "c3": dict(T=16384, H=7168, I=2048, E=256, k=8, recipe="fp8block", routing="grouped",
-               activation="silu", bias=False, n_group=8, topk_group=4, scale=2.5,
-               name="DeepSeek-V3-shaped routed experts, FP8 block-scaled, sigmoid + bias grouped "
-                    "top-8 (8 groups, 4 kept), scale 2.5; shared expert not included"),
+               activation="silu", bias=False, n_group=8, topk_group=4, scale=2.5, shared=True,
+               name="DeepSeek-V3-shaped layer, 256 routed experts, FP8 block-scaled, sigmoid + bias "
+                    "grouped top-8 (8 groups, 4 kept), scale 2.5; value = routed experts, the shared "
+                    "expert is timed separately (with_shared_expert)"),
 }
+DECODE_TOKENS = (1, 8, 32, 128, 256)
 
 
 def load_peaks():
@@ -130,11 +139,14 @@ def _quant_mxfp4(w):
     return (code[:, 1::2] << 4) | code[:, 0::2], (e + 127).to(torch.uint8)
 
 
+SHARED_EXPERT = -1   # pseudo expert id of the shared expert in make_device_layer
+
+
 def make_device_layer(cfg, dev, seed=0, experts=None):
-    """Synthetic weights generated on the device (the CPU generator of the oracle is too slow
-    at GB sizes): N(0, 1/fan_in), quantised per recipe, in the layouts the operators take.
-    Each expert has its own seed, so a rank that owns a slice of the experts builds only those."""
-    import vllm_xpu_kernels._C  # noqa: F401
+    """Synthetic weights generated on `dev` (the CPU generator of the oracle is too slow at GB
+    sizes): N(0, 1/fan_in), quantised per recipe, in the layouts the operators take.  Each
+    expert has its own seed, so a rank that owns a slice of the experts builds only those, and
+    any rank can rebuild any expert (the parity check does)."""
     H, I, recipe = cfg["H"], cfg["I"], cfg["recipe"]
     experts = list(range(cfg["E"])) if experts is None else list(experts)
 
@@ -158,9 +170,12 @@ def make_device_layer(cfg, dev, seed=0, experts=None):
     w2, s2 = build(I, H, 2)
     out = dict(w13=w13, w13_scale=s13, w2=w2, w2_scale=s2, w13_bias=None, w2_bias=None)
     if cfg["bias"]:
-        g = torch.Generator(device=dev).manual_seed(seed + 17)
-        out["w13_bias"] = (torch.randn(len(experts), 2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16)
-        out["w2_bias"] = (torch.randn(len(experts), H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+        b13, b2 = [], []
+        for e in experts:
+            g = torch.Generator(device=dev).manual_seed(seed * 100003 + e * 7 + 5)
+            b13.append((torch.randn(2 * I, generator=g, device=dev) * 0.02).to(torch.bfloat16))
+            b2.append((torch.randn(H, generator=g, device=dev) * 0.02).to(torch.bfloat16))
+        out["w13_bias"], out["w2_bias"] = torch.stack(b13), torch.stack(b2)
     return out
 
 
@@ -174,10 +189,14 @@ def make_inputs(cfg, T, seed):
     return x, logits
 
 
+def score_bias(cfg):
+    return torch.randn(cfg["E"], generator=torch.Generator().manual_seed(3)) * 0.01
+
+
 class Layer:
     """Routing + quantisation + XpuFusedMoe.apply, the sequence a caller runs per batch."""
 
-    def __init__(self, cfg, weights, T, dev, group=None):
+    def __init__(self, cfg, weights, T, dev, group=None, shared_weights=None):
         from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
         from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
         self.cfg, self.T, self.dev = cfg, T, dev
@@ -188,6 +207,12 @@ class Layer:
             w13, w2 = w13.view(torch.float4_e2m1fn_x2), w2.view(torch.float4_e2m1fn_x2)
         self.moe = XpuFusedMoe(w13, weights["w13_scale"], weights["w13_bias"], w2, weights["w2_scale"],
                                weights["w2_bias"], cfg["k"], cfg["activation"], E_loc)
+        self.shared = None
+        if shared_weights is not None:
+            s = shared_weights
+            self.shared = XpuFusedMoe(s["w13"], s["w13_scale"], None, s["w2"], s["w2_scale"], None, 1,
+                                      cfg["activation"], 1)
+        self.use_shared = False
         self.ep = None
         self.ep_backend = None
         if group is not None:
@@ -195,9 +220,11 @@ class Layer:
             self.ep_backend = os.environ.get("B200MOE_EP", "peer")
             if self.ep_backend == "peer":
                 fp8 = cfg["recipe"] == "fp8block"
-                self.ep = PeerExpertParallel(group, self.moe, T, cfg["k"], cfg["H"],
-                                             cfg["H"] * (1 if fp8 else 2),
-                                             (cfg["H"] // 128) * 4 if fp8 else 0, E_loc, dev)
+                mx = cfg["recipe"] == "mxfp4"
+                row_bytes = cfg["H"] * (1 if (fp8 or mx) else 2)
+                scale_bytes = (cfg["H"] // 128) * 4 if fp8 else ((cfg["H"] + 511) // 512 * 16 if mx else 0)
+                self.ep = PeerExpertParallel(group, self.moe, T, cfg["k"], cfg["H"], row_bytes,
+                                             scale_bytes, E_loc, dev)
             else:
                 self.ep = ExpertParallel(group, E_loc, make_local_fn(self.moe))
         k = cfg["k"]
@@ -205,10 +232,7 @@ class Layer:
         self.ids = torch.empty(T, k, dtype=torch.int32, device=dev)
         self.src = torch.empty(T, k, dtype=torch.int32, device=dev)
         self.out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=dev)
-        self.score_bias = None
-        if cfg["routing"] == "grouped":
-            g = torch.Generator().manual_seed(3)
-            self.score_bias = (torch.randn(cfg["E"], generator=g) * 0.01).to(dev)
+        self.score_bias = score_bias(cfg).to(dev) if cfg["routing"] == "grouped" else None
 
     def route(self, logits):
         cfg = self.cfg
@@ -221,16 +245,19 @@ class Layer:
     def step(self, x, logits):
         w, ids = self.route(logits)
         scales = None
-        if self.cfg["recipe"] == "fp8block":
+        recipe = self.cfg["recipe"]
+        if recipe == "fp8block":
             x, scales = self.quant(x)
+        elif recipe == "mxfp4" and self.moe._mx_native:
+            x, scales = torch.ops._xpu_C.b200_quant_mxfp8(x)
+        shared_out = self.shared.dense(x, scales) if (self.use_shared and self.shared is not None) else None
         if self.ep is not None:
             self.ep.apply(self.out, x, w, ids, scales=scales)
+            if shared_out is not None:
+                self.out.add_(shared_out)
         else:
-            self.moe.apply(self.out, x, w, ids, a1q_scale=scales)
+            self.moe.apply(self.out, x, w, ids, a1q_scale=scales, shared_output=shared_out)
         return self.out
-
-    def launches_per_step(self):
-        return 1 + (1 if self.cfg["recipe"] == "fp8block" else 0) + self.moe.launches_per_apply(self.T)
 
 
 def same_dtype_probe(dev, n=8192, iters=10):
@@ -239,7 +266,7 @@ def same_dtype_probe(dev, n=8192, iters=10):
     b = torch.randn(1, n, n, device=dev).to(torch.float8_e4m3fn)
     d = torch.empty(n, n, dtype=torch.bfloat16, device=dev)
     rows = torch.tensor([n], dtype=torch.int32, device=dev)
-    run = lambda: torch.ops._xpu_C.b200_grouped_gemm(a, None, b, None, None, d, rows, n, n, 1, 0, 0)
+    run = lambda: torch.ops._xpu_C.b200_grouped_gemm(a, None, b, None, None, d, rows, n, n, 1, 0, 0)  # noqa: E731
     for _ in range(3):
         run()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -256,22 +283,59 @@ def flops_per_token(cfg):
     return 6.0 * cfg["k"] * cfg["H"] * cfg["I"]
 
 
-def cpu_layer_step(cfg, layer_cpu, x, logits, O):
-    """One pass of the CPU oracle (a port of the reference's torch path) over a token sample."""
+def act_format(cfg):
+    return "mxfp8" if cfg["recipe"] == "mxfp4" else None
+
+
+def cpu_layer_step(cfg, layer_cpu, x, logits, O, expert_map=None):
+    """One pass of the CPU oracle (a port of the reference's torch path) over a token sample.
+    ``expert_map`` (global expert id -> index into layer_cpu's experts, -1 = not held) restricts
+    the pass to the experts whose weights are in ``layer_cpu``; rows routed elsewhere are
+    skipped, as on one rank of an expert-parallel layer."""
     if cfg["routing"] == "softmax":
         w, ids = O.topk_softmax(logits, cfg["k"], True)
     else:
-        bias = torch.randn(cfg["E"], generator=torch.Generator().manual_seed(3)) * 0.01
         w, ids = O.grouped_topk(logits, cfg["k"], True, cfg["n_group"], cfg["topk_group"], "sigmoid",
-                                cfg["scale"], bias)
-    return O.fused_moe(cfg["recipe"], x, layer_cpu["w13"], layer_cpu["w13_scale"], layer_cpu["w13_bias"],
-                       layer_cpu["w2"], layer_cpu["w2_scale"], layer_cpu["w2_bias"], w, ids,
-                       cfg["activation"], quant_act=cfg["recipe"] == "fp8block")
+                                cfg["scale"], score_bias(cfg))
+    out = O.fused_moe(cfg["recipe"], x, layer_cpu["w13"], layer_cpu["w13_scale"], layer_cpu["w13_bias"],
+                      layer_cpu["w2"], layer_cpu["w2_scale"], layer_cpu["w2_bias"], w, ids,
+                      cfg["activation"], expert_map=expert_map,
+                      num_local_experts=layer_cpu["w13"].shape[0],
+                      quant_act=cfg["recipe"] in ("fp8block", "mxfp4"),
+                      out_dtype=torch.float32, act_format=act_format(cfg))
+    return out, w, ids
 
 
-def cpu_sample_tokens(cfg):
-    """Tokens per CPU pass: sized so one pass is seconds, not minutes, on a 16-core host."""
-    return 256 if cfg["E"] <= 8 else 64
+def cpu_sample(cfg):
+    """(tokens, experts) of one CPU pass, sized so that a pass is a few seconds on a 16-core
+    host and a run of steps + warm-up passes ends within minutes.  Every pass dequantises the
+    experts it holds (the reference's torch path dequantises per call).  For the layers with
+    many experts the pass is one expert-parallel shard: all sampled tokens, the first 1/8 of
+    the experts, rows routed elsewhere skipped; its time x 8 stands for the whole layer."""
+    key = cfg.get("key")
+    tokens = min({"c1": 1024, "c2": 1024, "c3": 1024}.get(key, 256), cfg["T"])
+    experts = cfg["E"] // 8 if cfg["E"] >= 64 else cfg["E"]
+    return tokens, experts
+
+
+def cpu_pass_setup(cfg, dev_for_weights, x_host, logits_host, weights=None):
+    Tc, En = cpu_sample(cfg)
+    if weights is None:
+        layer = make_device_layer(cfg, dev_for_weights, experts=range(En))
+    else:
+        layer = {k: (v[:En] if v is not None else None) for k, v in weights.items()}
+    layer = {k: (v.cpu() if v is not None else None) for k, v in layer.items()}
+    emap = None
+    if En < cfg["E"]:
+        emap = torch.full((cfg["E"],), -1, dtype=torch.int32)
+        emap[:En] = torch.arange(En, dtype=torch.int32)
+    scale = cfg["E"] // En
+    what = (f"{Tc} of {cfg['T']} tokens per pass, "
+            + (f"all {cfg['E']} experts" if scale == 1 else
+               f"experts 0..{En - 1} of {cfg['E']} (one expert-parallel shard; pass time x {scale} "
+               "stands for the layer)")
+            + ", weights dequantised every pass, dequantise-then-fp32 matmul per expert")
+    return layer, emap, x_host[:Tc], logits_host[:Tc], Tc, scale, what
 
 
 def run_reference(args, cfg):
@@ -282,23 +346,21 @@ def run_reference(args, cfg):
     from oracle import moe_oracle as O
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    Tc = min(cpu_sample_tokens(cfg), cfg["T"])
-    layer = make_device_layer(cfg, torch.device("cpu"))
-    x, logits = make_inputs(cfg, Tc, seed=0)
+    x, logits = make_inputs(cfg, cpu_sample(cfg)[0], seed=0)
+    layer, emap, x, logits, Tc, scale, what = cpu_pass_setup(cfg, torch.device("cpu"), x, logits)
     for _ in range(min(args.warmup, 1)):
-        cpu_layer_step(cfg, layer, x, logits, O)
+        cpu_layer_step(cfg, layer, x, logits, O, emap)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_layer_step(cfg, layer, x, logits, O)
-    dt = (time.perf_counter() - t0) / args.steps
+        cpu_layer_step(cfg, layer, x, logits, O, emap)
+    dt = (time.perf_counter() - t0) / args.steps * scale
     v = Tc / dt
-    sample = f"{Tc} of {cfg['T']} tokens per step, all {cfg['E']} experts, dequantise-then-fp32-matmul"
     print(json.dumps({
         "impl": "reference", "metric": "fused_moe_layer_tokens_per_s", "value": v, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(args, cfg),
-        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": what},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -306,14 +368,278 @@ def run_reference(args, cfg):
 def workload_config(args, cfg):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     how = ("NCCL all-to-all dispatch/combine" if os.environ.get("B200MOE_EP", "peer") == "nccl" else
-           "dispatch and combine as stores into peer GPU memory from the library's own kernels "
-           "(second GEMM's epilogue writes the combine)")
+           "dispatch and combine move rows through peer GPU memory from the library's own kernels")
     par = "1 GPU" if world == 1 else (f"expert-parallel over {world} GPUs ({cfg['E'] // world} experts each), "
                                       f"tokens data-parallel, {how}")
-    return {"workload": f"{args.config}: {cfg['name']}", "parallelism": par, "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
+    return {"workload": f"{cfg.get('key', args.config)}: {cfg['name']}", "parallelism": par,
+            "tokens_per_gpu": cfg["T"], "hidden": cfg["H"], "intermediate": cfg["I"],
             "experts": cfg["E"], "topk": cfg["k"],
             "l2": "value: 256 MiB buffer written between timed steps; e2e: no flush, each step streams "
                   "its expert weights (far larger than the 126 MB L2) again"}
+
+
+# --------------------------------------------------------------------------------------
+class Timer:
+    def __init__(self, dev, world):
+        self.dev, self.world = dev, world
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def region(self, fn, steps):
+        """Mean ms of `steps` calls, each bracketed by its own event pair after an L2 flush."""
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(steps)]
+        self.barrier()
+        for s, e in evs:
+            self.flush.fill_(1)
+            s.record()
+            fn()
+            e.record()
+        self.barrier()
+        return sum(s.elapsed_time(e) for s, e in evs) / steps
+
+
+def e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, steps):
+    """K steps through the public calls from pinned host buffers: each step's x and logits are
+    copied in, its [T, H] result is copied out.  Copies run on their own streams so step i+1's
+    upload and step i-1's download overlap step i's kernels (double-buffered device tensors),
+    as a serving loop would arrange it."""
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    xd = [torch.empty_like(x) for _ in range(2)]
+    ld = [torch.empty_like(logits) for _ in range(2)]
+    od = [torch.empty_like(layer.out) for _ in range(2)]
+    ev_in, ev_comp, ev_out = [None] * steps, [None] * steps, [None] * steps
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    keep = layer.out
+    timer.barrier()
+    start.record(main)
+    s_in.wait_stream(main)
+    s_out.wait_stream(main)
+    for i in range(steps):
+        b = i % 2
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_comp[i - 2])
+            xd[b].copy_(x_pin, non_blocking=True)
+            ld[b].copy_(logits_pin, non_blocking=True)
+            ev_in[i] = torch.cuda.Event()
+            ev_in[i].record(s_in)
+        main.wait_event(ev_in[i])
+        if i >= 2:
+            main.wait_event(ev_out[i - 2])
+        layer.out = od[b]
+        layer.step(xd[b], ld[b])
+        ev_comp[i] = torch.cuda.Event()
+        ev_comp[i].record(main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[i])
+            out_pin.copy_(od[b], non_blocking=True)
+            ev_out[i] = torch.cuda.Event()
+            ev_out[i].record(s_out)
+    main.wait_stream(s_out)
+    end.record(main)
+    timer.barrier()
+    layer.out = keep
+    return start.elapsed_time(end) / steps
+
+
+def parity_check(cfg, layer, x_host, logits_host, out, dev, n_tokens=16, seed=1):
+    """The CPU oracle on a sample of this rank's tokens against the output the timed kernels
+    produced.  Only the experts those tokens hit are rebuilt (same per-expert seeds as the
+    ranks that own them) and dequantised on the CPU.  Bound: |err| <= 2e-2 + 2e-2 |ref|."""
+    from oracle import moe_oracle as O  # the checker, after the timed region
+    T = x_host.shape[0]
+    pick = torch.randperm(T, generator=torch.Generator().manual_seed(seed))[:min(n_tokens, T)]
+    xs, ls = x_host[pick], logits_host[pick]
+    if cfg["routing"] == "softmax":
+        _, ids = O.topk_softmax(ls, cfg["k"], True)
+    else:
+        _, ids = O.grouped_topk(ls, cfg["k"], True, cfg["n_group"], cfg["topk_group"], "sigmoid",
+                                cfg["scale"], score_bias(cfg))
+    hit = torch.unique(ids).tolist()
+    sub = make_device_layer(cfg, dev, experts=hit)
+    sub = {k: (v.cpu() if v is not None else None) for k, v in sub.items()}
+    emap = torch.full((cfg["E"],), -1, dtype=torch.int32)
+    emap[torch.tensor(hit, dtype=torch.long)] = torch.arange(len(hit), dtype=torch.int32)
+    ref, _, ref_ids = cpu_layer_step(cfg, sub, xs, ls, O, emap)
+    got = out[pick.to(out.device)].float().cpu()
+    ids_ok = bool(torch.equal(layer_ids(layer, logits_host, dev)[pick].cpu(), ref_ids))
+    err = (got - ref).abs()
+    tol = 2e-2
+    return {"tokens": int(pick.numel()), "experts_hit": len(hit), "routing_ids_equal": ids_ok,
+            "max_err": float(err.max()), "mean_err": float(err.mean()),
+            "mean_abs_ref": float(ref.abs().mean()),
+            "worst_err_over_bound": float((err / (tol + tol * ref.abs())).max()),
+            "tol": tol, "ok": bool(ids_ok and (err <= tol + tol * ref.abs()).all())}
+
+
+def layer_ids(layer, logits_host, dev):
+    _, ids = layer.route(logits_host.to(dev))
+    return ids
+
+
+def measure(cfg, dev, rank, world, group, steps, warmup, timer, with_e2e=True, clk_index=None):
+    """Builds the layer of `cfg` (this rank's experts), times `steps` steps and returns the
+    measurements plus the objects the caller may still need."""
+    T = cfg["T"]
+    per = cfg["E"] // world
+    weights = make_device_layer(cfg, dev, experts=range(rank * per, (rank + 1) * per))
+    shared_w = make_device_layer(dict(cfg, E=1), dev, seed=9, experts=[0]) if cfg.get("shared") else None
+    layer = Layer(cfg, weights, T, dev, group=group, shared_weights=shared_w)
+    x_host, logits_host = make_inputs(cfg, T, seed=rank)
+    x_pin, logits_pin = x_host.pin_memory(), logits_host.pin_memory()
+    out_pin = torch.empty(T, cfg["H"], dtype=torch.bfloat16).pin_memory()
+    x, logits = x_pin.to(dev), logits_pin.to(dev)
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+
+    for _ in range(warmup):
+        layer.step(x, logits)
+    timer.barrier()
+    res = dict(layer=layer, weights=weights, x_host=x_host, logits_host=logits_host, x=x, logits=logits)
+    sampler = ClockSampler(clk_index) if clk_index is not None else None
+    if sampler:
+        sampler.__enter__()
+    # The dominant kernel (w13 grouped GEMM) carries its own event pair inside the timed
+    # steps, so its duration is taken under exactly the clocks `value` is taken under.
+    gemm1_ev = []
+    layer.moe.stage_timer, layer.moe.stage_only = gemm1_ev, {"gemm1"}
+    launches0 = lib.b200moe_launch_count()
+    res["ms"] = timer.region(lambda: layer.step(x, logits), steps)
+    res["launches"] = int(lib.b200moe_launch_count() - launches0)
+    layer.moe.stage_timer, layer.moe.stage_only = None, None
+    gemm1 = [s.elapsed_time(e) for name, s, e in gemm1_ev if name == "gemm1"]
+    res["gemm1_ms"] = sum(gemm1) / max(len(gemm1), 1)
+    res["out"] = layer.out.clone()
+
+    # the same steps once more with an event pair around every stage (second pass, later in
+    # the run and so under a warmer power state: the stages need not add up to ms_per_step)
+    stage_ev = []
+    layer.moe.stage_timer = stage_ev
+    for _ in range(steps):
+        timer.flush.fill_(1)
+        layer.step(x, logits)
+    torch.cuda.synchronize()
+    layer.moe.stage_timer = None
+    stages = {}
+    for name, s, e in stage_ev:
+        stages.setdefault(name, []).append(s.elapsed_time(e))
+    res["stages"] = {k: round(sum(v) / len(v), 4) for k, v in stages.items()}
+
+    if layer.shared is not None:
+        layer.use_shared = True
+        for _ in range(2):
+            layer.step(x, logits)
+        res["ms_shared"] = timer.region(lambda: layer.step(x, logits), max(steps // 2, 3))
+        res["out_shared"] = layer.out.clone()
+        layer.use_shared = False
+    if with_e2e:
+        e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, 2)
+        res["ms_e2e"] = e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, steps)
+        res["h2d"] = x_pin.numel() * 2 + logits_pin.numel() * 4
+        res["d2h"] = out_pin.numel() * 2
+    if sampler:
+        sampler.__exit__()
+        res["clocks"] = sampler.summary()
+    return res
+
+
+def tensor_roofline(cfg, res, peaks, T):
+    """Roofline of the w13 grouped GEMM of one step."""
+    R = T * cfg["k"]
+    flops = 2.0 * R * cfg["H"] * 2 * cfg["I"]
+    ms = res["gemm1_ms"]
+    achieved = flops / (ms * 1e-3) / 1e12 if ms > 0 else 0.0
+    eight_bit = cfg["recipe"] in ("fp8block", "mxfp4")
+    mult = 2.0 if eight_bit else 1.0
+    peak = mult * peaks["bf16_tflops"]
+    nominal = 4500.0 if eight_bit else 2250.0
+    kernel = {"fp8block": "grouped_gemm_kernel (w13, FP8 block-scaled, fused SiLU*mul + group quantisation)",
+              "mxfp4": "grouped_gemm_mx_kernel (w13, MXFP8 x MXFP4 block-scaled MMA, fused SwigluOAI + "
+                       "MXFP8 quantisation)",
+              "bf16": "grouped_gemm_kernel (w13)"}[cfg["recipe"]]
+    return {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak,
+            "peak_source": (f"2 x {peaks['source']} burst bf16 cuBLAS rate (8-bit operands issue at twice the "
+                            "bf16 rate on tcgen05; the peaks file has no 8-bit figure)") if eight_bit
+            else f"{peaks['source']} burst bf16 cuBLAS rate",
+            "frac_of_sustained": achieved / (mult * peaks["bf16_tflops_sustained"]),
+            "nominal_peak": nominal, "frac_of_nominal": achieved / nominal,
+            "flops_per_launch": flops, "ms_per_launch": ms,
+            "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(cfg.get("key"))}
+
+
+def stream_stages(cfg, stages, peaks, T):
+    """Achieved HBM rate of the streaming stages either side of the GEMMs."""
+    R, H = T * cfg["k"], cfg["H"]
+    fp8 = cfg["recipe"] == "fp8block"
+    mx = cfg["recipe"] == "mxfp4"
+    b_in = 1 if (fp8 or mx) else 2
+    scale_row = (H // 128) * 4 if fp8 else ((H + 511) // 512 * 16 if mx else 0)
+    nbytes = {"remap": T * H * b_in + R * H * b_in + (R + T) * scale_row + T * cfg["k"] * 8,
+              "gather": R * H * 2 + T * H * 2 + T * cfg["k"] * 8}
+    return {name: {"gbs": round(nbytes[name] / (stages[name] * 1e-3) / 1e9, 1),
+                   "frac_of_measured_copy": round(nbytes[name] / (stages[name] * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                   "bytes": nbytes[name], "ms": stages[name]}
+            for name in nbytes if stages.get(name)}
+
+
+def short_config_run(key, dev, timer, peaks, steps=8, warmup=3):
+    """A short run of another configuration on one GPU: the figures that matter, plus parity."""
+    cfg = dict(CONFIGS[key], key=key)
+    res = measure(cfg, dev, 0, 1, None, steps, warmup, timer, with_e2e=False)
+    T = cfg["T"]
+    out = {"workload": cfg["name"], "tokens": T, "steps": steps, "ms_per_step": res["ms"],
+           "tokens_per_s": T / (res["ms"] * 1e-3), "tflops": T * flops_per_token(cfg) / (res["ms"] * 1e-3) / 1e12,
+           "stages_ms": res["stages"], "roofline": tensor_roofline(cfg, res, peaks, T),
+           "hbm_stages": stream_stages(cfg, res["stages"], peaks, T),
+           "parity": parity_check(cfg, res["layer"], res["x_host"], res["logits_host"], res["out"], dev)}
+    if key == "c2":
+        out["frac_of_nominal_fp4"] = out["tflops"] / 9000.0
+    return out
+
+
+def decode_sweep(cfg3, weights, dev, timer, peaks, steps=10):
+    """The decode regime on the DeepSeek-V3 shape: few tokens, Zipf-skewed routing.  The layer
+    streams the weights of the experts it touches once; reported against the copy bandwidth."""
+    out = {}
+    cfg = dict(cfg3, skew=True)
+    for T in DECODE_TOKENS:
+        c = dict(cfg, T=T)
+        layer = Layer(c, weights, T, dev)
+        x_host, logits_host = make_inputs(c, T, seed=0)
+        x, logits = x_host.to(dev), logits_host.to(dev)
+        for _ in range(3):
+            layer.step(x, logits)
+        ev = []
+        layer.moe.stage_timer = ev
+        ms = timer.region(lambda: layer.step(x, logits), steps)
+        layer.moe.stage_timer = None
+        st = {}
+        for name, s, e in ev:
+            st.setdefault(name, []).append(s.elapsed_time(e))
+        st = {k: sum(v) / len(v) for k, v in st.items()}
+        _, ids = layer.route(logits)
+        active = int(torch.unique(ids).numel())
+        R, H, I = T * c["k"], c["H"], c["I"]
+        w13_bytes = active * (H * 2 * I + (H // 128) * (2 * I // 128) * 4) + R * (H + I)
+        w2_bytes = active * (I * H + (I // 128) * (H // 128) * 4) + R * (I + 2 * H)
+        layer_bytes = w13_bytes + w2_bytes + T * H * 3
+        out[str(T)] = {
+            "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "active_experts": active,
+            "layer_gbs": layer_bytes / (ms * 1e-3) / 1e9,
+            "layer_frac_of_measured_copy": layer_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "w13_ms": st.get("gemm1"), "w13_gbs": w13_bytes / (st["gemm1"] * 1e-3) / 1e9 if st.get("gemm1") else None,
+            "w2_ms": st.get("gemm2"), "w2_gbs": w2_bytes / (st["gemm2"] * 1e-3) / 1e9 if st.get("gemm2") else None,
+            "parity": parity_check(c, layer, x_host, logits_host, layer.out.clone(), dev, n_tokens=8),
+        }
+    return out
 
 
 def main():
@@ -322,13 +648,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200")
-    ap.add_argument("--config", default="c1")
+    ap.add_argument("--config", default="c3")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the other configurations and the decode sweep")
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling, sweeps)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling)")
     ap.add_argument("--skew", action="store_true", help="Zipf-like expert load (decode sweep)")
     args = ap.parse_args()
-    cfg = dict(CONFIGS[args.config])
+    cfg = dict(CONFIGS[args.config], key=args.config)
     if args.skew:
         cfg["skew"] = True
     if args.tokens:
@@ -343,207 +670,111 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    group = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    import vllm_xpu_kernels._C  # noqa: F401  (registers the operators; fails loudly without the .so)
 
     T = cfg["T"]
     assert cfg["E"] % world == 0, "the expert count must divide over the ranks"
-    per = cfg["E"] // world
-    weights = make_device_layer(cfg, dev, experts=range(rank * per, (rank + 1) * per))
-    layer = Layer(cfg, weights, T, dev, group=dist.group.WORLD if world > 1 else None)
-    x_host, logits_host = make_inputs(cfg, T, seed=rank)
-    x_pin, logits_pin = x_host.pin_memory(), logits_host.pin_memory()
-    out_pin = torch.empty(T, cfg["H"], dtype=torch.bfloat16).pin_memory()
-    x, logits = x_pin.to(dev), logits_pin.to(dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    # per-stage events of the dominant kernel
-    gemm_ms = []
-    layer.moe.stage_timer = None
-
-    def timed_region(fn, steps):
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-               for _ in range(steps)]
-        barrier()
-        for s, e in evs:
-            flush.fill_(1)
-            s.record()
-            fn()
-            e.record()
-        barrier()
-        return sum(s.elapsed_time(e) for s, e in evs) / steps
-
-    for _ in range(args.warmup):
-        layer.step(x, logits)
-    barrier()
-
-    with ClockSampler(local) as clk:
-        # The dominant kernel (w13 grouped GEMM) carries its own event pair inside the timed
-        # steps, so its duration is taken under exactly the clocks `value` is taken under.
-        gemm1_ev = []
-        layer.moe.stage_timer, layer.moe.stage_only = gemm1_ev, {"gemm1"}
-        ms = timed_region(lambda: layer.step(x, logits), args.steps)
-        layer.moe.stage_timer, layer.moe.stage_only = None, None
-
-        # the same step sequence once more with an event pair around every stage, for the
-        # per-stage breakdown (`stages_ms`; later in the run, so under a warmer power state)
-        layer.moe.stage_timer = gemm_ms
-        for _ in range(args.steps):
-            flush.fill_(1)
-            layer.step(x, logits)
-        torch.cuda.synchronize()
-        layer.moe.stage_timer = None
-
-        def e2e_region(steps):
-            """K steps through the public calls from pinned host buffers: each step's x and
-            logits are copied in, its [T, H] result is copied out.  Copies run on their own
-            streams so step i+1's upload and step i-1's download overlap step i's kernels
-            (double-buffered device tensors), as a serving loop would arrange it."""
-            main = torch.cuda.current_stream()
-            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-            xd = [torch.empty_like(x) for _ in range(2)]
-            ld = [torch.empty_like(logits) for _ in range(2)]
-            od = [torch.empty_like(layer.out) for _ in range(2)]
-            ev_in, ev_comp, ev_out = [None] * steps, [None] * steps, [None] * steps
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            barrier()
-            start.record(main)
-            s_in.wait_stream(main)
-            s_out.wait_stream(main)
-            for i in range(steps):
-                b = i % 2
-                with torch.cuda.stream(s_in):
-                    if i >= 2:
-                        s_in.wait_event(ev_comp[i - 2])
-                    xd[b].copy_(x_pin, non_blocking=True)
-                    ld[b].copy_(logits_pin, non_blocking=True)
-                    ev_in[i] = torch.cuda.Event()
-                    ev_in[i].record(s_in)
-                main.wait_event(ev_in[i])
-                if i >= 2:
-                    main.wait_event(ev_out[i - 2])
-                layer.out = od[b]
-                layer.step(xd[b], ld[b])
-                ev_comp[i] = torch.cuda.Event()
-                ev_comp[i].record(main)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_comp[i])
-                    out_pin.copy_(od[b], non_blocking=True)
-                    ev_out[i] = torch.cuda.Event()
-                    ev_out[i].record(s_out)
-            main.wait_stream(s_out)
-            end.record(main)
-            barrier()
-            return start.elapsed_time(end) / steps
-        e2e_region(2)
-        ms_e2e = e2e_region(args.steps)
-
-    gemm1 = [s.elapsed_time(e) for name, s, e in gemm1_ev if name == "gemm1"]
-    gemm1_ms = sum(gemm1) / max(len(gemm1), 1)
-    stages = {}
-    for name, s, e in gemm_ms:
-        stages.setdefault(name, []).append(s.elapsed_time(e))
-    stages = {k: round(sum(v) / len(v), 4) for k, v in stages.items()}
-
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    timer = Timer(dev, world)
+    warmup = max(args.warmup, 3)
+    res = measure(cfg, dev, rank, world, group, args.steps, warmup, timer, with_e2e=True, clk_index=local)
+    ms, ms_e2e = res["ms"], res["ms_e2e"]
+    t = torch.tensor([ms, ms_e2e, res.get("ms_shared", 0.0)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t.tolist()
+    ms, ms_e2e, ms_shared = t.tolist()
 
     if rank == 0:
+        # correctness evidence at every N: rank 0's sampled tokens against the CPU oracle (their
+        # experts live on all ranks; rank 0 rebuilds the ones they hit from the per-expert seeds)
+        parity = parity_check(cfg, res["layer"], res["x_host"], res["logits_host"], res["out"], dev)
         peaks = load_peaks()
-        R = T * cfg["k"]
-        gemm1_flops = 2.0 * R * cfg["H"] * 2 * cfg["I"]
-        achieved = gemm1_flops / (gemm1_ms * 1e-3) / 1e12 if gemm1_ms > 0 else 0.0
-        fp8 = cfg["recipe"] == "fp8block"
-        peak = (2.0 if fp8 else 1.0) * peaks["bf16_tflops_sustained"]
-        # distinct experts this batch touches: in the decode regime the layer streams their weights
-        # once and the w13 GEMM is bound by HBM, not by the tensor pipe
-        _, ids_now = layer.route(logits)
-        active = int(torch.unique(ids_now).numel())
-        wbytes = {"fp8block": 1.0, "bf16": 2.0, "mxfp4": 2.0}[cfg["recipe"]]
-        gemm1_bytes = (active * cfg["H"] * 2 * cfg["I"] * wbytes
-                       + (active * (cfg["H"] // 128) * (2 * cfg["I"] // 128) * 4 if fp8 else 0)
-                       + R * cfg["H"] * (1 if fp8 else 2) + R * cfg["I"] * (1 if fp8 else 2))
-        decode = R / max(active, 1) < 64
+        modified = bool(args.tokens or args.experts or args.skew)
+        roof = tensor_roofline(cfg, res, peaks, T)
+        if modified:
+            roof["traffic"] = None
         line = {
             "metric": "fused_moe_layer_tokens_per_s", "value": world * T / (ms * 1e-3),
-            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"fp8block": "fp8_e4m3 (fp32 accumulate)", "bf16": "bf16 (fp32 accumulate)",
-                      "mxfp4": "mxfp4 weights as bf16 x bf16 (fp32 accumulate)"}[cfg["recipe"]],
+                      "mxfp4": "mxfp4 weights x mxfp8 activations (e8m0 block scales, fp32 accumulate)"}[cfg["recipe"]],
             "data": "synthetic",
             "config": workload_config(args, cfg),
             "tflops": world * T * flops_per_token(cfg) / (ms * 1e-3) / 1e12,
             "e2e": {"value": world * T / (ms_e2e * 1e-3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": x_pin.numel() * 2 + logits_pin.numel() * 4,
-                    "d2h_bytes_per_step": out_pin.numel() * 2},
-            "gpu_launches": layer.launches_per_step() * args.steps,
-            "roofline": {"bound": "tensor",
-                         "kernel": "grouped_gemm_kernel (w13" + (", fp8 block-scaled, fused SiLU*mul + "
-                                                                 "group quantisation)" if fp8 else ")"),
-                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(args.config)
-                         if not (args.tokens or args.experts) else None,
-                         "peak_source": (f"2 x {peaks['source']} sustained bf16 cuBLAS rate (fp8 issues at "
-                                         "twice the bf16 rate on tcgen05; MEASURED_PEAKS has no fp8 figure)")
-                         if fp8 else f"{peaks['source']} sustained bf16 cuBLAS rate",
-                         "flops_per_launch": gemm1_flops, "ms_per_launch": gemm1_ms},
-            "clocks": clk.summary(),
-            "stages_ms": stages, "active_experts": active,
+                    "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
+                    "h2d_gbs_per_rank": res["h2d"] / (ms_e2e * 1e-3) / 1e9,
+                    "d2h_gbs_per_rank": res["d2h"] / (ms_e2e * 1e-3) / 1e9},
+            "gpu_launches": res["launches"],
+            "gpu_launches_note": "kernels of this library enqueued inside the timed region (counted by the "
+                                 "library); torch adds one fill kernel per step (rows_per_expert) and the "
+                                 "256 MiB flush",
+            "roofline": roof,
+            "parity": parity,
+            "clocks": res["clocks"],
+            "stages_ms": res["stages"],
+            "stages_note": "per-stage events come from a second pass after the timed region",
+            "hbm_stages": stream_stages(cfg, res["stages"], peaks, T),
         }
-        # the streaming stages either side of the GEMMs: algorithmic bytes / stage time
-        b_in = 1 if fp8 else 2
-        H = cfg["H"]
-        stream_bytes = {
-            "remap": T * H * b_in + R * H * b_in + (R + T) * (H // 128) * 4 * (1 if fp8 else 0) + T * cfg["k"] * 8,
-            "gather": R * H * 2 + T * H * 2 + T * cfg["k"] * 8,
-        }
-        line["hbm_stages"] = {
-            name: {"gbs": round(stream_bytes[name] / (stages[name] * 1e-3) / 1e9, 1),
-                   "frac_of_measured_copy": round(stream_bytes[name] / (stages[name] * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
-                   "bytes": stream_bytes[name], "ms": stages[name]}
-            for name in stream_bytes if stages.get(name)}
-        nominal = 4500.0 if fp8 else 2250.0   # dense TFLOP/s of the part's data sheet
-        line["roofline"]["frac_of_nominal"] = achieved / nominal
-        line["roofline"]["nominal_peak"] = nominal
-        if fp8 and world == 1 and not decode:
-            # Same-dtype ceiling measured in this run: one plain e4m3 x e4m3 problem of 8192^3
-            # (unit scales, so no per-K-block promotion) through the same kernel family.
+        if ms_shared:
+            fl = flops_per_token(cfg) + 6.0 * cfg["H"] * cfg["I"]
+            line["with_shared_expert"] = {
+                "ms_per_step": ms_shared, "tokens_per_s": world * T / (ms_shared * 1e-3),
+                "tflops": world * T * fl / (ms_shared * 1e-3) / 1e12,
+                "what": "the same step plus one dense FP8-block SwiGLU expert over all tokens, added in the combine",
+                "parity": shared_parity(cfg, res, dev)}
+        extras = world == 1 and not modified and not args.no_extras
+        if extras and cfg["recipe"] == "fp8block":
             probe = same_dtype_probe(dev)
             line["roofline"]["same_dtype_probe"] = {
                 "tflops": probe, "what": "plain tcgen05 e4m3 GEMM, M=N=K=8192, unit scales, bf16 out"}
-            line["roofline"]["frac_of_probe"] = achieved / probe if probe > 0 else None
-        if decode and gemm1_ms > 0:
-            gbs = gemm1_bytes / (gemm1_ms * 1e-3) / 1e9
-            line["roofline"] = {"bound": "hbm", "kernel": "grouped_gemm_kernel (w13), weight streaming",
-                                "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": gbs / peaks["hbm_gbs"], "traffic": None,
-                                "peak_source": f"{peaks['source']} copy bandwidth",
-                                "bytes_per_launch": gemm1_bytes, "ms_per_launch": gemm1_ms}
+            line["roofline"]["frac_of_probe"] = roof["achieved"] / probe if probe > 0 else None
+        if extras and args.config == "c3":
+            line["decode"] = decode_sweep(cfg, res["weights"], dev, timer, peaks)
         if not args.no_cpu_baseline and world == 1:
             from oracle import moe_oracle as O  # CPU-baseline leg only
             cores = os.cpu_count() or 1
             torch.set_num_threads(cores)
-            Tc = min(cpu_sample_tokens(cfg), T)
-            cpu_layer = {k: (v.cpu() if v is not None else None) for k, v in weights.items()}
-            xs, ls = x_host[:Tc], logits_host[:Tc]
+            cpu_layer, emap, xs, ls, Tc, scale, what = cpu_pass_setup(
+                cfg, dev, res["x_host"], res["logits_host"], res["weights"])
             t0 = time.perf_counter()
-            cpu_layer_step(cfg, cpu_layer, xs, ls, O)
-            dt = time.perf_counter() - t0
-            line["cpu_baseline"] = {
-                "value": Tc / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
-                "sample": f"first {Tc} of {T} tokens, one pass, all {cfg['E']} experts "
-                          "(dequantise-then-fp32 matmul per expert)"}
+            cpu_layer_step(cfg, cpu_layer, xs, ls, O, emap)
+            dt = (time.perf_counter() - t0) * scale
+            del cpu_layer
+            line["cpu_baseline"] = {"value": Tc / dt, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                    "sample": what + f"; one pass, {dt / scale:.1f} s"}
+        if extras:
+            del res
+            torch.cuda.empty_cache()
+            line["other_configs"] = {k: short_config_run(k, dev, timer, peaks)
+                                     for k in ("c1", "c2", "c3") if k != args.config}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def shared_parity(cfg, res, dev):
+    """routed + shared output against the oracle on a few tokens."""
+    from oracle import moe_oracle as O
+    layer = res["layer"]
+    base = parity_check(cfg, layer, res["x_host"], res["logits_host"], res["out"], dev, n_tokens=8, seed=2)
+    pick = torch.randperm(res["x_host"].shape[0], generator=torch.Generator().manual_seed(2))[:8]
+    sw = make_device_layer(dict(cfg, E=1), dev, seed=9, experts=[0])
+    sw = {k: (v.cpu() if v is not None else None) for k, v in sw.items()}
+    xs = res["x_host"][pick]
+    extra = O.fused_moe(cfg["recipe"], xs, sw["w13"], sw["w13_scale"], None, sw["w2"], sw["w2_scale"], None,
+                        torch.ones(len(pick), 1), torch.zeros(len(pick), 1, dtype=torch.int32),
+                        cfg["activation"], quant_act=True, out_dtype=torch.float32)
+    diff = (res["out_shared"][pick.to(dev)].float() - res["out"][pick.to(dev)].float()).cpu()
+    err = (diff - extra).abs()
+    tol = 2e-2
+    return {"routed_ok": base["ok"], "max_err_shared_part": float(err.max()),
+            "ok": bool(base["ok"] and (err <= 2 * tol + tol * extra.abs()).all())}
 
 
 if __name__ == "__main__":

@@ -73,6 +73,10 @@ const char* b200moe_version(void);
 const char* b200moe_status_string(int status);
 /* Last CUDA error text seen by this library on the calling thread. */
 const char* b200moe_last_error(void);
+/* Kernels this library has enqueued in this process so far (all threads, all
+ * devices): a benchmark reads it before and after a timed region to report how
+ * many of its launches were this library's. */
+long long b200moe_launch_count(void);
 
 /* ---- routing ---------------------------------------------------------- */
 
@@ -197,6 +201,16 @@ int b200moe_remap_hidden_states(const void* hidden, const void* scales,
  * out[t,:] = sum_j w[t,j] * y[row_map[t,j],:] (fp32 accumulate, -1 skipped). */
 int b200moe_moe_gather(void* out, const void* y, int dtype, const float* weights,
                        const int32_t* row_map, int T, int k, int H, void* stream);
+
+/* moe_gather with one more source row per token, weight 1: out[t,:] = addend[t,:] +
+ * sum_j w[t,j] * y[row_map[t,j],:], one rounding.  The combine of a layer with a
+ * shared expert (every token goes through it, as in the DeepSeek-V3 layer); the
+ * reference project has no shared-expert operator, its moe_gather
+ * (csrc/moe/moe_gather.cpp:162-205) is the routed part of this.  `out` may be
+ * `addend`. */
+int b200moe_moe_gather_add(void* out, const void* y, int dtype, const float* weights,
+                           const int32_t* row_map, const void* addend, int T, int k,
+                           int H, void* stream);
 
 /* moe_sum (csrc/moe/torch_bindings.cpp:7-10, csrc/moe/moe_align_sum_kernels.cpp:1224-1372).
  * out[t,:] = sum_j in[t,j,:]; with topk_ids, slots with id < 0 or

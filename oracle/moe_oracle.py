@@ -146,6 +146,40 @@ def grouped_topk(gating_output, topk, renormalize, num_expert_group,
     return w.to(torch.float32), ids.to(torch.int32)
 
 
+def grouped_topk_kernel_semantics(gating_output, topk, renormalize, num_expert_group, topk_group,
+                                  scoring_func, routed_scaling_factor, e_score_correction_bias):
+    """grouped_topk with the three behaviours the reference's device kernel adds to its torch
+    oracle (csrc/moe/grouped_topk.cpp): a row whose ``topk_group``-th best group score is -inf
+    returns experts 0..k-1 with weight 1/k each (:608-624); experts whose raw score is +-inf
+    are never selected although they count for their group's score (:659-662); the
+    renormalising denominator is the sum + 1e-20 (:678-687).  On rows without such inputs it
+    equals ``grouped_topk``."""
+    if scoring_func == "sigmoid":
+        scores = torch.sigmoid(gating_output)
+    elif scoring_func == "none":
+        scores = gating_output.clone()
+    else:
+        raise ValueError(scoring_func)
+    T, E = scores.shape
+    per = E // num_expert_group
+    biased = scores + e_score_correction_bias.unsqueeze(0)
+    group_scores = stable_topk(biased.view(T, num_expert_group, per), 2)[0].sum(-1)
+    gval, gidx = stable_topk(group_scores, topk_group)
+    degenerate = gval[:, -1] == float("-inf")
+    gmask = torch.zeros_like(group_scores)
+    gmask.scatter_(1, gidx, 1)
+    smask = gmask.unsqueeze(-1).expand(T, num_expert_group, per).reshape(T, E).bool()
+    masked = biased.masked_fill(~smask | torch.isinf(gating_output), float("-inf"))
+    _, ids = stable_topk(masked, topk)
+    w = scores.gather(1, ids)
+    if renormalize:
+        w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
+    w = w * routed_scaling_factor
+    ids = torch.where(degenerate.unsqueeze(1), torch.arange(topk).expand(T, topk), ids)
+    w = torch.where(degenerate.unsqueeze(1), torch.full_like(w, 1.0 / topk), w)
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
 def routing_margin(keys: torch.Tensor, k: int) -> torch.Tensor:
     """Per row: gap between the k-th and (k+1)-th largest selection key.  Rows
     whose gap is a few ulps are the only ones where two correct fp32
@@ -632,10 +666,16 @@ def grouped_gemm(recipe, A, B, B_scale, bias, rows_per_expert, out_dtype=None):
     return D.to(out_dtype or A.dtype)
 
 
-def qdq_act(recipe, x):
+def qdq_act(recipe, x, act_format=None):
     """Quantise-dequantise an activation the way the layer's tensor-core path
     sees it: per-token-group-128 FP8 for block-FP8 weights
-    (moe_utils.py:190-204), nothing for bf16 and for MXFP4 weights (W4A16)."""
+    (moe_utils.py:190-204), nothing for bf16 and for MXFP4 weights run W4A16.
+    ``act_format="mxfp8"``: e4m3 with e8m0 scales per 32 columns
+    (moe_utils.py:84-109, 198-200), what the block-scaled MXFP4 path feeds its
+    tensor cores."""
+    if act_format == "mxfp8":
+        q, sf = quant_mxfp8_act(x)
+        return dequant_mxfp8_act(q, sf)
     if recipe == "fp8block":
         q, s = per_token_group_fp8_quant(x, 128)
         return dequant_fp8_group_act(q, s)
@@ -645,7 +685,7 @@ def qdq_act(recipe, x):
 def fused_moe(recipe, x, w13, w13_scale, w13_bias, w2, w2_scale, w2_bias,
               topk_weights, topk_ids, activation="silu", expert_map=None,
               num_local_experts=None, quant_act=True, out_dtype=None,
-              gemm1_clamp_limit=None, situ_beta=None, situ_linear_beta=None):
+              gemm1_clamp_limit=None, situ_beta=None, situ_linear_beta=None, act_format=None):
     """Layer oracle: permute, per-expert dequantise-then-fp32 matmuls with the
     activation between them, weighted un-permute
     (tests/fused_moe/test_fused_moe.py:93-166 for the structure,
@@ -653,7 +693,7 @@ def fused_moe(recipe, x, w13, w13_scale, w13_bias, w2, w2_scale, w2_bias,
     quantise-dequantised).  Intermediates stay fp32, so this is the
     'dequantise-then-fp32 matmul' the tolerance is stated against."""
     E = num_local_experts if num_local_experts is not None else w13.shape[0]
-    xa = qdq_act(recipe, x) if quant_act else x.float()
+    xa = qdq_act(recipe, x, act_format) if quant_act else x.float()
     perm, _, rows, row_map = remap_hidden_states(xa, None, topk_ids, expert_map, E)
     h = grouped_gemm(recipe, perm, w13, w13_scale, w13_bias, rows, torch.float32)
     if gemm1_clamp_limit:
@@ -662,7 +702,7 @@ def fused_moe(recipe, x, w13, w13_scale, w13_bias, w2, w2_scale, w2_bias,
         h[:, d:].clamp_(min=-gemm1_clamp_limit, max=gemm1_clamp_limit)
     a = layer_activation(h, activation, situ_beta, situ_linear_beta)
     if quant_act:
-        a = qdq_act(recipe, a)
+        a = qdq_act(recipe, a, act_format)
     y = grouped_gemm(recipe, a, w2, w2_scale, w2_bias, rows, torch.float32)
     return moe_gather(y, topk_weights, row_map, out_dtype or x.dtype)
 

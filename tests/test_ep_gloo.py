@@ -96,3 +96,24 @@ def test_missing_rank_is_an_error_not_a_hang():
         mp.spawn(_late_worker, args=(2, 29613, result), nprocs=2, join=True)
         assert result[1] == "never joined"
         assert result[0].startswith("error")
+
+
+def test_peer_exchange_refuses_calls_beyond_its_buffers():
+    """PeerExpertParallel sizes its exchange buffers and address tables at construction; a call
+    with more tokens, another top-k, another row width or missing scales must be refused before
+    any kernel is enqueued (no device needed for the check itself)."""
+    from vllm_xpu_kernels.ep import PeerExpertParallel
+    ep = object.__new__(PeerExpertParallel)
+    ep.T, ep.k, ep.H, ep.row_bytes, ep.scale_row_bytes = 16, 2, 64, 64, 0
+    x = torch.zeros(16, 64, dtype=torch.float8_e4m3fn)
+    ids = torch.zeros(16, 2, dtype=torch.int32)
+    ep.check_call(x, ids, None)                                        # fits
+    ep.check_call(x[:8], ids[:8], None)                                # fewer tokens fit too
+    with pytest.raises(ValueError, match="at most 16 tokens"):
+        ep.check_call(torch.zeros(17, 64, dtype=torch.float8_e4m3fn), torch.zeros(17, 2, dtype=torch.int32), None)
+    with pytest.raises(ValueError, match="top-2"):
+        ep.check_call(x, torch.zeros(16, 4, dtype=torch.int32), None)
+    with pytest.raises(ValueError, match="rows of 64 bytes"):
+        ep.check_call(torch.zeros(16, 64, dtype=torch.bfloat16), ids, None)
+    with pytest.raises(ValueError, match="activation scales"):
+        ep.check_call(x, ids, torch.zeros(16, 1))

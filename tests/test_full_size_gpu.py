@@ -17,7 +17,14 @@ def test_c3_routing_and_permutation_full_size(ops):
     bias = torch.randn(E, generator=g) * 0.01
     w, ids = ops._moe_C.grouped_topk(logits.to(DEV), 8, 4, 8, True, 2.5, bias.to(DEV), 1)
     rw, rids = O.grouped_topk(logits, k, True, 8, 4, "sigmoid", 2.5, bias)
-    assert (ids.cpu() != rids).any(dim=1).float().mean() < 1e-3      # near-ties only, normally none
+    if not torch.equal(ids.cpu(), rids):
+        # diagnosis only: a differing row is excusable when the oracle's own selection margin on
+        # it is a few fp32 ulps (two correct evaluations of the sigmoid may then disagree)
+        bad = (ids.cpu() != rids).any(dim=1)
+        keys = torch.sigmoid(logits) + bias
+        margin = O.routing_margin(keys[bad], k)
+        raise AssertionError(f"{int(bad.sum())} of {T} rows differ from the oracle; their selection "
+                             f"margins: {margin[:8].tolist()}")
     # align: a permutation of the flat indices plus padding, blocks labelled by their expert
     n, nb = O.align_sizes(T * k, E, 128)
     s = torch.empty(n, dtype=torch.int32, device=DEV)
@@ -79,10 +86,87 @@ def test_c1_layer_full_size_sampled_tokens(ops):
     ref = O.fused_moe("fp8block", x[pick], cpu_w["w13"], cpu_w["w13_scale"], None, cpu_w["w2"],
                       cpu_w["w2_scale"], None, rw[pick], rids[pick], "silu", out_dtype=torch.float32)
     err = (out[pick] - ref).abs()
-    assert (err <= 5e-2 + 5e-2 * ref.abs()).all(), f"max err {err.max():.4g}"
+    assert (err <= 2e-2 + 2e-2 * ref.abs()).all(), f"max err {err.max():.4g}"
     assert err.mean() < 1e-2 * ref.abs().mean() + 1e-3
     # the same batch through already-quantised inputs is bit-identical (no hidden state between calls)
     xq, xs = quant_fp8_block_act(x.to(dev))
     out2 = torch.empty_like(layer.out)
     layer.moe.apply(out2, xq, layer.w, layer.ids, a1q_scale=xs)
     assert torch.equal(out2.float().cpu(), out)
+
+
+# ---- the other configurations at full size ------------------------------------------------
+# Same pattern: the whole layer on the GPU, the CPU oracle on a sample of its tokens with only
+# the experts those tokens hit rebuilt and dequantised (bench.parity_check), bound 2e-2
+# absolute + relative against the quantise-dequantise oracle.
+
+def _full_layer(key, T=None, skew=False):
+    import bench
+    cfg = dict(bench.CONFIGS[key], key=key)
+    if skew:
+        cfg["skew"] = True
+    if T:
+        cfg["T"] = T
+    return bench, cfg
+
+
+def _check(res):
+    assert res["routing_ids_equal"], res
+    assert res["ok"], res
+    assert res["mean_err"] < 1e-2 * res["mean_abs_ref"] + 1e-3, res
+
+
+def test_c2_layer_full_size_sampled_tokens(ops):
+    """gpt-oss shape, 8192 tokens, 128 experts, MXFP4 weights on the block-scaled tensor-core
+    path: 16 sampled tokens against the oracle fed the same MXFP8-quantised activations."""
+    bench, cfg = _full_layer("c2")
+    dev = torch.device(DEV)
+    weights = bench.make_device_layer(cfg, dev)
+    layer = bench.Layer(cfg, weights, cfg["T"], dev)
+    assert layer.moe._mx_native
+    x, logits = bench.make_inputs(cfg, cfg["T"], seed=0)
+    out = layer.step(x.to(dev), logits.to(dev)).clone()
+    assert torch.ops._xpu_C.b200_device_status() == 0
+    assert torch.isfinite(out.float()).all()
+    _check(bench.parity_check(cfg, layer, x, logits, out, dev, n_tokens=16))
+
+
+@pytest.fixture(scope="module")
+def c3_weights():
+    import bench
+    dev = torch.device(DEV)
+    cfg = dict(bench.CONFIGS["c3"], key="c3")
+    w = bench.make_device_layer(cfg, dev)
+    yield cfg, w
+    del w
+    torch.cuda.empty_cache()
+
+
+def test_c3_layer_full_size_sampled_tokens(ops, c3_weights):
+    """DeepSeek-V3 shape, 16384 tokens, 256 experts, grouped routing: 16 sampled tokens."""
+    import bench
+    cfg, weights = c3_weights
+    dev = torch.device(DEV)
+    layer = bench.Layer(cfg, weights, cfg["T"], dev)
+    x, logits = bench.make_inputs(cfg, cfg["T"], seed=0)
+    out = layer.step(x.to(dev), logits.to(dev)).clone()
+    assert torch.ops._xpu_C.b200_device_status() == 0
+    assert torch.isfinite(out.float()).all()
+    _check(bench.parity_check(cfg, layer, x, logits, out, dev, n_tokens=16))
+
+
+@pytest.mark.parametrize("T", [1, 8, 32, 128, 256])
+def test_c4_decode_sweep_with_zipf_routing(ops, c3_weights, T):
+    """The decode regime on the same weights: few tokens and router logits offset by
+    1.5*log(1/rank) so that a handful of experts take most rows (hot experts span several
+    32-token chunks of the decode-regime kernel).  Every token is checked for T <= 8."""
+    import bench
+    cfg, weights = c3_weights
+    cfg = dict(cfg, T=T, skew=True)
+    dev = torch.device(DEV)
+    layer = bench.Layer(cfg, weights, T, dev)
+    x, logits = bench.make_inputs(cfg, T, seed=0)
+    out = layer.step(x.to(dev), logits.to(dev)).clone()
+    assert torch.ops._xpu_C.b200_device_status() == 0
+    res = bench.parity_check(cfg, layer, x, logits, out, dev, n_tokens=8)
+    _check(res)

@@ -1,9 +1,10 @@
 """The whole layer through XpuFusedMoe.apply against the layer oracle, on the
 benchmark configurations: the tiny bf16 one at full size, the others with the
 token count (and, for the CPU-side check, the set of experts) cut down so the
-fp32 oracle finishes in seconds.  Tolerance 2e-2 for bf16 (the stated bound),
-5e-2 for block-FP8 (the reference's own bound for that recipe,
-tests/fused_moe/test_fused_moe.py:676,798 there)."""
+fp32 oracle finishes in seconds.  Tolerance for every recipe: |err| <= 2e-2 + 2e-2 |ref|
+against the oracle that quantise-dequantises the activations the way the kernels do
+(the reference's own tests allow 5e-2 for block-FP8, tests/fused_moe/test_fused_moe.py:676,798
+there), and a mean error below 1 % of the mean magnitude (measured: about 0.2 %)."""
 import pytest
 import torch
 
@@ -45,8 +46,8 @@ def check(out, ref, tol):
     err = (out - ref).abs()
     bound = tol + tol * ref.abs()
     assert (err <= bound).all(), f"max err {err.max():.4g}, {int((err > bound).sum())} of {err.numel()} out of bound"
-    # and in the aggregate the match is tighter than the element bound
-    assert err.mean() < 0.5 * tol * max(ref.abs().mean().item(), 1e-3) + 1e-3
+    # and in the aggregate the match is far tighter than the element bound
+    assert err.mean() < 0.01 * ref.abs().mean().item() + 2e-4, (err.mean().item(), ref.abs().mean().item())
 
 
 def test_c0_full(ops):
@@ -63,9 +64,9 @@ def test_c0_full(ops):
     check(out, ref, 2e-2)
 
 
-@pytest.mark.parametrize("name,T,E_limit,tol,decode", [("c1", 96, None, 5e-2, "0"), ("c2", 160, 24, 2e-2, "0"),
-                                                       ("c3", 48, 20, 5e-2, "0"), ("c1", 24, None, 5e-2, "1"),
-                                                       ("c3", 40, 20, 5e-2, "1")])
+@pytest.mark.parametrize("name,T,E_limit,tol,decode", [("c1", 96, None, 2e-2, "0"), ("c2", 160, 24, 2e-2, "0"),
+                                                       ("c3", 48, 20, 2e-2, "0"), ("c1", 24, None, 2e-2, "1"),
+                                                       ("c3", 40, 20, 2e-2, "1")])
 def test_reduced_configs(ops, name, T, E_limit, tol, decode, monkeypatch):
     monkeypatch.setenv("B200MOE_DECODE_PATH", decode)   # "1": the weight-streaming kernels
     """Real H/I/E of the config, few tokens.  Only the first E_limit experts'
@@ -88,11 +89,53 @@ def test_reduced_configs(ops, name, T, E_limit, tol, decode, monkeypatch):
         moe.total_experts_num = E
     out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=DEV)
     moe.apply(out, to_dev(layer["x"]), w, ids, expert_map=to_dev(emap))
+    # MXFP4 weights run on the block-scaled tensor-core path: MXFP8 activations, and the oracle
+    # quantise-dequantises them the same way
+    mx = cfg["recipe"] == "mxfp4"
+    assert moe._mx_native == mx
     ref = O.fused_moe(cfg["recipe"], layer["x"], layer["w13"], layer["w13_scale"], layer["w13_bias"],
                       layer["w2"], layer["w2_scale"], layer["w2_bias"], rw, rids, cfg["activation"],
                       expert_map=emap, num_local_experts=E_loc,
-                      quant_act=cfg["recipe"] == "fp8block", out_dtype=torch.float32)
+                      quant_act=cfg["recipe"] == "fp8block" or mx, out_dtype=torch.float32,
+                      act_format="mxfp8" if mx else None)
     check(out, ref, tol)
+
+
+@pytest.mark.parametrize("mode", ["w4a16", "mxfp4_fp8", "prequantised", "silu"])
+def test_mxfp4_layer_variants(ops, mode, monkeypatch):
+    """The gpt-oss widths on a few experts: the W4A16 arithmetic of the reference kernel
+    (B200MOE_MXFP4_W4A16), the reference's mxfp4_fp8 recipe flag, activations that arrive
+    already quantised to MXFP8, and an activation that is not fused into the first GEMM."""
+    cfg = dict(O.CONFIGS["c2"])
+    if mode == "silu":
+        cfg["activation"] = "silu"
+    T, E_limit, E = 96, 12, cfg["E"]
+    layer = O.make_layer(cfg, T=T, E_limit=E_limit)
+    if mode == "w4a16":
+        monkeypatch.setenv("B200MOE_MXFP4_W4A16", "1")
+    if mode == "mxfp4_fp8":
+        monkeypatch.setenv("VLLM_XPU_FUSED_MOE_USE_MXFP4_FP8", "1")
+    w, ids = route_gpu(ops, cfg, layer)
+    rw, rids = O.route(cfg, layer)
+    emap = torch.full((E,), -1, dtype=torch.int32)
+    emap[:E_limit] = torch.arange(E_limit, dtype=torch.int32)
+    moe = build(cfg, layer)
+    moe.total_experts_num = E
+    assert moe._mx_native == (mode != "w4a16")
+    assert moe.recipe == ("mxfp4_fp8" if mode == "mxfp4_fp8" else "mxfp4")
+    out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=DEV)
+    if mode == "prequantised":
+        xq, xsf = O.quant_mxfp8_act(layer["x"])
+        moe.apply(out, to_dev(xq), w, ids, expert_map=to_dev(emap),
+                  a1q_scale=to_dev(xsf).view(torch.float8_e8m0fnu))
+    else:
+        moe.apply(out, to_dev(layer["x"]), w, ids, expert_map=to_dev(emap))
+    native = mode != "w4a16"
+    ref = O.fused_moe("mxfp4", layer["x"], layer["w13"], layer["w13_scale"], layer["w13_bias"],
+                      layer["w2"], layer["w2_scale"], layer["w2_bias"], rw, rids, cfg["activation"],
+                      expert_map=emap, num_local_experts=E_limit, quant_act=native,
+                      out_dtype=torch.float32, act_format="mxfp8" if native else None)
+    check(out, ref, 2e-2)
 
 
 def test_expert_parallel_partial_sums(ops):
@@ -179,8 +222,37 @@ def test_few_tokens_take_the_decode_kernels(ops, T, monkeypatch):
     moe.apply(out, to_dev(layer["x"]), w, ids)
     ref = O.fused_moe("fp8block", layer["x"], layer["w13"], layer["w13_scale"], None, layer["w2"],
                       layer["w2_scale"], None, rw, rids, "silu", out_dtype=torch.float32)
-    check(out, ref, 5e-2)
+    check(out, ref, 2e-2)
     monkeypatch.setenv("B200MOE_DECODE_PATH", "0")
     out2 = torch.empty_like(out)
     moe.apply(out2, to_dev(layer["x"]), w, ids)
-    check(out2, ref, 5e-2)
+    check(out2, ref, 2e-2)
+
+
+@pytest.mark.parametrize("T", [3, 200])
+def test_shared_expert_added_in_the_combine(ops, T):
+    """A DeepSeek-V3-style layer: routed experts plus one shared expert every token passes
+    through, its rows added inside the weighted combine (``dense`` + ``shared_output``).  The
+    oracle is the routed layer oracle plus the same oracle on a one-expert layer with weight 1.
+    T = 3 takes the decode-regime kernels for the routed part."""
+    from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
+    cfg = dict(O.CONFIGS["c1"], H=512, I=256, E=16, k=4)
+    layer = O.make_layer(cfg, T=T)
+    shared = O.make_layer(dict(cfg, E=1), seed=7, T=T)
+    w, ids = route_gpu(ops, cfg, layer)
+    rw, rids = O.route(cfg, layer)
+    moe = build(cfg, layer)
+    dense = XpuFusedMoe(to_dev(shared["w13"]), to_dev(shared["w13_scale"]), None, to_dev(shared["w2"]),
+                        to_dev(shared["w2_scale"]), None, 1, "silu", 1)
+    x = to_dev(layer["x"])
+    out = torch.empty(T, cfg["H"], dtype=torch.bfloat16, device=DEV)
+    sh = dense.dense(x)
+    moe.apply(out, x, w, ids, shared_output=sh)
+    args = dict(out_dtype=torch.float32)
+    routed = O.fused_moe("fp8block", layer["x"], layer["w13"], layer["w13_scale"], None, layer["w2"],
+                         layer["w2_scale"], None, rw, rids, "silu", **args)
+    extra = O.fused_moe("fp8block", layer["x"], shared["w13"], shared["w13_scale"], None, shared["w2"],
+                        shared["w2_scale"], None, torch.ones(T, 1), torch.zeros(T, 1, dtype=torch.int32),
+                        "silu", **args)
+    check(sh, extra, 2e-2)
+    check(out, routed + extra, 2e-2)

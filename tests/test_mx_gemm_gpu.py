@@ -71,6 +71,10 @@ def run_mx(ops, Aq, Asf, Bq, Bs, rows, N, K, epi, bias=None, quant_out=False):
     (5, [100, 300, 0, 129, 171], 384, 384),
     (3, [1, 0, 260], 2880, 2880),               # the gpt-oss widths: K = 22.5 stages
     (8, [40, 0, 13, 128, 129, 255, 256, 257], 1024, 640),
+    (1, [128], 576, 192),                       # K tail in the last slot of the five-stage ring
+    (1, [128], 704, 192),                       # K tail in the first slot of the next round
+    (3, [700, 900, 704], 704, 1728),            # 171 tiles on 148 CTAs: two tiles per CTA, K tail
+    (2, [1100, 1204], 2880, 1728),              # the same with the gpt-oss K
 ])
 def test_mxfp4_native_store(ops, E, rows, K, N):
     Aq, Asf, Bq, Bs, rpe = make_case(E, rows, K, N, seed=K + N)

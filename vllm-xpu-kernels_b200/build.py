@@ -64,7 +64,8 @@ def build_capi(force=False):
     stamp = os.path.join(BUILD, "libb200moe.stamp")
     want = _hash(objs)
     if force or not os.path.exists(lib) or not os.path.exists(stamp) or open(stamp).read() != want:
-        _run(["nvcc", "-shared", "-o", lib] + objs + ["-lcudart"])
+        _run(["nvcc", "-shared", "-o", lib + ".tmp"] + objs + ["-lcudart"])
+        os.replace(lib + ".tmp", lib)  # a reader (or a snapshot of the tree) never sees half a file
         open(stamp, "w").write(want)
     return lib
 
@@ -83,11 +84,12 @@ def build_torch_ops(force=False):
     tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
     abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
     cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-D_GLIBCXX_USE_CXX11_ABI=%d" % abi,
-           "-DTORCH_EXTENSION_NAME=_b200_torch_ops"] + inc + [TORCH_SRC, "-o", out,
+           "-DTORCH_EXTENSION_NAME=_b200_torch_ops"] + inc + [TORCH_SRC, "-o", out + ".tmp",
            "-L", tlib, "-L", PKG, "-L", "/usr/local/cuda/lib64",
            "-lc10", "-ltorch_cpu", "-ltorch", "-lc10_cuda", "-ltorch_cuda", "-lb200moe", "-lcudart",
            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + tlib]
     _run(cmd)
+    os.replace(out + ".tmp", out)
     open(stamp, "w").write(want)
     return out
 

@@ -14,7 +14,7 @@ constexpr int kMaxTopK = 64;
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gather_kernel(
     T* __restrict__ out, const T* __restrict__ y, const float* __restrict__ weights,
-    const int32_t* __restrict__ row_map, int k, int H) {
+    const int32_t* __restrict__ row_map, const T* __restrict__ addend, int k, int H) {
   constexpr int V = 16 / sizeof(T);
   const int64_t t = blockIdx.x;
   __shared__ int rows[kMaxTopK];
@@ -26,8 +26,12 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(
   __syncthreads();
   for (int c = threadIdx.x * V; c < H; c += blockDim.x * V) {
     float acc[V];
+    if (addend) {  // e.g. the shared expert's row of this token, weight 1
+      load_f32<T, V>(addend + t * H + c, acc);
+    } else {
 #pragma unroll
-    for (int i = 0; i < V; ++i) acc[i] = 0.f;
+      for (int i = 0; i < V; ++i) acc[i] = 0.f;
+    }
     for (int j = 0; j < k; ++j) {
       const int r = rows[j];
       if (r < 0) continue;
@@ -76,8 +80,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
 
 using namespace b200moe;
 
-extern "C" int b200moe_moe_gather(void* out, const void* y, int dtype, const float* weights,
-                                  const int32_t* row_map, int T, int k, int H, void* stream) {
+static int gather_impl(void* out, const void* y, int dtype, const float* weights,
+                       const int32_t* row_map, const void* addend, int T, int k, int H, void* stream) {
   if (T < 0 || k <= 0 || k > kMaxTopK || H <= 0) return B200MOE_INVALID_ARG;
   if (T == 0) return B200MOE_OK;
   if (!out || !y || !weights || !row_map) return B200MOE_INVALID_ARG;
@@ -88,9 +92,21 @@ extern "C" int b200moe_moe_gather(void* out, const void* y, int dtype, const flo
     threads = threads > 256 ? 256 : threads;
     moe_gather_kernel<scalar_t><<<T, threads, 0, as_stream(stream)>>>(
         reinterpret_cast<scalar_t*>(out), reinterpret_cast<const scalar_t*>(y), weights, row_map,
-        k, H);
+        reinterpret_cast<const scalar_t*>(addend), k, H);
     return launch_status("moe_gather_kernel");
   });
+}
+
+extern "C" int b200moe_moe_gather(void* out, const void* y, int dtype, const float* weights,
+                                  const int32_t* row_map, int T, int k, int H, void* stream) {
+  return gather_impl(out, y, dtype, weights, row_map, nullptr, T, k, H, stream);
+}
+
+extern "C" int b200moe_moe_gather_add(void* out, const void* y, int dtype, const float* weights,
+                                      const int32_t* row_map, const void* addend, int T, int k,
+                                      int H, void* stream) {
+  if (!addend) return B200MOE_INVALID_ARG;
+  return gather_impl(out, y, dtype, weights, row_map, addend, T, k, H, stream);
 }
 
 extern "C" int b200moe_moe_sum(const void* in, void* out, int dtype, int T, int k, int H,

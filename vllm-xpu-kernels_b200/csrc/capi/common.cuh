@@ -8,6 +8,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "b200moe.h"
 
 namespace b200moe {
@@ -19,8 +21,13 @@ void set_last_error(const char* what, cudaError_t err);
 // (read and cleared by b200moe_device_status); null if it cannot be resolved.
 int* device_status_word();
 
+// Kernels this library has enqueued in this process (every launch goes through
+// launch_status); read by b200moe_launch_count.
+void count_launch();
+
 // Checks the launch that was just enqueued and maps a failure to a status.
 inline int launch_status(const char* what) {
+  count_launch();
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) {
     set_last_error(what, err);
@@ -30,6 +37,28 @@ inline int launch_status(const char* what) {
 }
 
 inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
+
+// Raises a kernel's dynamic shared-memory limit.  The attribute belongs to the (kernel,
+// device) pair, so it is set once per device this process launches on, under a lock.
+// `Tag` separates the bookkeeping of kernels that share one function-pointer type.
+template <typename Tag, typename Kernel>
+int ensure_dynamic_smem(Kernel kernel, size_t bytes, const char* what) {
+  constexpr int kMaxDev = 64;
+  static std::mutex mu;
+  static bool done[kMaxDev] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) dev = -1;
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && done[dev]) return B200MOE_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(bytes));
+  if (e != cudaSuccess) {
+    set_last_error(what, e);
+    return B200MOE_CUDA_ERROR;
+  }
+  if (dev >= 0) done[dev] = true;
+  return B200MOE_OK;
+}
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {

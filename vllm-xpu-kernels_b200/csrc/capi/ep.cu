@@ -479,16 +479,10 @@ extern "C" int b200moe_ep_gather(void* out, int dtype, const float* weights, con
     const int n_chunks = (row_bytes + cmax - 1) / cmax;
     const int chunk_bytes = ((row_bytes + n_chunks - 1) / n_chunks + 15) / 16 * 16;
     const size_t smem = 2 * static_cast<size_t>(k) * chunk_bytes;
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaError_t e = cudaFuncSetAttribute(ep_gather_bulk_kernel<scalar_t>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-      if (e != cudaSuccess) {
-        set_last_error("cudaFuncSetAttribute(ep_gather_bulk_kernel)", e);
-        return static_cast<int>(B200MOE_CUDA_ERROR);
-      }
-      attr_set = true;
-    }
+    struct Tag {};
+    const int arc = ensure_dynamic_smem<Tag>(ep_gather_bulk_kernel<scalar_t>, 100 * 1024,
+                                             "cudaFuncSetAttribute(ep_gather_bulk_kernel)");
+    if (arc != B200MOE_OK) return arc;
     int* status = device_status_word();
     if (!status) return static_cast<int>(B200MOE_CUDA_ERROR);
     const int64_t items = static_cast<int64_t>(T) * n_chunks;
@@ -517,16 +511,10 @@ extern "C" int b200moe_ep_dispatch(const void* hidden, const void* scales, int64
   if (smem > 200 * 1024) return B200MOE_UNSUPPORTED;
   int* status = device_status_word();
   if (!status) return B200MOE_CUDA_ERROR;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(ep_dispatch_bulk_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) {
-      set_last_error("cudaFuncSetAttribute(ep_dispatch_bulk_kernel)", e);
-      return B200MOE_CUDA_ERROR;
-    }
-    attr_set = true;
-  }
+  struct DispatchTag {};
+  const int arc = ensure_dynamic_smem<DispatchTag>(ep_dispatch_bulk_kernel, 200 * 1024,
+                                                   "cudaFuncSetAttribute(ep_dispatch_bulk_kernel)");
+  if (arc != B200MOE_OK) return arc;
   int per_sm = static_cast<int>((216 * 1024) / (smem + 1024));
   per_sm = per_sm > 32 ? 32 : (per_sm < 1 ? 1 : per_sm);
   const int64_t pairs = static_cast<int64_t>(num_tokens) * topk;

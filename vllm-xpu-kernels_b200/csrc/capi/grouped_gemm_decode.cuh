@@ -429,17 +429,11 @@ int launch_decode(const b200moe_gemm_args& a, cudaStream_t st) {
   constexpr int kMaxDecodeKBlocks = 160;  // K <= 20480: the staged scales fit beside the stages
   if (a.K / kBK > kMaxDecodeKBlocks) return B200MOE_UNSUPPORTED;
   const size_t smem = C::SMEM_BYTES + static_cast<size_t>(a.K / kBK) * (kNTok + 2) * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(
-        decode_gemm_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-        static_cast<int>(C::SMEM_BYTES + kMaxDecodeKBlocks * (kNTok + 2) * sizeof(float)));
-    if (e != cudaSuccess) {
-      set_last_error("cudaFuncSetAttribute", e);
-      return B200MOE_CUDA_ERROR;
-    }
-    attr_set = true;
-  }
+  struct Tag {};  // one record per instantiation of this function
+  const int arc = ensure_dynamic_smem<Tag>(
+      decode_gemm_kernel<GATED>, C::SMEM_BYTES + kMaxDecodeKBlocks * (kNTok + 2) * sizeof(float),
+      "cudaFuncSetAttribute");
+  if (arc != B200MOE_OK) return arc;
   decode_gemm_kernel<GATED><<<kNumSMs, C::THREADS, smem, st>>>(map_tok, map_w, p);
   return launch_status("decode_gemm_kernel");
 }

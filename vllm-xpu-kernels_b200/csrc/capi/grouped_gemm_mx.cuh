@@ -89,19 +89,14 @@ __device__ __forceinline__ uint32_t mx_scale_byte(float amax, float* scale) {
   return e;
 }
 
+// The reader warps only run epilogues here (the scales are applied inside the MMA), one tile
+// behind the tensor pipe, so a row's results leave with plain 16-byte stores from the thread
+// that owns the row: no shared-memory staging, which leaves room for a fifth operand stage.
 template <typename C>
 __device__ __forceinline__ void mx_tile_epilogue(const MxParams& p, const TileCoord& tc, int g,
-                                                 bool row_ok, int64_t grow, float (&acc)[64],
-                                                 uint4* wbuf) {
-  const int lane = threadIdx.x & 31;
+                                                 bool row_ok, int64_t grow, float (&acc)[64]) {
   const int col0 = tc.n_tile * C::BN + g * 64;  // first accumulator column of this thread
   if (col0 >= p.N) return;
-  const int64_t warp_row0 = grow - lane;
-  const int warp_rows_valid = tc.rows_valid - static_cast<int>(warp_row0 - tc.row_start);
-  auto local_row = [&](int rr) -> void* {
-    if (rr >= warp_rows_valid) return nullptr;
-    return reinterpret_cast<uint8_t*>(p.D) + (warp_row0 + rr) * p.ldd * 2;
-  };
   if (p.bias) {
 #pragma unroll
     for (int j = 0; j < 64; ++j)
@@ -109,7 +104,7 @@ __device__ __forceinline__ void mx_tile_epilogue(const MxParams& p, const TileCo
         acc[j] += load_bias(p.bias, p.bias_dtype, static_cast<int64_t>(tc.expert) * p.N + col0 + j);
   }
   if constexpr (C::EPI == B200MOE_EPI_STORE) {
-    store_rows_coalesced<64>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, local_row);
+    if (row_ok) store_row16<64>(p.D, p.d_dtype, grow * p.ldd + col0, acc, p.N - col0);
   } else {  // SWIGLU_OAI: (gate, up) pairs are adjacent columns -> 32 results
     float o[32];
 #pragma unroll
@@ -146,8 +141,8 @@ __device__ __forceinline__ void mx_tile_epilogue(const MxParams& p, const TileCo
           for (int j = 0; j < n_valid; ++j) dst[j] = b[j];
         }
       }
-    } else {
-      store_rows_coalesced<32>(wbuf, lane, p.d_dtype, ocol0, o, n_valid, local_row);
+    } else if (row_ok) {
+      store_row16<32>(p.D, p.d_dtype, grow * p.ldd + ocol0, o, n_valid);
     }
   }
 }
@@ -162,7 +157,6 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ MxBarriers bars;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ uint4 epi_buf[C::EPI_WARPS][128];
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -216,7 +210,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint8_t* sfb_tile =
             p.b_sf + (static_cast<int64_t>(tc.expert) * num_kb * p.b_atoms + n0 / 128) * kMxAtomBytes;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
-          ok = mbar_wait(&bars.empty[stage], phase ^ 1u, abort_p);
+          ok = mbar_wait_spin(&bars.empty[stage], phase ^ 1u, abort_p);
           if (!ok) break;
           const bool tail = tail_skip && kb == num_kb - 1;
           uint8_t* a_dst = tiles + stage * C::STAGE_BYTES;
@@ -234,48 +228,83 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
-      int stage = 0;
+      // One thread feeds the tensor pipe, and an MMA of this shape takes about 100 cycles:
+      // the scalar instructions between two tcgen05.mma decide whether the pipe stays busy.
+      // So the stage index is a compile-time constant (the K loop is unrolled over the ring
+      // and runs across tile boundaries), every descriptor is a register base plus an
+      // immediate, and the instruction descriptors are constants.  Control flow around the
+      // MMAs is kept to whole blocks of straight-line issues: a per-instruction guard inside
+      // the unrolled loop (skip sub-block kk when kk < n) made the tail stage read the wrong
+      // sub-blocks whenever it fell on the first or last slot of the ring.
+      const uint32_t a0 = smem_u32(tiles);
+      const uint32_t sw_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version, 128-byte swizzle
+      const uint32_t sf_hi = (128u >> 4) | (1u << 14);                // SBO 128, version, no swizzle
+      const uint32_t a_lo0 = ((a0 & 0x3FFFFu) >> 4) | ((16u >> 4) << 16);
+      const uint32_t b_lo0 = a_lo0 + (C::A_BYTES >> 4);
+      const uint32_t sfa_lo0 = (smem_u32(sfa_smem) & 0x3FFFFu) >> 4;
+      const uint32_t sfb_lo0 = (smem_u32(sfb_smem) & 0x3FFFFu) >> 4;
+      const uint32_t sfa_t = tmem_base + kMxSfaCol;
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
       uint32_t phase = 0;
       int buf = 0;
       uint32_t buf_phase = 0;
       bool ok = true;
-      const uint32_t sfa_t = tmem_base + kMxSfaCol;
-      for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
-        const TileCoord tc = decode_tile(sched, t);
-        // a tile that starts inside a 128-row piece of the scales (N tile 192: every odd
-        // tile starts at row 64) reads its scale columns from that offset on
-        const uint32_t sfb_t = tmem_base + kMxSfbCol + ((tc.n_tile * C::BN) % 128) / 32;
-        ok = mbar_wait(&bars.tempty[buf], buf_phase ^ 1u, abort_p);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * C::ACC_STRIDE;
-        uint32_t accum = 0;
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-          ok = mbar_wait(&bars.full[stage], phase, abort_p);
+      int t = sched_id;
+      int kb = 0;
+      uint32_t d_tmem = 0, sfb_t = 0, accum = 0;
+      bool more = t < num_tiles;
+      while (more && ok) {
+#pragma unroll
+        for (int s = 0; s < C::STAGES; ++s) {
+          if (kb == 0) {
+            // next tile: its accumulator buffer must have been read out
+            const int n_tile = decode_tile(sched, t).n_tile;
+            // a tile that starts inside a 128-row piece of the scales (192-column tiles: every
+            // odd one starts at row 64) reads its scale columns from that offset on
+            sfb_t = tmem_base + kMxSfbCol + ((n_tile * C::BN) % 128) / 32;
+            ok = mbar_wait(&bars.tempty[buf], buf_phase ^ 1u, abort_p);
+            if (!ok) break;
+            d_tmem = tmem_base + buf * C::ACC_STRIDE;
+            accum = 0;
+          }
+          ok = mbar_wait_spin(&bars.full[s], phase, abort_p);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
-          const uint32_t b_addr = a_addr + C::A_BYTES;
-          tmem_cp_32x128b_x4(sfa_t, make_sdesc_rows16(smem_u32(sfa_smem + stage * kMxSfaBytes)));
+          tmem_cp_32x128b_x4(sfa_t, desc(sfa_lo0 + s * (kMxSfaBytes >> 4), sf_hi));
 #pragma unroll
           for (int a = 0; a < C::B_ATOMS; ++a)
             tmem_cp_32x128b_x4(tmem_base + kMxSfbCol + 4 * a,
-                               make_sdesc_rows16(smem_u32(sfb_smem + stage * C::SFB_BYTES + a * kMxAtomBytes)));
-          const int kk0 = (tail_skip && kb == num_kb - 1) ? tail_skip : 0;
-#pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            if (kk < kk0) continue;
-            const uint64_t a_desc = make_sdesc_sw128(a_addr + kk * 32, 16, 1024);
-            const uint64_t b_desc = make_sdesc_sw128(b_addr + kk * 32, 16, 1024);
-            const uint32_t idesc = make_idesc_mx(0u, 5u, 0u, BM, C::BN, kk, kk);
-            mma_mxf8f6f4(d_tmem, a_desc, b_desc, idesc, sfa_t, sfb_t, accum);
+                               desc(sfb_lo0 + (s * C::SFB_BYTES + a * kMxAtomBytes) / 16, sf_hi));
+          const uint32_t a_lo = a_lo0 + s * (C::STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + s * (C::STAGE_BYTES >> 4);
+          if (tail_skip && kb == num_kb - 1) {
+            // K % 128 == 64 (rows of packed 4-bit weights have a 32-byte pitch, so K is a multiple
+            // of 64): the stage was loaded at K-128 and its first two sub-blocks were issued with
+            // the stage before
+            mma_mxf8f6f4(d_tmem, desc(a_lo + 4, sw_hi), desc(b_lo + 4, sw_hi),
+                         make_idesc_mx(0u, 5u, 0u, BM, C::BN, 2, 2), sfa_t, sfb_t, accum);
+            mma_mxf8f6f4(d_tmem, desc(a_lo + 6, sw_hi), desc(b_lo + 6, sw_hi),
+                         make_idesc_mx(0u, 5u, 0u, BM, C::BN, 3, 3), sfa_t, sfb_t, 1u);
             accum = 1;
+          } else {
+            mma_mxf8f6f4(d_tmem, desc(a_lo, sw_hi), desc(b_lo, sw_hi),
+                         make_idesc_mx(0u, 5u, 0u, BM, C::BN, 0, 0), sfa_t, sfb_t, accum);
+            accum = 1;
+#pragma unroll
+            for (int kk = 1; kk < 4; ++kk)
+              mma_mxf8f6f4(d_tmem, desc(a_lo + kk * 2, sw_hi), desc(b_lo + kk * 2, sw_hi),
+                           make_idesc_mx(0u, 5u, 0u, BM, C::BN, kk, kk), sfa_t, sfb_t, 1u);
           }
-          mma_commit(&bars.empty[stage]);
-          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          mma_commit(&bars.empty[s]);
+          if (++kb == num_kb) {
+            mma_commit(&bars.tfull[buf]);
+            kb = 0;
+            if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+            t += sched_stride;
+            if (t >= num_tiles) { more = false; break; }
+          }
         }
-        if (ok) mma_commit(&bars.tfull[buf]);
-        if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
+        phase ^= 1u;
       }
     }
   } else if (warp == 2) {
@@ -323,7 +352,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
             }
             ow[c] = v;
           }
-          ok = mbar_wait(&bars.empty[stage], phase ^ 1u, abort_p);
+          ok = mbar_wait_spin(&bars.empty[stage], phase ^ 1u, abort_p);
           if (!ok) break;
           *reinterpret_cast<uint4*>(sfa_smem + stage * kMxSfaBytes + lane * 16) = o;
           fence_proxy_async_smem();
@@ -337,9 +366,8 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp >= 4) {
     // ---------------- accumulator readers / epilogue ----------------
-    const int ew = warp - 4;
     const int quad = warp & 3;
-    const int g = ew >> 2;
+    const int g = (warp - 4) >> 2;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     int buf = 0;
@@ -356,13 +384,13 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t src = tmem_base + lane_addr + buf * C::ACC_STRIDE + g * 64;
       tmem_ld_32x32(src, *reinterpret_cast<float(*)[32]>(acc));
       tmem_ld_32x32(src + 32, *reinterpret_cast<float(*)[32]>(acc + 32));
-      tmem_ld_wait();
+      tmem_ld_wait_on2(*reinterpret_cast<float(*)[32]>(acc), *reinterpret_cast<float(*)[32]>(acc + 32));
       // the accumulator is in registers: the MMA warp may start the tile after next
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars.tempty[buf]);
       if (++buf == 2) { buf = 0; buf_phase ^= 1u; }
-      mx_tile_epilogue<C>(p, tc, g, row_ok, grow, acc, epi_buf[ew]);
+      mx_tile_epilogue<C>(p, tc, g, row_ok, grow, acc);
     }
   }
 
@@ -398,26 +426,6 @@ inline int make_map_fp4(CUtensorMap* map, const void* base, uint64_t cols, uint6
     set_last_error("cuTensorMapEncodeTiled (packed 4-bit)", cudaErrorInvalidValue);
     return B200MOE_CUDA_ERROR;
   }
-  return B200MOE_OK;
-}
-
-// cudaFuncSetAttribute is per device: remember which devices have been set up.  `Tag`
-// makes the bookkeeping per kernel instantiation (all of them share one pointer type).
-template <typename Tag, typename Kernel>
-int ensure_dynamic_smem(Kernel kernel, size_t bytes, const char* what) {
-  static std::mutex mu;
-  static bool done[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
-  std::lock_guard<std::mutex> lock(mu);
-  if (done[dev]) return B200MOE_OK;
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(bytes));
-  if (e != cudaSuccess) {
-    set_last_error(what, e);
-    return B200MOE_CUDA_ERROR;
-  }
-  done[dev] = true;
   return B200MOE_OK;
 }
 

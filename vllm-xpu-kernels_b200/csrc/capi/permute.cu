@@ -348,6 +348,7 @@ int run_grouping(const GroupParams& p, const AlignOut& ao, int32_t* rows_per_key
     place_align_kernel<<<n_cta, kThreads, place_smem, st>>>(p, counts, ao);
   else
     place_remap_kernel<<<n_cta, kThreads, place_smem, st>>>(p, counts, row_map);
+  for (int i = 0; i < (ao.sorted_ids ? 3 : 2); ++i) count_launch();  // launch_status counts the last one
   return launch_status("stable grouping");
 }
 

@@ -199,6 +199,8 @@ __global__ void __launch_bounds__(128) grouped_topk_kernel(
 
   float s[VPT];
   float key[VPT];
+  uint32_t inf_in = 0;  // experts whose raw score is +-inf: they count for their group's score
+                        // but are never selected (grouped_topk.cpp:659-662 of the reference)
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int e = lane + 32 * i;
@@ -206,6 +208,7 @@ __global__ void __launch_bounds__(128) grouped_topk_kernel(
     if (e < E) {
       x = Elem<T>::to_f32(scores[row * E + e]);
       b = Elem<TB>::to_f32(bias[e]);
+      if (isinf(x)) inf_in |= 1u << i;
       if (scoring_func == 1) x = round_through<T>(1.0f / (1.0f + expf(-x)));
     }
     s[i] = x;
@@ -244,21 +247,32 @@ __global__ void __launch_bounds__(128) grouped_topk_kernel(
 
   // Stable top-`topk_group` over the n_group (<= 32) group scores.
   uint32_t group_mask = 0;
+  float last_group_score = -CUDART_INF_F;
   {
     bool taken = lane >= n_group;
     for (int j = 0; j < topk_group; ++j) {
       Best b{taken ? -CUDART_INF_F : my_group_score, taken ? kInvalidIdx : lane};
       float pay = 0.f;
       b = group_argmax<32>(b, pay);
+      last_group_score = b.idx == kInvalidIdx ? -CUDART_INF_F : b.key;
       if (b.idx == kInvalidIdx) break;
       group_mask |= 1u << b.idx;
       if (b.idx == lane) taken = true;
     }
   }
+  // Fewer than `topk_group` groups with a finite score: the reference kernel gives up on the
+  // row and returns experts 0..k-1 with weight 1/k each, unscaled (grouped_topk.cpp:608-624).
+  if (topk_group > 0 && last_group_score == -CUDART_INF_F) {
+    if (lane < k) {
+      values[row * k + lane] = 1.0f / static_cast<float>(k);
+      ids[row * k + lane] = lane;
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int e = lane + 32 * i;
-    if (e < E && !((group_mask >> (e / per)) & 1u)) key[i] = -CUDART_INF_F;
+    if (e < E && (!((group_mask >> (e / per)) & 1u) || ((inf_in >> i) & 1u))) key[i] = -CUDART_INF_F;
   }
 
   uint32_t taken = 0;
@@ -286,7 +300,9 @@ __global__ void __launch_bounds__(128) grouped_topk_kernel(
     }
   }
   if (lane < k) {
-    float w = renorm ? my_w / wsum : my_w;
+    // the reference kernel's denominator carries 1e-20 (grouped_topk.cpp:678-687): selected
+    // scores that are all zero give weight 0, not NaN; invisible in fp32 otherwise
+    float w = renorm ? my_w / (wsum + 1e-20f) : my_w;
     w *= scale;
     values[row * k + lane] = w;
     ids[row * k + lane] = my_id;

@@ -344,6 +344,23 @@ void remap_hidden_states(const Tensor& hidden_states, const OptTensor& hidden_st
         "remap_hidden_states");
 }
 
+void b200_moe_gather_add(Tensor& output, const Tensor& moe_output, const Tensor& topk_weights,
+                         const Tensor& row_map, const Tensor& addend) {
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "b200_moe_gather_add: topk_weights must be float32");
+  TORCH_CHECK(output.scalar_type() == moe_output.scalar_type() && addend.scalar_type() == output.scalar_type(),
+              "b200_moe_gather_add: dtype mismatch");
+  TORCH_CHECK(output.is_contiguous() && moe_output.is_contiguous() && topk_weights.is_contiguous() &&
+                  row_map.is_contiguous() && addend.is_contiguous() && addend.sizes() == output.sizes(),
+              "b200_moe_gather_add: contiguous tensors, addend shaped like the output");
+  TORCH_CHECK(row_map.scalar_type() == at::kInt, "b200_moe_gather_add: row map must be int32");
+  const int64_t T = output.size(0), H = output.size(1), k = topk_weights.size(1);
+  c10::cuda::CUDAGuard guard(output.device());
+  check(b200moe_moe_gather_add(output.data_ptr(), moe_output.data_ptr(), float_code(output, "b200_moe_gather_add"),
+                               topk_weights.data_ptr<float>(), row_map.data_ptr<int>(), addend.data_ptr(),
+                               T, k, H, cur_stream()),
+        "b200_moe_gather_add");
+}
+
 void moe_gather(Tensor& output, const Tensor& moe_output, const Tensor& topk_weights,
                 const Tensor& unpermuted_row_to_permuted_row, int64_t /*num_experts*/) {
   TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "moe_gather: topk_weights must be float32");
@@ -874,6 +891,9 @@ TORCH_LIBRARY(B200MOE_NS_MOE_C, m) {
   m.def(
       "moe_gather(Tensor! output, Tensor moe_output, Tensor topk_weights, Tensor "
       "unpermuted_row_to_permuted_row, int num_experts) -> ()");
+  m.def(
+      "b200_moe_gather_add(Tensor! output, Tensor moe_output, Tensor topk_weights, Tensor row_map, "
+      "Tensor addend) -> ()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
   m.def(
       "moe_lora_align_block_size(Tensor topk_ids, Tensor token_lora_mapping, int num_experts, int "
@@ -904,6 +924,7 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_MOE_C, CUDA, m) {
   m.impl("topk_softmax", &topk_softmax);
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
+  m.impl("b200_moe_gather_add", &b200_moe_gather_add);
   m.impl("init_expert_map", &init_expert_map);
   m.impl("batched_moe_align_block_size", &batched_moe_align_block_size);
   m.impl("moe_lora_align_block_size", &moe_lora_align_block_size);

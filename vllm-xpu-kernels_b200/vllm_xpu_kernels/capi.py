@@ -42,6 +42,7 @@ SIGNATURES = {
     "b200moe_version": (c_char_p, []),
     "b200moe_status_string": (c_char_p, [c_int]),
     "b200moe_last_error": (c_char_p, []),
+    "b200moe_launch_count": (ctypes.c_longlong, []),
     "b200moe_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                      c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200moe_topk_sigmoid": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
@@ -64,6 +65,8 @@ SIGNATURES = {
                                             c_void_p]),
     "b200moe_moe_gather": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                    c_int, c_void_p]),
+    "b200moe_moe_gather_add": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                       c_int, c_int, c_void_p]),
     "b200moe_moe_sum": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                 c_void_p, c_void_p]),
     "b200moe_moe_lora_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_void_p, c_int,

@@ -223,7 +223,22 @@ class PeerExpertParallel:
         if rc != 0:
             raise RuntimeError(f"{what}: {self.capi.status_string(rc)} ({self.lib.b200moe_last_error().decode()})")
 
+    def check_call(self, hidden, topk_ids, scales):
+        """Refuses a call that does not fit the buffers sized at construction: more tokens or
+        another top-k would make the address tables and the exchange buffers too small."""
+        T, k = topk_ids.shape
+        if T > self.T or k != self.k:
+            raise ValueError(f"PeerExpertParallel was built for at most {self.T} tokens with top-{self.k}; "
+                             f"got {T} tokens with top-{k}")
+        if hidden.shape[0] != T or hidden.shape[1] * hidden.element_size() != self.row_bytes:
+            raise ValueError(f"hidden states must be [{T}, .] rows of {self.row_bytes} bytes; "
+                             f"got {tuple(hidden.shape)} {hidden.dtype}")
+        got = 0 if scales is None else scales.shape[1] * scales.element_size()
+        if got != self.scale_row_bytes or (scales is not None and scales.shape[0] != T):
+            raise ValueError(f"activation scales must be rows of {self.scale_row_bytes} bytes; got {got}")
+
     def apply(self, output, hidden, topk_weights, topk_ids, scales=None):
+        self.check_call(hidden, topk_ids, scales)
         lib, G, me = self.lib, self.G, self.rank
         T, k = topk_ids.shape
         dev = hidden.device

@@ -19,10 +19,16 @@ Recipes, detected from the weight dtypes as the reference does
   as ``a1q_scale`` or quantised here), tcgen05 kind::f8f6f4 with the scales
   applied per 128 of K; SiLU*mul and the re-quantisation for the second GEMM are
   one fused kernel.
-* MXFP4 weights ``[E, N, K/2]`` + e8m0 scales ``[E, N, K/32]``: expanded once,
-  exactly, to bf16 ``[E, N, K]`` at construction (every e2m1 x 2^e product is a
-  bf16 number) and run on the 16-bit path with bf16 activations, which is the
-  W4A16 arithmetic of the reference kernel.
+* MXFP4 weights ``[E, N, K/2]`` + e8m0 scales ``[E, N, K/32]``: the weights stay
+  4-bit in memory.  Activations are quantised to MXFP8 (e4m3 with one e8m0
+  scale per 32 columns, the quantisation moe_utils.py:84-109 of the reference
+  applies to activations) and both scale sets are applied inside tcgen05.mma
+  kind::mxf8f6f4.block_scale; SwigluOAI and the re-quantisation for the second
+  GEMM run in the first GEMM's epilogue.  ``VLLM_XPU_FUSED_MOE_USE_MXFP4_FP8``
+  (the reference's ``mxfp4_fp8`` recipe: FP8 activations on MXFP4 weights)
+  selects the same path.  ``B200MOE_MXFP4_W4A16=1`` gives the W4A16 arithmetic
+  of the reference kernel instead: weights expanded once, exactly, to bf16
+  ``[E, N, K]`` (every e2m1 x 2^e product is a bf16 number), bf16 activations.
 """
 import contextlib
 import math
@@ -58,13 +64,20 @@ def _get_weights_dtype(weight, scales):
     return is_fp8, is_int4, is_mxfp4, is_mxfp8, is_block_fp8
 
 
+USE_MXFP4_FP8_ENV = "VLLM_XPU_FUSED_MOE_USE_MXFP4_FP8"
+
+
+def _is_env_enabled(name: str, default: str = "0") -> bool:
+    return os.environ.get(name, default).strip().upper() in ("1", "ON", "TRUE", "YES", "Y")
+
+
 def _get_recipe(is_fp8, is_mxfp8, is_mxfp4, is_int4, is_block_fp8):
     if is_mxfp8:
         return "mxfp8"
     if is_block_fp8:
         return "fp8block"
     if is_mxfp4:
-        return "mxfp4"
+        return "mxfp4_fp8" if _is_env_enabled(USE_MXFP4_FP8_ENV) else "mxfp4"
     if is_int4:
         return "int4"
     if is_fp8:
@@ -109,8 +122,6 @@ class XpuFusedMoe:
         self.is_fp8, self.is_int4, self.is_mxfp4, self.is_mxfp8, self.is_block_fp8 = flags
         self.recipe = _get_recipe(self.is_fp8, self.is_mxfp8, self.is_mxfp4, self.is_int4,
                                   self.is_block_fp8)
-        if self.recipe == "mxfp4_fp8":
-            raise NotImplementedError("the mxfp4 x fp8-activation recipe is not part of the B200 path")
         self._act_code = _ACT_CODES.get("swigluoai" if _is_swigluoai(activation) else activation)
         if self._act_code is None:
             raise ValueError(f"Unsupported FusedMoe activation: {activation}.")
@@ -141,12 +152,26 @@ class XpuFusedMoe:
         self.ep_rank, self.ep_size = ep_rank, ep_size
         self.gemm1_clamp_limit = gemm1_clamp_limit
 
+        self._mx_native = False
         if self.is_mxfp4:
-            # One-time exact expansion; tagged on the object so it happens once.
-            self._w13_16 = torch.ops._xpu_C.b200_dequant_weights(
-                w13.view(torch.uint8), w13_scales.view(torch.uint8))
-            self._w2_16 = torch.ops._xpu_C.b200_dequant_weights(
-                w2.view(torch.uint8), w2_scales.view(torch.uint8))
+            hidden = w13.shape[-1] * 2
+            # the block-scaled tensor-core path reads packed 4-bit rows with TMA: 32-byte row pitch
+            self._mx_native = (hidden % 64 == 0 and self.inter_size % 64 == 0 and hidden >= 128
+                               and self.inter_size >= 128 and activation != "relu2_no_mul"
+                               and (self.recipe == "mxfp4_fp8"
+                                    or not _is_env_enabled("B200MOE_MXFP4_W4A16")))
+            if self._mx_native:
+                # weight scales rearranged once into the order the tensor core reads them
+                self._w13_sf = torch.ops._xpu_C.b200_mx_prepare_weight_scales(
+                    w13_scales.view(torch.uint8), hidden)
+                self._w2_sf = torch.ops._xpu_C.b200_mx_prepare_weight_scales(
+                    w2_scales.view(torch.uint8), self.inter_size)
+            else:
+                # W4A16: one-time exact expansion to bf16
+                self._w13_16 = torch.ops._xpu_C.b200_dequant_weights(
+                    w13.view(torch.uint8), w13_scales.view(torch.uint8))
+                self._w2_16 = torch.ops._xpu_C.b200_dequant_weights(
+                    w2.view(torch.uint8), w2_scales.view(torch.uint8))
 
         # Optional list; when set, apply() appends (stage, start_event, end_event)
         # for each stage, the way the reference's benchmark brackets its stages
@@ -185,7 +210,7 @@ class XpuFusedMoe:
 
     # ------------------------------------------------------------------
     def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
-              a1q_scale=None, row_destinations=None):
+              a1q_scale=None, row_destinations=None, shared_output=None):
         """output[T, H] = sum_j w[t, j] * Expert_{ids[t, j]}(hidden_states[t]).
 
         ``hidden_states`` is bf16/fp16 ``[T, H]``, or already quantised
@@ -196,7 +221,11 @@ class XpuFusedMoe:
         ``row_destinations`` (not in the reference signature; used by the expert-parallel
         exchange): a callable that gets the ``[T, k]`` row map and returns an int64 device
         table with, per permuted row, the address the second GEMM must store that row at.
-        ``output`` is then not written and the weighted combine is the caller's."""
+        ``output`` is then not written and the weighted combine is the caller's.
+
+        ``shared_output`` (not in the reference signature): ``[T, H]`` rows added to the
+        routed result inside the combine, weight 1 - the output of a shared expert every
+        token passes through (see ``dense``)."""
         num_rows, hidden_size = hidden_states.shape
         k = topk_ids.shape[1]  # n_experts_per_token, or 1 for rows that arrive already dispatched
         R = num_rows * k
@@ -210,14 +239,20 @@ class XpuFusedMoe:
                 and self.activation == "silu" and not (self.gemm1_clamp_limit or 0) > 0
                 and self.inter_size % 128 == 0):
             return self._apply_decode(output, hidden_states, topk_weights, topk_ids, expert_map,
-                                      a1q_scale)
+                                      a1q_scale, shared_output)
         if self.is_block_fp8 and a1q_scale is None:
             # dynamic per-token-group-128 quantisation, once per token (not per routed row)
             from .moe_utils import quant_fp8_block_act
             hidden_states, a1q_scale = quant_fp8_block_act(hidden_states)
+        if self._mx_native:
+            if a1q_scale is None:
+                hidden_states, a1q_scale = torch.ops._xpu_C.b200_quant_mxfp8(hidden_states)
+            else:
+                a1q_scale = self._pad_mx_scales(a1q_scale, hidden_size)
         act_quant = a1q_scale is not None
-        if act_quant and not self.is_block_fp8:
-            raise NotImplementedError("quantised activations are only taken with block-FP8 weights")
+        if act_quant and not (self.is_block_fp8 or self._mx_native):
+            raise NotImplementedError(
+                "quantised activations are taken with block-FP8 weights and on the MXFP4 tensor-core path")
 
         remapped = torch.empty((R, hidden_size), dtype=hidden_states.dtype, device=dev)
         remapped_scales = (torch.empty((R, a1q_scale.shape[1]), dtype=a1q_scale.dtype, device=dev)
@@ -235,8 +270,30 @@ class XpuFusedMoe:
         if row_ptr is not None:
             return
         with self._stage("gather"):
-            torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
-                                        self.num_experts)
+            if shared_output is not None:
+                torch.ops._moe_C.b200_moe_gather_add(output, gemm2_out, topk_weights, row_map,
+                                                     shared_output)
+            else:
+                torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
+                                            self.num_experts)
+
+    def dense(self, hidden_states, a1q_scale=None, out_dtype=torch.bfloat16):
+        """A layer built with one expert used as a plain gated MLP over all rows: the shared
+        expert of a DeepSeek-V3-style layer (the reference project has no operator for it; it
+        is the grouped GEMM with a single group).  Returns ``[T, H]``; pass it to ``apply`` of
+        the routed layer as ``shared_output``."""
+        assert self.num_experts == 1, "dense() is for a layer built with a single expert"
+        T = hidden_states.shape[0]
+        if self.is_block_fp8 and a1q_scale is None:
+            from .moe_utils import quant_fp8_block_act
+            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states)
+        elif self._mx_native and a1q_scale is None:
+            hidden_states, a1q_scale = torch.ops._xpu_C.b200_quant_mxfp8(hidden_states)
+        rows = getattr(self, "_dense_rows", None)
+        if rows is None or rows[0] != T:
+            rows = (T, torch.full((1,), T, dtype=torch.int32, device=hidden_states.device))
+            self._dense_rows = rows
+        return self.run_experts(hidden_states, a1q_scale, rows[1], out_dtype)
 
     def run_experts(self, rows, row_scales, rows_per_expert, out_dtype, row_ptr=None, out=None):
         """The two grouped GEMMs with the activation between them on rows that are already
@@ -252,6 +309,10 @@ class XpuFusedMoe:
         oai = _is_swigluoai(self.activation)
         gemm = torch.ops._xpu_C.b200_grouped_gemm
         clamp = self.gemm1_clamp_limit is not None and self.gemm1_clamp_limit > 0
+        if self._mx_native:
+            if row_ptr is not None:
+                raise NotImplementedError("per-row destinations are not taken on the MXFP4 tensor-core path")
+            return self._run_experts_mx(rows, row_scales, rows_per_expert, out_dtype, out, oai, clamp)
         if self.is_block_fp8:
             K2 = I * self.inter_size_scale
             if (self.activation == "silu" and not clamp and I % 128 == 0
@@ -307,6 +368,46 @@ class XpuFusedMoe:
                      E, EPI_STORE, layout, 1.702, 7.0, None, row_ptr)
         return gemm2_out
 
+    @staticmethod
+    def _pad_mx_scales(scales, width):
+        """e8m0 scales [T, width/32] (uint8 or float8_e8m0fnu) -> uint8 [T, 16*ceil(width/512)],
+        the row pitch the block-scaled GEMM reads 16 bytes at a time."""
+        sf = scales.view(torch.uint8)
+        pitch = (width + 511) // 512 * 16
+        if sf.shape[1] == pitch:
+            return sf.contiguous()
+        out = torch.full((sf.shape[0], pitch), 127, dtype=torch.uint8, device=sf.device)
+        out[:, :width // 32] = sf[:, :width // 32]
+        return out
+
+    def _run_experts_mx(self, rows, row_sf, rows_per_expert, out_dtype, out, oai, clamp):
+        """MXFP8 rows x MXFP4 weights on the block-scaled tensor-core path."""
+        R, H = rows.shape
+        dev = rows.device
+        I, E = self.inter_size, self.num_experts
+        gemm = torch.ops._xpu_C.b200_grouped_gemm_mx
+        w13, w2 = self.w13.view(torch.uint8), self.w2.view(torch.uint8)
+        pitch_i = (I + 511) // 512 * 16
+        if oai and not clamp:
+            # SwigluOAI and the MXFP8 quantisation of its result run in the GEMM's epilogue
+            act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
+            act_sf = torch.empty((R, pitch_i), dtype=torch.uint8, device=dev)
+            with self._stage("gemm1"):
+                gemm(rows, row_sf, w13, self._w13_sf, self.w13_bias, act_q, act_sf, rows_per_expert,
+                     2 * I, H, E, EPI_SWIGLU_OAI, 1.702, 7.0)
+        else:
+            gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
+            with self._stage("gemm1"):
+                gemm(rows, row_sf, w13, self._w13_sf, self.w13_bias, gemm1_out, None, rows_per_expert,
+                     2 * I, H, E, EPI_STORE, 1.702, 7.0)
+            with self._stage("act_quant"):
+                act_q, act_sf = torch.ops._xpu_C.b200_quant_mxfp8(self._activate(gemm1_out))
+        gemm2_out = out if out is not None else torch.empty((R, H), dtype=out_dtype, device=dev)
+        with self._stage("gemm2"):
+            gemm(act_q, act_sf, w2, self._w2_sf, self.w2_bias, gemm2_out, None, rows_per_expert, H, I, E,
+                 EPI_STORE, 1.702, 7.0)
+        return gemm2_out
+
     def _decode_regime(self, routed_rows: int) -> bool:
         """Whether to run the two GEMMs on the decode-regime kernel (weights on the M side of
         the MMA, 32 tokens per tile).  With at most about one routed row per local expert it is
@@ -318,7 +419,8 @@ class XpuFusedMoe:
             return forced == "1"
         return routed_rows <= self.num_experts
 
-    def _apply_decode(self, output, hidden_states, topk_weights, topk_ids, expert_map, a1q_scale):
+    def _apply_decode(self, output, hidden_states, topk_weights, topk_ids, expert_map, a1q_scale,
+                      shared_output=None):
         """Same sequence of launches as the default path, with the two grouped GEMMs on the
         decode-regime kernel (weights on the M side of the MMA, 32 tokens per tile); the first
         one quantises its output per token per 128 columns in its epilogue."""
@@ -351,7 +453,11 @@ class XpuFusedMoe:
             gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out, rows_per_expert,
                  H, I, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None, None, A_SCALE_ROW_MAJOR_DECODE)
         with self._stage("gather"):
-            torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
+            if shared_output is not None:
+                torch.ops._moe_C.b200_moe_gather_add(output, gemm2_out, topk_weights, row_map,
+                                                     shared_output)
+            else:
+                torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
 
     def _weights_16(self, dtype):
         """(w13, w2, layout) as 16-bit operands of the grouped GEMM."""
