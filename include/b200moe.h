@@ -428,8 +428,33 @@ int b200moe_device_status(void* stream, int* status_host);
  * NVLink/NVSwitch domain.  `peer_bases_host` is a HOST array of `world` device
  * addresses: the base of every rank's symmetric allocation, mapped into this
  * process.  Offsets are byte offsets inside that allocation, the same on every
- * rank.  All four only enqueue kernels that write; the device-wide barriers
- * between them are the caller's. */
+ * rank.  The data entry points only enqueue kernels that write or read; the
+ * cross-rank ordering between them is b200moe_ep_barrier on the same stream. */
+
+/* Barrier over the ranks of the symmetric allocation, as one small kernel on
+ * `stream`: orders everything this rank's earlier kernels on the stream wrote to
+ * peer memory before the peers' later kernels, and the other way round.  The
+ * allocation holds B200MOE_EP_BARRIER_CHANNELS x 16 u32 flag words at
+ * `flags_offset` (zero before the first barrier, never written by the host
+ * afterwards); `epochs` is this rank's own device array u32
+ * [B200MOE_EP_BARRIER_CHANNELS], zero at first.  Every rank must call the
+ * barriers of one channel in the same order.  The wait polls local memory and is
+ * bounded: after `budget_ns` (<= 0: B200MOE_EP_BARRIER_TIMEOUT_MS from the
+ * environment, default 30 s) the kernel leaves B200MOE_TIMEOUT in the device
+ * status word (b200moe_device_status) and returns; later kernels then run on
+ * whatever the peers have delivered so far, inside their buffers. */
+#define B200MOE_EP_BARRIER_CHANNELS 4
+int b200moe_ep_barrier(const int64_t* peer_bases_host, int64_t flags_offset,
+                       int my_rank, int world, int channel, uint32_t* epochs,
+                       int64_t budget_ns, void* stream);
+
+/* The same protocol with all `world` ranks played by the CTAs of one
+ * cooperative launch on one device (rank r's flag words at flags + r * CHANNELS *
+ * 16, its epochs at epochs + r * CHANNELS), for exercising it where each rank
+ * cannot have a GPU of its own; ranks in `absent_mask` never arrive. */
+int b200moe_ep_barrier_emulated(uint32_t* flags, uint32_t* epochs, int world,
+                                int channel, uint32_t absent_mask, int64_t budget_ns,
+                                void* stream);
 
 /* Writes my rows-per-global-expert (i32 [num_counts], num_counts = world *
  * experts_per_rank) into row `my_rank` of every rank's i32 [world, num_counts]

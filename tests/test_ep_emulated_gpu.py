@@ -153,3 +153,75 @@ def test_exchange_with_emulated_ranks(ops, G, E_loc, T, k, H, scale_bytes, gathe
             ops._moe_C.moe_gather(res, ret, rk.w, rk.row_map, 0)
             torch.testing.assert_close(res.float(), expected(rk).float(), atol=2e-2, rtol=2e-2)
     assert ops._xpu_C.b200_device_status() == 0
+
+
+# ---- the cross-rank barrier, all ranks as the CTAs of one cooperative launch ----------------
+CH = 4          # B200MOE_EP_BARRIER_CHANNELS
+MAXR = 16
+
+
+def _status(lib):
+    st = ctypes.c_int(0)
+    assert lib.b200moe_device_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(st)) == 0
+    return st.value
+
+
+def _barrier(lib, flags, epochs, G, channel, absent=0, budget_ns=0):
+    return lib.b200moe_ep_barrier_emulated(flags.data_ptr(), epochs.data_ptr(), G, channel, absent,
+                                           budget_ns, torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("G", [1, 2, 8, 16])
+def test_barrier_epochs_advance_together(ops, G):
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+    flags = torch.zeros(G * CH * MAXR, dtype=torch.int32, device=DEV)
+    epochs = torch.zeros(G * CH, dtype=torch.int32, device=DEV)
+    for _ in range(3):
+        assert _barrier(lib, flags, epochs, G, 0) == capi.OK
+    assert _barrier(lib, flags, epochs, G, 2) == capi.OK
+    assert _status(lib) == 0
+    want = torch.tensor([3, 0, 1, 0], dtype=torch.int32).repeat(G)
+    assert torch.equal(epochs.cpu(), want)
+    f = flags.cpu().view(G, CH, MAXR)
+    assert (f[:, 0, :G] == 3).all() and (f[:, 2, :G] == 1).all()
+    assert (f[:, :, G:] == 0).all() and (f[:, 1] == 0).all() and (f[:, 3] == 0).all()
+
+
+def test_barrier_gives_up_on_a_missing_rank_and_recovers(ops):
+    """Rank 2 of 4 does not arrive: the others wait out their budget, report B200MOE_TIMEOUT
+    and carry on.  When the late rank then runs its barrier it finds the others' flags already
+    there, and the next common barrier is clean again."""
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+    G = 4
+    flags = torch.zeros(G * CH * MAXR, dtype=torch.int32, device=DEV)
+    epochs = torch.zeros(G * CH, dtype=torch.int32, device=DEV)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    assert _barrier(lib, flags, epochs, G, 1, absent=0b0100, budget_ns=20_000_000) == capi.OK
+    t1.record()
+    assert _status(lib) == capi.TIMEOUT
+    assert 15.0 < t0.elapsed_time(t1) < 500.0          # one budget of 20 ms, not a hang
+    assert epochs.cpu().view(G, CH)[:, 1].tolist() == [1, 1, 0, 1]
+    assert _barrier(lib, flags, epochs, G, 1, absent=0b1011, budget_ns=20_000_000) == capi.OK
+    assert _status(lib) == 0
+    assert epochs.cpu().view(G, CH)[:, 1].tolist() == [1, 1, 1, 1]
+    assert _barrier(lib, flags, epochs, G, 1, budget_ns=20_000_000) == capi.OK
+    assert _status(lib) == 0
+    assert epochs.cpu().view(G, CH)[:, 1].tolist() == [2, 2, 2, 2]
+    x = torch.ones(8, device=DEV)
+    assert float((x * 2).sum()) == 16.0                # the context is still usable
+
+
+def test_barrier_argument_checks(ops):
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+    flags = torch.zeros(2 * CH * MAXR, dtype=torch.int32, device=DEV)
+    epochs = torch.zeros(2 * CH, dtype=torch.int32, device=DEV)
+    assert _barrier(lib, flags, epochs, 17, 0) == capi.INVALID_ARG
+    assert _barrier(lib, flags, epochs, 2, CH) == capi.INVALID_ARG
+    bases = (ctypes.c_int64 * 2)(flags.data_ptr(), flags.data_ptr())
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.b200moe_ep_barrier(bases, 0, 2, 2, 0, epochs.data_ptr(), 0, st) == capi.INVALID_ARG
+    assert lib.b200moe_ep_barrier(bases, 0, 0, 2, 0, None, 0, st) == capi.INVALID_ARG

@@ -79,3 +79,77 @@ def test_expert_parallel_two_gpus(recipe, backend):
         result = m.dict()
         mp.spawn(_worker, args=(2, port, recipe, backend, result), nprocs=2, join=True)
         assert result[0] and result[1]
+
+
+def _barrier_worker(rank, world, port, result):
+    for p in (ROOT, PKG_DIR):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import ctypes
+
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+    n = 1 << 20
+    buf = symm_mem.empty(4096 + n * 4, dtype=torch.uint8, device=dev)
+    hdl = symm_mem.rendezvous(buf, dist.group.WORLD.group_name)
+    buf.zero_()
+    torch.cuda.synchronize()
+    dist.barrier()
+    bases = (ctypes.c_int64 * world)(*[int(p) for p in hdl.buffer_ptrs])
+    epochs = torch.zeros(capi.EP_BARRIER_CHANNELS, dtype=torch.int32, device=dev)
+    st = torch.cuda.current_stream().cuda_stream
+
+    def barrier(ch, budget=0):
+        assert lib.b200moe_ep_barrier(bases, 0, rank, world, ch, epochs.data_ptr(), budget, st) == capi.OK
+
+    def status():
+        s = ctypes.c_int(0)
+        assert lib.b200moe_device_status(st, ctypes.byref(s)) == capi.OK
+        return s.value
+
+    ok = True
+    # (1) ordering: write into the peer's memory, barrier, read what the peer wrote into mine
+    mine = buf[4096:].view(torch.int32)
+    peer = hdl.get_buffer((rank + 1) % world, (n,), torch.int32, 1024)
+    for it in range(3):
+        peer.copy_(torch.arange(n, dtype=torch.int32, device=dev) + (rank + 1) * 1000 + it)
+        barrier(0)
+        src = (rank - 1) % world
+        ok = ok and bool((mine == torch.arange(n, dtype=torch.int32, device=dev) + (src + 1) * 1000 + it).all())
+        barrier(0)   # nobody overwrites a buffer that is still being checked
+    ok = ok and status() == 0
+    # (2) a rank that skips a barrier: the other one gives up after its budget and says so
+    dist.barrier()
+    if rank == 0:
+        barrier(1, 50_000_000)
+        ok = ok and status() == capi.TIMEOUT
+    torch.cuda.synchronize()
+    dist.barrier()          # the skipped barrier is over on rank 0 before rank 1 goes on
+    if rank != 0:
+        barrier(1, 50_000_000)      # late: the flag of rank 0 is already there
+        ok = ok and status() == 0
+    barrier(1, 5_000_000_000)
+    ok = ok and status() == 0 and epochs.cpu().tolist()[:2] == [6, 2]
+    result[rank] = ok
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_bounded_barrier_two_gpus():
+    """The library's cross-rank barrier between two processes with a GPU each: it orders peer
+    writes, and when one rank does not call it the other returns after its budget with
+    B200MOE_TIMEOUT in the status word.  No rank exits or faults; the failure is played by
+    the host skipping a call between steps."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with mp.Manager() as m:
+        result = m.dict()
+        mp.spawn(_barrier_worker, args=(2, 29641, result), nprocs=2, join=True)
+        assert result[0] and result[1]

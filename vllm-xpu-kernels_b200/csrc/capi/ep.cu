@@ -31,9 +31,14 @@
 // The receive buffer is already in the order the grouped GEMM wants, so the
 // receiving side runs no permutation at all.
 //
-// The barriers between the steps are issued by the caller on the same stream.
-// No kernel here spins on remote data; the bulk-copy kernels wait only on the
-// mbarrier of their own copies, with a cycle budget.
+// The barriers between the steps are kernels of this file too (ep_barrier): every
+// rank stores a rising epoch number into a flag word it owns in each peer's
+// allocation and then polls its own copy of the words until every peer's epoch
+// has arrived.  The poll reads local memory only and is bounded by a wall-clock
+// budget; on expiry the kernel leaves B200MOE_TIMEOUT in the device status word
+// and returns, so a rank that never shows up costs the others one budget and a
+// wrong result, not a hung GPU.  The bulk-copy kernels wait only on the mbarrier
+// of their own copies, with a cycle budget.
 #include "common.cuh"
 #include "tcgen05.cuh"
 
@@ -370,6 +375,89 @@ __global__ void __launch_bounds__(32) ep_dispatch_bulk_kernel(
   if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
+// ---- cross-rank barrier ----------------------------------------------------------
+// Flag words: kBarrierChannels x kMaxRanks u32 in every rank's allocation; word [c][s] of
+// rank r is written by rank s only.  A channel's epoch counts the barriers this rank has
+// run on it and lives in this rank's own memory; ranks call the barriers of a channel in
+// the same order, so equal epochs mean the same barrier.  "Arrived" is epoch - want >= 0 in
+// wrap-around arithmetic: a fast peer that is already one barrier further still counts.
+constexpr int kBarrierChannels = B200MOE_EP_BARRIER_CHANNELS;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// One warp; lane s talks to rank s.  Everything this rank's earlier kernels on the stream
+// wrote to peer memory is ordered before the flag by the system-scope fence + release store;
+// the acquire load orders the peers' writes before whatever this stream runs next.
+__device__ __forceinline__ void ep_barrier_body(const PeerPtrs& peers, int64_t flags_off, int me,
+                                                int G, int channel, uint32_t* epoch,
+                                                long long budget_ns, int* status) {
+  const int s = threadIdx.x;
+  const uint32_t want = epoch[channel] + 1u;
+  bool late = false;
+  if (s < G) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<uint32_t*>(peers.base[s] + flags_off) + channel * kMaxRanks + me, want);
+    const uint32_t* mine =
+        reinterpret_cast<const uint32_t*>(peers.base[me] + flags_off) + channel * kMaxRanks + s;
+    const unsigned long long t0 = globaltimer_ns();
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - want) < 0) {
+      if (static_cast<long long>(globaltimer_ns() - t0) > budget_ns) {
+        late = true;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  const bool any_late = __any_sync(0xffffffffu, late);
+  if (s == 0) {
+    epoch[channel] = want;  // the count advances either way: a late peer's next barrier still matches
+    if (any_late) atomicExch(status, B200MOE_TIMEOUT);
+  }
+}
+
+__global__ void __launch_bounds__(32) ep_barrier_kernel(PeerPtrs peers, int64_t flags_off, int me,
+                                                        int G, int channel, uint32_t* epoch,
+                                                        long long budget_ns, int* status) {
+  ep_barrier_body(peers, flags_off, me, G, channel, epoch, budget_ns, status);
+}
+
+// All ranks of the barrier as the CTAs of ONE cooperative launch over one device buffer
+// (CTA r is rank r; its flag words start at flags + r * channels * kMaxRanks, its epochs at
+// epochs + r * channels).  Kernels that wait on one another must not be separate launches
+// on one GPU, so this is how the protocol is exercised on a single device; ranks in
+// `absent_mask` return at once without arriving, which is how a missing rank is played.
+__global__ void __launch_bounds__(32) ep_barrier_emulated_kernel(uint32_t* flags, uint32_t* epochs,
+                                                                 int G, int channel,
+                                                                 uint32_t absent_mask,
+                                                                 long long budget_ns, int* status) {
+  const int me = blockIdx.x;
+  if ((absent_mask >> me) & 1u) return;
+  PeerPtrs peers;
+  for (int r = 0; r < kMaxRanks; ++r)
+    peers.base[r] = reinterpret_cast<uint8_t*>(flags + static_cast<int64_t>(r < G ? r : 0) * kBarrierChannels * kMaxRanks);
+  ep_barrier_body(peers, 0, me, G, channel, epochs + me * kBarrierChannels, budget_ns, status);
+}
+
+long long barrier_budget_ns(int64_t budget_ns) {
+  if (budget_ns > 0) return budget_ns;
+  // read per call: a host may shorten it for a drill without restarting
+  const char* env = getenv("B200MOE_EP_BARRIER_TIMEOUT_MS");
+  const long long ms = env ? atoll(env) : 0;
+  return (ms > 0 ? ms : 30000ll) * 1000000ll;
+}
+
 bool load_peers(const int64_t* peer_bases_host, int G, PeerPtrs* out) {
   if (!peer_bases_host || G <= 0 || G > kMaxRanks) return false;
   for (int i = 0; i < kMaxRanks; ++i)
@@ -381,6 +469,40 @@ bool load_peers(const int64_t* peer_bases_host, int G, PeerPtrs* out) {
 }  // namespace b200moe
 
 using namespace b200moe;
+
+extern "C" int b200moe_ep_barrier(const int64_t* peer_bases_host, int64_t flags_offset, int my_rank,
+                                  int world, int channel, uint32_t* epochs, int64_t budget_ns,
+                                  void* stream) {
+  PeerPtrs peers;
+  if (!load_peers(peer_bases_host, world, &peers) || my_rank < 0 || my_rank >= world || channel < 0 ||
+      channel >= kBarrierChannels || !epochs || flags_offset < 0 || flags_offset % 4 != 0)
+    return B200MOE_INVALID_ARG;
+  int* status = device_status_word();
+  if (!status) return B200MOE_CUDA_ERROR;
+  ep_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(peers, flags_offset, my_rank, world, channel,
+                                                     epochs, barrier_budget_ns(budget_ns), status);
+  return launch_status("ep_barrier_kernel");
+}
+
+extern "C" int b200moe_ep_barrier_emulated(uint32_t* flags, uint32_t* epochs, int world, int channel,
+                                           uint32_t absent_mask, int64_t budget_ns, void* stream) {
+  if (!flags || !epochs || world <= 0 || world > kMaxRanks || channel < 0 || channel >= kBarrierChannels)
+    return B200MOE_INVALID_ARG;
+  int* status = device_status_word();
+  if (!status) return B200MOE_CUDA_ERROR;
+  long long budget = barrier_budget_ns(budget_ns);
+  void* args[] = {&flags, &epochs, &world, &channel, &absent_mask, &budget, &status};
+  // cooperative: all `world` CTAs are resident together, or the launch fails
+  const cudaError_t err = cudaLaunchCooperativeKernel(
+      reinterpret_cast<const void*>(ep_barrier_emulated_kernel), dim3(world), dim3(32), args, 0,
+      as_stream(stream));
+  if (err != cudaSuccess) {
+    set_last_error("cudaLaunchCooperativeKernel(ep_barrier_emulated_kernel)", err);
+    return B200MOE_CUDA_ERROR;
+  }
+  count_launch();
+  return B200MOE_OK;
+}
 
 extern "C" int b200moe_ep_put_counts(const int32_t* send_counts, int num_counts,
                                      const int64_t* peer_bases_host, int64_t counts_offset,

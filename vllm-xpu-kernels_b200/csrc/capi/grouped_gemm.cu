@@ -553,51 +553,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-    } else if (warp == 1 && lane == 0 && rank == 0 && C::PROMOTE && !C::PAIR && C::B_MN_MAJOR &&
-               C::ACC_BUFS == 2 && C::STAGES % 2 == 0) {
-      // ---------------- MMA issuer, block-scaled FP8 ----------------
-      // Every 128 of K is an accumulation phase of its own (the readers apply the scales), so
-      // this thread keeps no per-tile state: it walks a flat sequence of phases.  One thread
-      // feeds the tensor pipe and an MMA of this shape takes 128 cycles, so the scalar work
-      // between two MMAs is kept minimal: the loop is unrolled over the operand ring, which
-      // makes the stage and the accumulator buffer compile-time constants, descriptors are a
-      // register base plus an immediate, and ready barriers are tested, not waited on.
-      const uint32_t a0 = smem_u32(tiles);
-      const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version, 128-byte swizzle
-      const uint32_t a_lo0 = ((a0 & 0x3FFFFu) >> 4) | ((16u >> 4) << 16);
-      const uint32_t b_lo0 = (((a0 + C::A_BYTES) & 0x3FFFFu) >> 4) | (((C::BK * kStageRowBytes) >> 4) << 16);
-      const uint32_t idesc = make_idesc(p.ab_fmt, p.ab_fmt, 0u, 1u, C::TILE_M, C::BN);
-      auto desc = [](uint32_t lo, uint32_t hi_) { return (static_cast<uint64_t>(hi_) << 32) | lo; };
-      long long todo = 0;  // phases this CTA issues
-      for (int t = sched_id; t < num_tiles; t += sched_stride) todo += num_kb;
-      uint32_t phase = 0, bph0 = 0, bph1 = 0;
-      bool ok = true;
-      while (todo > 0 && ok) {
-#pragma unroll
-        for (int s = 0; s < C::STAGES; ++s) {
-          if (todo == 0) break;
-          constexpr int kDummy = 0;
-          (void)kDummy;
-          if ((s & 1) == 0) { ok = mbar_wait_spin(&bars.tempty[0], bph0 ^ 1u, abort_p); bph0 ^= 1u; }
-          else { ok = mbar_wait_spin(&bars.tempty[1], bph1 ^ 1u, abort_p); bph1 ^= 1u; }
-          if (!ok) break;
-          ok = mbar_wait_spin(&bars.full[s], phase, abort_p);
-          if (!ok) break;
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (s & 1) * C::BN;
-          const uint32_t a_lo = a_lo0 + s * (C::STAGE_BYTES >> 4);
-          const uint32_t b_lo = b_lo0 + s * (C::STAGE_BYTES >> 4);
-          mma_f8(d_tmem, desc(a_lo, hi), desc(b_lo, hi), idesc, 0u);
-#pragma unroll
-          for (int kk = 1; kk < C::BK / C::UMMA_K; ++kk)
-            mma_f8(d_tmem, desc(a_lo + kk * 2, hi), desc(b_lo + kk * ((C::UMMA_K * kStageRowBytes) >> 4), hi),
-                   idesc, 1u);
-          mma_commit(&bars.empty[s]);
-          mma_commit(&bars.tfull[s & 1]);
-          --todo;
-        }
-        phase ^= 1u;
-      }
     } else if (warp == 1 && lane == 0 && rank == 0) {
       // ---------------- MMA issuer (the even CTA of a pair) ----------------
       const uint32_t idesc =

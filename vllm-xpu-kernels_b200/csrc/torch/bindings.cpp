@@ -640,9 +640,19 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
                   op, ": float8 activations need float32 per-token-group-128 scales");
       a.a_scale = A_scale->data_ptr<float>();
     }
+  } else if (bt == at::kChar) {
+    // the reference's INT4 recipe (int8 pairs + 16-bit group scales,
+    // csrc/xpu/grouped_gemm/xe_2/grouped_gemm_xe2_interface.hpp:193).  This operator keeps no
+    // state between calls, so it does not widen such weights on every call behind the
+    // caller's back: widen once and pass the result.
+    TORCH_CHECK(false, op, ": INT4 weights are widened once with _xpu_C.b200_expand_weights(B, scales, "
+                "\"int4\", dtype) (XpuFusedMoe(is_int4=True) does so at first use); pass the widened weights");
   } else if (bt == at::kFloat4_e2m1fn_x2 || (bt == at::kByte && B_scale.has_value())) {
+    // uint8 is accepted as a view of packed e2m1 pairs only together with one-byte (e8m0)
+    // scales; INT4 is int8 in the reference and never reaches this branch
     TORCH_CHECK(B_scale.has_value() && B_scale->element_size() == 1 && B_scale->is_contiguous(), op,
-                ": MXFP4 weights need e8m0 scales [E, N, K/32]");
+                ": MXFP4 weights need e8m0 scales [E, N, K/32] (uint8 weights with wider scales are "
+                "not a recipe of this operator)");
     TORCH_CHECK(K % 32 == 0, op, ": MXFP4 needs K to be a multiple of 32");
     a.recipe = B200MOE_RECIPE_MXFP4;
     a.b_scale = B_scale->data_ptr();

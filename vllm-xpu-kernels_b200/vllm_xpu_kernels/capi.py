@@ -10,6 +10,7 @@ from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int
 from ._loader import CAPI_PATH
 
 OK, INVALID_ARG, UNSUPPORTED, WORKSPACE_TOO_SMALL, CUDA_ERROR, TIMEOUT = 0, -1, -2, -3, -4, -5
+EP_BARRIER_CHANNELS = 4   # B200MOE_EP_BARRIER_CHANNELS of include/b200moe.h
 F32, F16, BF16, E4M3, I32, I64, U32, U8, E2M1X2 = range(9)
 RECIPE_BF16, RECIPE_FP8_BLOCK, RECIPE_MXFP4 = 0, 1, 2
 B_LAYOUT_KN, B_LAYOUT_NK = 0, 1
@@ -108,6 +109,9 @@ SIGNATURES = {
     "b200moe_batched_moe_align_block_size": (c_int, [c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                      c_void_p, c_void_p]),
     "b200moe_reorder_mxfp_scales": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p,
+                                            c_void_p]),
+    "b200moe_ep_barrier": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
+    "b200moe_ep_barrier_emulated": (c_int, [c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_int64,
                                             c_void_p]),
     "b200moe_ep_put_counts": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "b200moe_ep_offsets": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,

@@ -152,8 +152,10 @@ class PeerExpertParallel:
     The receiving side runs no permutation: senders place rows where the grouped GEMM wants
     them.  Receive and output buffers are sized for the worst case (every routed row of
     every rank lands here); unused rows cost nothing in the GEMMs, whose row counts live on
-    the device.  The three barriers are device-side (symmetric-memory signal pads),
-    stream-ordered, about 7 us each on NVSwitch; there is no host synchronisation.
+    the device.  The three barriers are this library's own kernel (b200moe_ep_barrier: epoch
+    flags stored into the peers' memory, a bounded poll of local memory), stream-ordered;
+    there is no host synchronisation, and a peer that never arrives costs one time budget and
+    leaves B200MOE_TIMEOUT in the device status word instead of hanging the GPU.
     """
 
     def __init__(self, group, moe, tokens_per_rank: int, topk: int, hidden: int, row_bytes: int,
@@ -176,6 +178,7 @@ class PeerExpertParallel:
         self.R, self.cap = R, G * R
         self.ret_row_bytes = hidden * torch.empty((), dtype=out_dtype).element_size()
         off = 0
+        self.off_flags = off; off = _align(off + self.capi.EP_BARRIER_CHANNELS * 16 * 4)
         self.off_counts = off; off = _align(off + G * self.E * 4)
         self.off_rows = off; off = _align(off + self.cap * row_bytes)
         self.off_scales = off; off = _align(off + self.cap * max(scale_row_bytes, 4))
@@ -217,7 +220,17 @@ class PeerExpertParallel:
         self.rows_per_expert = torch.zeros(experts_per_rank, **i32)
         self.recv_total = torch.zeros(1, **i32)
         self._ws = None
-        self.hdl.barrier(channel=0)
+        self.epochs = torch.zeros(self.capi.EP_BARRIER_CHANNELS, **i32)
+        # the flag words must be zero on every rank before anyone's first barrier writes one:
+        # once, at construction, through the host
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def barrier(self, channel: int, budget_ns: int = 0):
+        """Cross-rank barrier on the current stream (see b200moe_ep_barrier)."""
+        self._check(self.lib.b200moe_ep_barrier(
+            self.peer_bases, self.off_flags, self.rank, self.G, channel, self.epochs.data_ptr(),
+            budget_ns, torch.cuda.current_stream().cuda_stream), "ep_barrier")
 
     def _check(self, rc, what):
         if rc != 0:
@@ -260,7 +273,7 @@ class PeerExpertParallel:
         with stage("ep_counts"):
             self._check(lib.b200moe_ep_put_counts(send_counts.data_ptr(), self.E, self.peer_bases,
                                                   self.off_counts, me, G, st), "ep_put_counts")
-            self.hdl.barrier(channel=0)
+            self.barrier(0)
             self._check(lib.b200moe_ep_offsets(self.counts.data_ptr(), me, G, self.E_loc,
                                                self.my_prefix.data_ptr(), self.dst_start.data_ptr(),
                                                self.rows_per_expert.data_ptr(),
@@ -271,7 +284,7 @@ class PeerExpertParallel:
                 self.scale_row_bytes, topk_ids.data_ptr(), ids_code, row_map.data_ptr(), T, k, me, G,
                 self.E_loc, self.my_prefix.data_ptr(), self.dst_start.data_ptr(), self.peer_bases,
                 self.off_rows, self.off_scales, self.off_meta, self.cap, st), "ep_dispatch")
-            self.hdl.barrier(channel=1)
+            self.barrier(1)
         rows = self.recv_rows.view(hidden.dtype).view(self.cap, -1)
         rscales = self.recv_scales.view(scales.dtype).view(self.cap, -1) if scales is not None else None
         if self.combine == "push":
@@ -281,7 +294,7 @@ class PeerExpertParallel:
                     self.ret_row_bytes, self.dst_addr.data_ptr(), st), "ep_return_table")
             self.moe.run_experts(rows, rscales, self.rows_per_expert, self.out_dtype, self.dst_addr)
             with stage("ep_combine"):
-                self.hdl.barrier(channel=2)
+                self.barrier(2)
                 torch.ops._moe_C.moe_gather(output, self.ret, topk_weights, row_map, 0)
             return output
         with stage("ep_table"):
@@ -291,7 +304,7 @@ class PeerExpertParallel:
                 self.src_addr.data_ptr(), st), "ep_source_table")
         self.moe.run_experts(rows, rscales, self.rows_per_expert, self.out_dtype, None, self.out_rows)
         with stage("ep_combine"):
-            self.hdl.barrier(channel=2)
+            self.barrier(2)
             self._check(lib.b200moe_ep_gather(
                 output.data_ptr(), _FLOAT_CODES[output.dtype], topk_weights.data_ptr(),
                 row_map.data_ptr(), self.src_addr.data_ptr(), T, k, self.H, st), "ep_gather")
