@@ -37,9 +37,10 @@ sys.path.insert(0, os.path.join(ROOT, "vllm-xpu-kernels_b200"))
 import torch  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one w13 GEMM launch: measured with ncu on
-# a slice of the experts and scaled by the expert count (traffic grows with the experts
-# touched; every expert's weights are streamed once).
-TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 269.44e6}
+# a slice of the configuration (c1: 2 of 8 experts; c3: 1/8 of the experts and of the tokens)
+# and scaled by that factor -- traffic grows with the experts touched, every expert's
+# weights are streamed once, and rows per expert are the same in the slice.
+TRAFFIC_BYTES_PER_LAUNCH = {"c1": 4 * 269.44e6, "c3": 8 * 1549.5e6}
 
 # The benchmark configurations (shapes of the four layer configurations; the fifth, the
 # decode sweep, is c3 with few tokens and skewed routing).
@@ -216,15 +217,16 @@ class Layer:
         self.ep = None
         self.ep_backend = None
         if group is not None:
-            from vllm_xpu_kernels.ep import ExpertParallel, PeerExpertParallel, make_local_fn
-            self.ep_backend = os.environ.get("B200MOE_EP", "peer")
-            if self.ep_backend == "peer":
+            from vllm_xpu_kernels.ep import (ExpertParallel, PeerExpertParallel, TokenExpertParallel,
+                                             make_local_fn)
+            self.ep_backend = os.environ.get("B200MOE_EP", "token")
+            if self.ep_backend in ("peer", "token"):
                 fp8 = cfg["recipe"] == "fp8block"
                 mx = cfg["recipe"] == "mxfp4"
                 row_bytes = cfg["H"] * (1 if (fp8 or mx) else 2)
                 scale_bytes = (cfg["H"] // 128) * 4 if fp8 else ((cfg["H"] + 511) // 512 * 16 if mx else 0)
-                self.ep = PeerExpertParallel(group, self.moe, T, cfg["k"], cfg["H"], row_bytes,
-                                             scale_bytes, E_loc, dev)
+                cls = TokenExpertParallel if self.ep_backend == "token" else PeerExpertParallel
+                self.ep = cls(group, self.moe, T, cfg["k"], cfg["H"], row_bytes, scale_bytes, E_loc, dev)
             else:
                 self.ep = ExpertParallel(group, E_loc, make_local_fn(self.moe))
         k = cfg["k"]
@@ -367,8 +369,12 @@ def run_reference(args, cfg):
 
 def workload_config(args, cfg):
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    how = ("NCCL all-to-all dispatch/combine" if os.environ.get("B200MOE_EP", "peer") == "nccl" else
-           "dispatch and combine move rows through peer GPU memory from the library's own kernels")
+    how = {"nccl": "NCCL all-to-all dispatch/combine",
+           "peer": "dispatch and combine move one row per (token, expert) through peer GPU memory from "
+                   "the library's own kernels",
+           "token": "dispatch and combine move one row per (token, rank) through peer GPU memory from "
+                    "the library's own kernels; each rank runs its local layer on the tokens it got and "
+                    "returns one partial sum per token"}[os.environ.get("B200MOE_EP", "token")]
     par = "1 GPU" if world == 1 else (f"expert-parallel over {world} GPUs ({cfg['E'] // world} experts each), "
                                       f"tokens data-parallel, {how}")
     return {"workload": f"{cfg.get('key', args.config)}: {cfg['name']}", "parallelism": par,
@@ -511,7 +517,11 @@ def measure(cfg, dev, rank, world, group, steps, warmup, timer, with_e2e=True, c
     gemm1_ev = []
     layer.moe.stage_timer, layer.moe.stage_only = gemm1_ev, {"gemm1"}
     launches0 = lib.b200moe_launch_count()
+    # cudaProfilerStart/Stop around the timed region: a profiler run with
+    # --profile-from-start off lists exactly these launches (a no-op otherwise)
+    torch.cuda.profiler.start()
     res["ms"] = timer.region(lambda: layer.step(x, logits), steps)
+    torch.cuda.profiler.stop()
     res["launches"] = int(lib.b200moe_launch_count() - launches0)
     layer.moe.stage_timer, layer.moe.stage_only = None, None
     gemm1 = [s.elapsed_time(e) for name, s, e in gemm1_ev if name == "gemm1"]
@@ -625,6 +635,20 @@ def decode_sweep(cfg3, weights, dev, timer, peaks, steps=10):
         for name, s, e in ev:
             st.setdefault(name, []).append(s.elapsed_time(e))
         st = {k: sum(v) / len(v) for k, v in st.items()}
+        # the same step captured once into a CUDA graph and replayed: what a serving loop pays
+        # when the launches of the step are not issued one by one from the host
+        graph_ms = None
+        try:
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                layer.step(x, logits)
+            for _ in range(2):
+                graph.replay()
+            graph_ms = timer.region(graph.replay, steps)
+            del graph
+        except Exception as exc:  # reported, not hidden: the eager figure stands on its own
+            graph_ms = f"capture failed: {type(exc).__name__}: {exc}"[:200]
         _, ids = layer.route(logits)
         active = int(torch.unique(ids).numel())
         R, H, I = T * c["k"], c["H"], c["I"]
@@ -633,6 +657,9 @@ def decode_sweep(cfg3, weights, dev, timer, peaks, steps=10):
         layer_bytes = w13_bytes + w2_bytes + T * H * 3
         out[str(T)] = {
             "ms_per_step": ms, "tokens_per_s": T / (ms * 1e-3), "active_experts": active,
+            "ms_per_step_cuda_graph": graph_ms,
+            "layer_gbs_cuda_graph": (layer_bytes / (graph_ms * 1e-3) / 1e9
+                                     if isinstance(graph_ms, float) else None),
             "layer_gbs": layer_bytes / (ms * 1e-3) / 1e9,
             "layer_frac_of_measured_copy": layer_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
             "w13_ms": st.get("gemm1"), "w13_gbs": w13_bytes / (st["gemm1"] * 1e-3) / 1e9 if st.get("gemm1") else None,

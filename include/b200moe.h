@@ -212,6 +212,15 @@ int b200moe_moe_gather_add(void* out, const void* y, int dtype, const float* wei
                            const int32_t* row_map, const void* addend, int T, int k,
                            int H, void* stream);
 
+/* moe_gather over a token buffer sized for the worst case: only the first
+ * *num_valid_tokens (i32 on the device) rows of `out` are computed and written;
+ * the rest of `out` is left as it was.  Used on the receiving side of the
+ * expert-parallel token exchange, where the number of tokens that arrived is
+ * known on the device only. */
+int b200moe_moe_gather_bounded(void* out, const void* y, int dtype, const float* weights,
+                               const int32_t* row_map, const int32_t* num_valid_tokens,
+                               int T, int k, int H, void* stream);
+
 /* moe_sum (csrc/moe/torch_bindings.cpp:7-10, csrc/moe/moe_align_sum_kernels.cpp:1224-1372).
  * out[t,:] = sum_j in[t,j,:]; with topk_ids, slots with id < 0 or
  * expert_map[id] < 0 are skipped. */
@@ -455,6 +464,31 @@ int b200moe_ep_barrier(const int64_t* peer_bases_host, int64_t flags_offset,
 int b200moe_ep_barrier_emulated(uint32_t* flags, uint32_t* epochs, int world,
                                 int channel, uint32_t absent_mask, int64_t budget_ns,
                                 void* stream);
+
+/* Token-level exchange (a token crosses to a rank ONCE, however many of its
+ * experts live there; the receiving rank runs its local layer on the tokens it
+ * got and returns one partial sum per token).  It reuses the entry points below
+ * with experts_per_rank = 1 and top-k = world on the matrix this one builds:
+ * hits i32 [num_tokens, world], hits[t,r] = r if any expert of token t lives on
+ * rank r (ids in [r*experts_per_rank, (r+1)*experts_per_rank)), else -1. */
+int b200moe_ep_rank_hits(const void* topk_ids, int ids_dtype, int num_tokens, int topk,
+                         int experts_per_rank, int world, int32_t* hits, void* stream);
+
+/* What travels with a token: side i32 [num_tokens, side_stride] = its expert ids
+ * as i32, then its routing weights (f32 bits); side_stride >= 2*topk words (rounded
+ * up to a multiple of 4 so that the row is a whole number of 16-byte pieces). */
+int b200moe_ep_pack_routing(const void* topk_ids, int ids_dtype, const float* topk_weights,
+                            int num_tokens, int topk, int side_stride, int32_t* side,
+                            void* stream);
+
+/* On the receiving rank: for the recv_total[0] (device) tokens that arrived,
+ * ids_local i32 [capacity_tokens, topk] = local expert id, or -1 where the expert
+ * lives on another rank, and weights f32 (0 there); rows past recv_total get -1,
+ * so stale rows of the worst-case buffer are never routed. */
+int b200moe_ep_unpack_routing(const int32_t* side, const int32_t* recv_total,
+                              int64_t capacity_tokens, int topk, int side_stride, int my_rank,
+                              int experts_per_rank, int32_t* ids_local, float* weights,
+                              void* stream);
 
 /* Writes my rows-per-global-expert (i32 [num_counts], num_counts = world *
  * experts_per_rank) into row `my_rank` of every rank's i32 [world, num_counts]

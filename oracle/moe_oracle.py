@@ -209,14 +209,21 @@ def moe_align_block_size(topk_ids, block_size, num_experts, expert_map=None,
     run padded to ``block_size`` with the sentinel ``numel``
     (tests/test_moe_align_block_size.py:97-183).  ``expert_ids`` holds one
     (local) expert per block, 0 in the unused tail.  Experts mapped to -1 are
-    dropped; ids >= num_experts are ignored."""
+    dropped; ids >= num_experts are ignored.  With an ``expert_map`` the runs are
+    keyed and ordered by the MAPPED id, which is what the reference kernel does
+    (csrc/moe/moe_align_sum_kernels.cpp:196-205: ``expert_id =
+    expert_map[expert_id]`` before counting).  The reference's torch golden walks
+    the global ids instead (tests/test_moe_align_block_size.py:156-176); the two
+    agree for every map whose kept entries are increasing - all its tests use -
+    and differ only for a permuted map, where this follows the kernel."""
     numel = topk_ids.numel()
     max_padded, max_blocks = align_sizes(numel, num_experts, block_size, pad_sorted_ids)
     flat = topk_ids.flatten().to(torch.int64)
     valid = (flat >= 0) & (flat < num_experts)
     if expert_map is not None:
         mapped = expert_map.to(torch.int64)[flat.clamp(0, num_experts - 1)]
-        valid &= mapped >= 0
+        valid &= (mapped >= 0) & (mapped < num_experts)
+        flat = torch.where(valid, mapped, flat)     # the key is the mapped id
     counts = torch.bincount(flat[valid], minlength=num_experts)
     padded = (counts + block_size - 1) // block_size * block_size
     starts = torch.cumsum(padded, 0) - padded
@@ -230,8 +237,6 @@ def moe_align_block_size(topk_ids, block_size, num_experts, expert_map=None,
     sorted_ids[(starts[e_sorted] + rank)] = order.to(torch.int32)
     blocks = padded // block_size
     owner = torch.repeat_interleave(torch.arange(num_experts), blocks)
-    if expert_map is not None:
-        owner = expert_map.to(torch.int64)[owner]
     expert_ids[: owner.numel()] = owner.to(torch.int32)
     total = torch.tensor([int(padded.sum())], dtype=torch.int32)
     return sorted_ids, expert_ids, total

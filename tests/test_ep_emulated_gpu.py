@@ -225,3 +225,64 @@ def test_barrier_argument_checks(ops):
     st = torch.cuda.current_stream().cuda_stream
     assert lib.b200moe_ep_barrier(bases, 0, 2, 2, 0, epochs.data_ptr(), 0, st) == capi.INVALID_ARG
     assert lib.b200moe_ep_barrier(bases, 0, 0, 2, 0, None, 0, st) == capi.INVALID_ARG
+
+
+# ---- the token-level exchange's own three kernels ---------------------------------------------
+@pytest.mark.parametrize("T,k,E_loc,G,idt", [(37, 3, 4, 4, torch.int32), (200, 8, 32, 8, torch.int64),
+                                             (5, 2, 8, 1, torch.int32)])
+def test_token_exchange_helpers(ops, T, k, E_loc, G, idt):
+    from vllm_xpu_kernels import capi
+    lib = capi.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator().manual_seed(T)
+    E = E_loc * G
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(idt)
+    ids[torch.rand(T, k, generator=g) < 0.1] = -1
+    w = torch.rand(T, k, generator=g)
+    code = I32 if idt == torch.int32 else I64
+    d_ids, d_w = ids.to(DEV), w.to(DEV)
+    # which ranks a token hits
+    hits = torch.full((T, G), 77, dtype=torch.int32, device=DEV)
+    assert lib.b200moe_ep_rank_hits(d_ids.data_ptr(), code, T, k, E_loc, G, hits.data_ptr(), st) == capi.OK
+    want = torch.full((T, G), -1, dtype=torch.int32)
+    for t in range(T):
+        for e in ids[t].tolist():
+            if e >= 0:
+                want[t, e // E_loc] = e // E_loc
+    assert torch.equal(hits.cpu(), want)
+    # routing data out and back in: rank 1 (or 0) sees local ids of its own experts only
+    sw = (2 * k + 3) // 4 * 4
+    side = torch.zeros(T, sw, dtype=torch.int32, device=DEV)
+    assert lib.b200moe_ep_pack_routing(d_ids.data_ptr(), code, d_w.data_ptr(), T, k, sw, side.data_ptr(),
+                                       st) == capi.OK
+    assert torch.equal(side[:, :k].cpu(), ids.to(torch.int32))
+    assert torch.equal(side[:, k:2 * k].view(torch.float32).cpu(), w)
+    me, cap, n_in = G - 1, T + 9, T - 2
+    buf = torch.full((cap, sw), 3, dtype=torch.int32, device=DEV)      # stale rows route to expert 3
+    buf[:T] = side
+    total = torch.tensor([n_in], dtype=torch.int32, device=DEV)
+    ids_local = torch.empty(cap, k, dtype=torch.int32, device=DEV)
+    w_local = torch.empty(cap, k, dtype=torch.float32, device=DEV)
+    assert lib.b200moe_ep_unpack_routing(buf.data_ptr(), total.data_ptr(), cap, k, sw, me, E_loc,
+                                         ids_local.data_ptr(), w_local.data_ptr(), st) == capi.OK
+    loc = ids.to(torch.int32) - me * E_loc
+    ok = (loc >= 0) & (loc < E_loc)
+    ok[n_in:] = False
+    want_ids = torch.full((cap, k), -1, dtype=torch.int32)
+    want_ids[:T][ok] = loc[ok]
+    want_w = torch.zeros(cap, k)
+    want_w[:T][ok] = w[ok]
+    assert torch.equal(ids_local.cpu(), want_ids) and torch.equal(w_local.cpu(), want_w)
+
+
+def test_bounded_gather_leaves_rows_past_the_count_alone(ops):
+    T, k, H = 40, 3, 256
+    g = torch.Generator().manual_seed(0)
+    y = torch.randn(T * k, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.rand(T, k, generator=g).to(DEV)
+    rm = torch.randperm(T * k, generator=g).to(torch.int32).view(T, k).to(DEV)
+    out = torch.full((T, H), 5.0, dtype=torch.bfloat16, device=DEV)
+    ref = torch.empty_like(out)
+    ops._moe_C.moe_gather(ref, y, w, rm, 1)
+    ops._moe_C.b200_moe_gather_bounded(out, y, w, rm, torch.tensor([25], dtype=torch.int32, device=DEV))
+    assert torch.equal(out[:25], ref[:25]) and (out[25:] == 5.0).all()

@@ -62,6 +62,16 @@ def test_align_documented_example():
     assert e[:4].tolist() == [0, 1, 2, 3] and n.item() == 16
 
 
+def test_align_with_a_permuted_expert_map_follows_the_reference_kernel():
+    # expert_id = expert_map[expert_id] happens BEFORE counting in the reference kernel
+    # (csrc/moe/moe_align_sum_kernels.cpp:196-205): runs are ordered by the mapped id.
+    ids = torch.tensor([[0, 1], [2, 3], [0, 3]], dtype=torch.int32)
+    emap = torch.tensor([2, -1, 0, 1], dtype=torch.int32)
+    s, e, n = O.moe_align_block_size(ids, 2, 4, expert_map=emap)
+    # key 0 <- id 2 (flat 2); key 1 <- id 3 (flat 3, 5); key 2 <- id 0 (flat 0, 4); id 1 dropped
+    assert s[:6].tolist() == [2, 6, 3, 5, 0, 4] and e[:3].tolist() == [0, 1, 2] and n.item() == 6
+
+
 @pytest.mark.parametrize("name", _names("remap_"))
 def test_remap_and_gather_match_reference(name):
     g = load_golden(name)

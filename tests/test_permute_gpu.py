@@ -51,6 +51,19 @@ def test_align_vs_oracle(ops, T, k, E, bs, dtype):
     assert torch.equal(s, s2)
 
 
+@pytest.mark.parametrize("T,k,E,bs", [(3, 2, 4, 2), (500, 4, 32, 16), (5000, 8, 256, 128)])
+def test_align_with_a_permuted_expert_map(ops, T, k, E, bs):
+    """A map that is not monotone reorders the runs: they follow the mapped id, as in the
+    reference kernel (csrc/moe/moe_align_sum_kernels.cpp:196-205)."""
+    g = torch.Generator().manual_seed(E)
+    ids = torch.randint(0, E, (T, k), generator=g).to(torch.int32)
+    emap = torch.randperm(E, generator=g).to(torch.int32)
+    emap[torch.rand(E, generator=g) < 0.3] = -1
+    rs, re, rt = O.moe_align_block_size(ids, bs, E, expert_map=emap)
+    s, e, t = run_align(ops, ids, bs, E, emap)
+    assert torch.equal(t, rt) and torch.equal(e, re) and torch.equal(s, rs)
+
+
 def test_align_skewed_and_out_of_range(ops):
     ids = torch.zeros(5000, 4, dtype=torch.int32)       # every token on expert 0
     ids[::7, 1] = 99                                     # ids >= num_experts are ignored

@@ -14,9 +14,11 @@ constexpr int kMaxTopK = 64;
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gather_kernel(
     T* __restrict__ out, const T* __restrict__ y, const float* __restrict__ weights,
-    const int32_t* __restrict__ row_map, const T* __restrict__ addend, int k, int H) {
+    const int32_t* __restrict__ row_map, const T* __restrict__ addend,
+    const int32_t* __restrict__ num_valid, int k, int H) {
   constexpr int V = 16 / sizeof(T);
   const int64_t t = blockIdx.x;
+  if (num_valid && t >= *num_valid) return;  // rows of a worst-case buffer nobody will read
   __shared__ int rows[kMaxTopK];
   __shared__ float w[kMaxTopK];
   for (int j = threadIdx.x; j < k; j += blockDim.x) {
@@ -81,7 +83,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(
 using namespace b200moe;
 
 static int gather_impl(void* out, const void* y, int dtype, const float* weights,
-                       const int32_t* row_map, const void* addend, int T, int k, int H, void* stream) {
+                       const int32_t* row_map, const void* addend, const int32_t* num_valid, int T,
+                       int k, int H, void* stream) {
   if (T < 0 || k <= 0 || k > kMaxTopK || H <= 0) return B200MOE_INVALID_ARG;
   if (T == 0) return B200MOE_OK;
   if (!out || !y || !weights || !row_map) return B200MOE_INVALID_ARG;
@@ -92,21 +95,28 @@ static int gather_impl(void* out, const void* y, int dtype, const float* weights
     threads = threads > 256 ? 256 : threads;
     moe_gather_kernel<scalar_t><<<T, threads, 0, as_stream(stream)>>>(
         reinterpret_cast<scalar_t*>(out), reinterpret_cast<const scalar_t*>(y), weights, row_map,
-        reinterpret_cast<const scalar_t*>(addend), k, H);
+        reinterpret_cast<const scalar_t*>(addend), num_valid, k, H);
     return launch_status("moe_gather_kernel");
   });
 }
 
 extern "C" int b200moe_moe_gather(void* out, const void* y, int dtype, const float* weights,
                                   const int32_t* row_map, int T, int k, int H, void* stream) {
-  return gather_impl(out, y, dtype, weights, row_map, nullptr, T, k, H, stream);
+  return gather_impl(out, y, dtype, weights, row_map, nullptr, nullptr, T, k, H, stream);
 }
 
 extern "C" int b200moe_moe_gather_add(void* out, const void* y, int dtype, const float* weights,
                                       const int32_t* row_map, const void* addend, int T, int k,
                                       int H, void* stream) {
   if (!addend) return B200MOE_INVALID_ARG;
-  return gather_impl(out, y, dtype, weights, row_map, addend, T, k, H, stream);
+  return gather_impl(out, y, dtype, weights, row_map, addend, nullptr, T, k, H, stream);
+}
+
+extern "C" int b200moe_moe_gather_bounded(void* out, const void* y, int dtype, const float* weights,
+                                          const int32_t* row_map, const int32_t* num_valid_tokens,
+                                          int T, int k, int H, void* stream) {
+  if (!num_valid_tokens) return B200MOE_INVALID_ARG;
+  return gather_impl(out, y, dtype, weights, row_map, nullptr, num_valid_tokens, T, k, H, stream);
 }
 
 extern "C" int b200moe_moe_sum(const void* in, void* out, int dtype, int T, int k, int H,

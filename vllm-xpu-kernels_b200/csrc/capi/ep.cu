@@ -450,6 +450,62 @@ __global__ void __launch_bounds__(32) ep_barrier_emulated_kernel(uint32_t* flags
   ep_barrier_body(peers, 0, me, G, channel, epochs + me * kBarrierChannels, budget_ns, status);
 }
 
+// ---- token-level exchange: a token crosses to a rank once, however many of its experts
+// live there -----------------------------------------------------------------------------
+// hits[t, r] = r if any of token t's expert ids lives on rank r, else -1: the "ids" matrix
+// that turns the row-grouping and dispatch kernels above into a token-to-rank exchange
+// (experts_per_rank = 1, top-k = world).
+__global__ void ep_rank_hits_kernel(const void* __restrict__ ids, int ids_dtype, int T, int k,
+                                    int E_loc, int G, int32_t* __restrict__ hits) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  uint32_t mask = 0;
+  for (int j = 0; j < k; ++j) {
+    const int64_t e = load_index(ids, ids_dtype, static_cast<int64_t>(t) * k + j);
+    if (e >= 0 && e < static_cast<int64_t>(E_loc) * G) mask |= 1u << static_cast<int>(e / E_loc);
+  }
+  for (int r = 0; r < G; ++r) hits[static_cast<int64_t>(t) * G + r] = (mask >> r) & 1u ? r : -1;
+}
+
+// side[t] = (k expert ids as i32 | k routing weights as f32 | padding to `stride` words):
+// what travels with a token.
+__global__ void ep_pack_routing_kernel(const void* __restrict__ ids, int ids_dtype,
+                                       const float* __restrict__ weights, int64_t n, int k,
+                                       int stride, int32_t* __restrict__ side) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const int64_t t = i / k;
+  const int j = static_cast<int>(i - t * k);
+  side[t * stride + j] = static_cast<int32_t>(load_index(ids, ids_dtype, i));
+  side[t * stride + k + j] = __float_as_int(weights[i]);
+}
+
+// The receiving side of the same: for the *recv_total tokens that arrived, ids become LOCAL
+// expert ids (or -1 where the expert lives elsewhere) and the weights are copied; every
+// later row of the worst-case buffer gets -1, so whatever an earlier call left there is
+// never routed.
+__global__ void ep_unpack_routing_kernel(const int32_t* __restrict__ side,
+                                         const int32_t* __restrict__ recv_total, int64_t n, int k,
+                                         int stride, int me, int E_loc,
+                                         int32_t* __restrict__ ids_local,
+                                         float* __restrict__ weights) {
+  const int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+  if (i >= n) return;
+  const int64_t t = i / k;
+  const int j = static_cast<int>(i - t * k);
+  int32_t id = -1;
+  float w = 0.f;
+  if (t < recv_total[0]) {
+    const int32_t local = side[t * stride + j] - me * E_loc;
+    if (local >= 0 && local < E_loc) {
+      id = local;
+      w = __int_as_float(side[t * stride + k + j]);
+    }
+  }
+  ids_local[i] = id;
+  weights[i] = w;
+}
+
 long long barrier_budget_ns(int64_t budget_ns) {
   if (budget_ns > 0) return budget_ns;
   // read per call: a host may shorten it for a drill without restarting
@@ -502,6 +558,44 @@ extern "C" int b200moe_ep_barrier_emulated(uint32_t* flags, uint32_t* epochs, in
   }
   count_launch();
   return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_rank_hits(const void* topk_ids, int ids_dtype, int num_tokens, int topk,
+                                    int experts_per_rank, int world, int32_t* hits, void* stream) {
+  if (!topk_ids || !hits || !is_index_dtype(ids_dtype) || num_tokens < 0 || topk <= 0 ||
+      experts_per_rank <= 0 || world <= 0 || world > kMaxRanks)
+    return B200MOE_INVALID_ARG;
+  if (num_tokens == 0) return B200MOE_OK;
+  ep_rank_hits_kernel<<<(num_tokens + 255) / 256, 256, 0, as_stream(stream)>>>(
+      topk_ids, ids_dtype, num_tokens, topk, experts_per_rank, world, hits);
+  return launch_status("ep_rank_hits_kernel");
+}
+
+extern "C" int b200moe_ep_pack_routing(const void* topk_ids, int ids_dtype, const float* topk_weights,
+                                       int num_tokens, int topk, int side_stride, int32_t* side,
+                                       void* stream) {
+  if (!topk_ids || !topk_weights || !side || !is_index_dtype(ids_dtype) || num_tokens < 0 || topk <= 0 ||
+      side_stride < 2 * topk)
+    return B200MOE_INVALID_ARG;
+  if (num_tokens == 0) return B200MOE_OK;
+  const int64_t n = static_cast<int64_t>(num_tokens) * topk;
+  ep_pack_routing_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+      topk_ids, ids_dtype, topk_weights, n, topk, side_stride, side);
+  return launch_status("ep_pack_routing_kernel");
+}
+
+extern "C" int b200moe_ep_unpack_routing(const int32_t* side, const int32_t* recv_total,
+                                         int64_t capacity_tokens, int topk, int side_stride,
+                                         int my_rank, int experts_per_rank, int32_t* ids_local,
+                                         float* weights, void* stream) {
+  if (!side || !recv_total || !ids_local || !weights || capacity_tokens < 0 || topk <= 0 ||
+      side_stride < 2 * topk || my_rank < 0 || experts_per_rank <= 0)
+    return B200MOE_INVALID_ARG;
+  if (capacity_tokens == 0) return B200MOE_OK;
+  const int64_t n = capacity_tokens * topk;
+  ep_unpack_routing_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+      side, recv_total, n, topk, side_stride, my_rank, experts_per_rank, ids_local, weights);
+  return launch_status("ep_unpack_routing_kernel");
 }
 
 extern "C" int b200moe_ep_put_counts(const int32_t* send_counts, int num_counts,

@@ -49,7 +49,8 @@ __device__ __forceinline__ int key_of(const GroupParams& p, int64_t i) {
   if (p.map) {
     const int m = p.map[id];
     if (m < 0) return -1;
-    return p.map_is_filter ? static_cast<int>(id) : m;
+    if (p.map_is_filter) return static_cast<int>(id);
+    return m < p.num_keys ? m : -1;  // a map value outside the key space is dropped, not binned
   }
   return static_cast<int>(id);
 }
@@ -423,9 +424,13 @@ extern "C" int b200moe_moe_align_block_size(const void* topk_ids, int ids_dtype,
       !sorted_token_ids || !expert_ids || !num_tokens_post_pad || (numel > 0 && !topk_ids))
     return B200MOE_INVALID_ARG;
   if (numel >= (1ll << 31)) return B200MOE_UNSUPPORTED;
-  GroupParams p{topk_ids, ids_dtype, numel, num_experts, num_experts, expert_map, 1, block_size};
+  // With an expert map the runs are keyed and ordered by the MAPPED (local) id, as the
+  // reference kernel does (expert_id = expert_map[expert_id] before counting,
+  // csrc/moe/moe_align_sum_kernels.cpp:201-205), so a map that is not monotone reorders the
+  // runs; expert_ids then holds the keys themselves.
+  GroupParams p{topk_ids, ids_dtype, numel, num_experts, num_experts, expert_map, 0, block_size};
   AlignOut ao{sorted_token_ids, sorted_capacity, expert_ids, blocks_capacity, num_tokens_post_pad,
-              expert_map};
+              nullptr};
   return run_grouping(p, ao, nullptr, nullptr, workspace, workspace_bytes, as_stream(stream));
 }
 

@@ -361,6 +361,24 @@ void b200_moe_gather_add(Tensor& output, const Tensor& moe_output, const Tensor&
         "b200_moe_gather_add");
 }
 
+void b200_moe_gather_bounded(Tensor& output, const Tensor& moe_output, const Tensor& topk_weights,
+                             const Tensor& row_map, const Tensor& valid_tokens) {
+  const char* op = "b200_moe_gather_bounded";
+  TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, op, ": topk_weights must be float32");
+  TORCH_CHECK(output.scalar_type() == moe_output.scalar_type(), op, ": dtype mismatch");
+  TORCH_CHECK(output.is_contiguous() && moe_output.is_contiguous() && topk_weights.is_contiguous() &&
+                  row_map.is_contiguous(), op, ": tensors must be contiguous");
+  TORCH_CHECK(row_map.scalar_type() == at::kInt && valid_tokens.scalar_type() == at::kInt &&
+                  valid_tokens.numel() >= 1 && valid_tokens.is_cuda(),
+              op, ": row map and the valid-token count must be int32 on the device");
+  const int64_t T = output.size(0), H = output.size(1), k = topk_weights.size(1);
+  c10::cuda::CUDAGuard guard(output.device());
+  check(b200moe_moe_gather_bounded(output.data_ptr(), moe_output.data_ptr(), float_code(output, op),
+                                   topk_weights.data_ptr<float>(), row_map.data_ptr<int>(),
+                                   valid_tokens.data_ptr<int>(), T, k, H, cur_stream()),
+        op);
+}
+
 void moe_gather(Tensor& output, const Tensor& moe_output, const Tensor& topk_weights,
                 const Tensor& unpermuted_row_to_permuted_row, int64_t /*num_experts*/) {
   TORCH_CHECK(topk_weights.scalar_type() == at::kFloat, "moe_gather: topk_weights must be float32");
@@ -904,6 +922,9 @@ TORCH_LIBRARY(B200MOE_NS_MOE_C, m) {
   m.def(
       "b200_moe_gather_add(Tensor! output, Tensor moe_output, Tensor topk_weights, Tensor row_map, "
       "Tensor addend) -> ()");
+  m.def(
+      "b200_moe_gather_bounded(Tensor! output, Tensor moe_output, Tensor topk_weights, Tensor row_map, "
+      "Tensor valid_tokens) -> ()");
   m.def("init_expert_map(Tensor expert_map, int num_experts, int ep_rank, int ep_size) -> ()");
   m.def(
       "moe_lora_align_block_size(Tensor topk_ids, Tensor token_lora_mapping, int num_experts, int "
@@ -935,6 +956,7 @@ TORCH_LIBRARY_IMPL(B200MOE_NS_MOE_C, CUDA, m) {
   m.impl("topk_sigmoid", &topk_sigmoid);
   m.impl("moe_gather", &moe_gather);
   m.impl("b200_moe_gather_add", &b200_moe_gather_add);
+  m.impl("b200_moe_gather_bounded", &b200_moe_gather_bounded);
   m.impl("init_expert_map", &init_expert_map);
   m.impl("batched_moe_align_block_size", &batched_moe_align_block_size);
   m.impl("moe_lora_align_block_size", &moe_lora_align_block_size);

@@ -113,6 +113,13 @@ SIGNATURES = {
     "b200moe_ep_barrier": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_int64, c_void_p]),
     "b200moe_ep_barrier_emulated": (c_int, [c_void_p, c_void_p, c_int, c_int, ctypes.c_uint32, c_int64,
                                             c_void_p]),
+    "b200moe_ep_rank_hits": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "b200moe_ep_pack_routing": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+                                        c_void_p]),
+    "b200moe_ep_unpack_routing": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                                          c_void_p, c_void_p, c_void_p]),
+    "b200moe_moe_gather_bounded": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_int, c_int, c_int, c_void_p]),
     "b200moe_ep_put_counts": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "b200moe_ep_offsets": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p]),

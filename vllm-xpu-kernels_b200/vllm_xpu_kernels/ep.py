@@ -309,3 +309,142 @@ class PeerExpertParallel:
                 output.data_ptr(), _FLOAT_CODES[output.dtype], topk_weights.data_ptr(),
                 row_map.data_ptr(), self.src_addr.data_ptr(), T, k, self.H, st), "ep_gather")
         return output
+
+
+class TokenExpertParallel(PeerExpertParallel):
+    """The same exchange at TOKEN granularity: a token crosses to a rank once, however many
+    of its experts live there, and one partial sum per (token, rank) comes back.
+
+      which ranks does each token hit (ep_rank_hits) -> rank the (token, rank) pairs by rank
+      (remap_hidden_states, grouping only) -> put_counts -> barrier -> offsets -> dispatch each
+      token's row + scales, and its k (expert id, weight) pairs, to every rank it hits ->
+      barrier -> the receiving rank turns the ids into local ids (-1 elsewhere) and runs its
+      ordinary local layer on the tokens it got (permutation, the two grouped GEMMs, weighted
+      combine over the LOCAL experts of each token) -> barrier -> the token's owner reads one
+      partial row per rank it hit and adds them in rank order (ep_gather with weights 1).
+
+    With group-limited routing a token of the DeepSeek-V3 layer reaches at most 4 of 8 ranks
+    (2 of 2 on two GPUs) with 8 experts, so rows out and results back are 2-4x fewer than with
+    one row per (token, expert).  Every kernel is one the row-level exchange or the single-GPU
+    layer already uses; a rank is "an expert" (experts_per_rank = 1, top-k = world) for the
+    grouping, offset, dispatch, address-table and gather kernels.  The partial sums are
+    rounded to the output dtype once per rank before the final fp32 sum.
+    """
+
+    def __init__(self, group, moe, tokens_per_rank: int, topk: int, hidden: int, row_bytes: int,
+                 scale_row_bytes: int, experts_per_rank: int, device, out_dtype=torch.bfloat16):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import capi
+        self.lib, self.capi = capi.lib(), capi
+        self.group, self.moe = group, moe
+        self.G = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.T, self.k, self.H = tokens_per_rank, topk, hidden
+        self.row_bytes, self.scale_row_bytes = row_bytes, scale_row_bytes
+        self.E_loc, self.dev, self.out_dtype = experts_per_rank, device, out_dtype
+        G = self.G
+        self.E = G * experts_per_rank
+        self.cap = G * tokens_per_rank                     # tokens this rank can receive
+        self.side_w = (2 * topk + 3) // 4 * 4              # i32 words of routing data per token
+        self.ret_row_bytes = hidden * torch.empty((), dtype=out_dtype).element_size()
+        cap, off = self.cap, 0
+        self.off_flags = off; off = _align(off + capi.EP_BARRIER_CHANNELS * 16 * 4)
+        self.off_counts = off; off = _align(off + G * G * 4)
+        self.off_rows = off; off = _align(off + cap * row_bytes)
+        self.off_scales = off; off = _align(off + cap * max(scale_row_bytes, 4))
+        self.off_meta = off; off = _align(off + cap * 8)
+        self.off_side = off; off = _align(off + cap * self.side_w * 4)
+        self.off_out = off; off = _align(off + cap * self.ret_row_bytes)
+        self.buf = symm_mem.empty(off, dtype=torch.uint8, device=device)
+        self.hdl = symm_mem.rendezvous(self.buf, group.group_name)
+        self.buf.zero_()
+        self.peer_bases = (ctypes.c_int64 * G)(*[int(p) for p in self.hdl.buffer_ptrs])
+        b = self.buf
+        self.counts = b[self.off_counts: self.off_counts + G * G * 4].view(torch.int32)
+        self.recv_rows = b[self.off_rows: self.off_rows + cap * row_bytes]
+        self.recv_scales = (b[self.off_scales: self.off_scales + cap * scale_row_bytes]
+                            if scale_row_bytes else None)
+        self.recv_side = b[self.off_side: self.off_side + cap * self.side_w * 4].view(torch.int32)
+        self.partial = b[self.off_out: self.off_out + cap * self.ret_row_bytes] \
+            .view(out_dtype).view(cap, hidden)
+        i32 = dict(dtype=torch.int32, device=device)
+        self.my_prefix = torch.zeros(G + 1, **i32)
+        self.dst_start = torch.zeros(G, **i32)
+        self.tokens_in = torch.zeros(1, **i32)             # "rows per expert" of the one-expert-per-rank view
+        self.recv_total = torch.zeros(1, **i32)
+        self.src_addr = torch.zeros(tokens_per_rank * G, dtype=torch.int64, device=device)
+        self.hits = torch.empty(tokens_per_rank, G, **i32)
+        self.side = torch.zeros(tokens_per_rank, self.side_w, **i32)
+        self.ids_local = torch.empty(cap, topk, **i32)
+        self.w_local = torch.empty(cap, topk, dtype=torch.float32, device=device)
+        self.ones = torch.ones(tokens_per_rank, G, dtype=torch.float32, device=device)
+        self._ws = None
+        self.epochs = torch.zeros(capi.EP_BARRIER_CHANNELS, **i32)
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def apply(self, output, hidden, topk_weights, topk_ids, scales=None):
+        self.check_call(hidden, topk_ids, scales)
+        lib, G, me = self.lib, self.G, self.rank
+        T, k = topk_ids.shape
+        dev = hidden.device
+        st = torch.cuda.current_stream().cuda_stream
+        stage = self.moe._stage
+        ids_code, I32 = _INDEX_CODES[topk_ids.dtype], _INDEX_CODES[torch.int32]
+        send_counts = torch.zeros(G, dtype=torch.int32, device=dev)
+        row_map = torch.empty((T, G), dtype=torch.int32, device=dev)
+        hits = self.hits[:T]
+        ws_bytes = lib.b200moe_remap_hidden_states_workspace_bytes(T, G, G)
+        if self._ws is None or self._ws.numel() < ws_bytes:
+            self._ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=dev)
+        with stage("ep_group"):
+            self._check(lib.b200moe_ep_rank_hits(topk_ids.data_ptr(), ids_code, T, k, self.E_loc, G,
+                                                 hits.data_ptr(), st), "ep_rank_hits")
+            self._check(lib.b200moe_remap_hidden_states(
+                None, None, None, None, self.row_bytes, self.scale_row_bytes, hits.data_ptr(), I32,
+                None, T, G, G, G, send_counts.data_ptr(), row_map.data_ptr(), self._ws.data_ptr(),
+                self._ws.numel(), st), "remap_hidden_states")
+            self._check(lib.b200moe_ep_pack_routing(topk_ids.data_ptr(), ids_code, topk_weights.data_ptr(),
+                                                    T, k, self.side_w, self.side.data_ptr(), st),
+                        "ep_pack_routing")
+        with stage("ep_counts"):
+            self._check(lib.b200moe_ep_put_counts(send_counts.data_ptr(), G, self.peer_bases,
+                                                  self.off_counts, me, G, st), "ep_put_counts")
+            self.barrier(0)
+            self._check(lib.b200moe_ep_offsets(self.counts.data_ptr(), me, G, 1, self.my_prefix.data_ptr(),
+                                               self.dst_start.data_ptr(), self.tokens_in.data_ptr(),
+                                               self.recv_total.data_ptr(), st), "ep_offsets")
+        with stage("ep_push"):
+            self._check(lib.b200moe_ep_dispatch(
+                hidden.data_ptr(), scales.data_ptr() if scales is not None else None, self.row_bytes,
+                self.scale_row_bytes, hits.data_ptr(), I32, row_map.data_ptr(), T, G, me, G, 1,
+                self.my_prefix.data_ptr(), self.dst_start.data_ptr(), self.peer_bases, self.off_rows,
+                self.off_scales, self.off_meta, self.cap, st), "ep_dispatch")
+            self._check(lib.b200moe_ep_dispatch(
+                self.side.data_ptr(), None, self.side_w * 4, 0, hits.data_ptr(), I32, row_map.data_ptr(),
+                T, G, me, G, 1, self.my_prefix.data_ptr(), self.dst_start.data_ptr(), self.peer_bases,
+                self.off_side, 0, self.off_meta, self.cap, st), "ep_dispatch (routing data)")
+            self.barrier(1)
+        with stage("ep_table"):
+            self._check(lib.b200moe_ep_unpack_routing(
+                self.recv_side.data_ptr(), self.recv_total.data_ptr(), self.cap, k, self.side_w, me,
+                self.E_loc, self.ids_local.data_ptr(), self.w_local.data_ptr(), st), "ep_unpack_routing")
+            self._check(lib.b200moe_ep_source_table(
+                self.my_prefix.data_ptr(), self.dst_start.data_ptr(), T * G, G, 1, self.peer_bases,
+                self.off_out, self.ret_row_bytes, self.cap, self.src_addr.data_ptr(), st),
+                "ep_source_table")
+        rows = self.recv_rows.view(hidden.dtype).view(self.cap, -1)
+        rscales = self.recv_scales.view(scales.dtype).view(self.cap, -1) if scales is not None else None
+        # the ordinary local layer on the tokens that arrived; rows past recv_total carry ids of
+        # -1 and their partial rows are not written
+        self.moe.apply(self.partial, rows, self.w_local, self.ids_local, a1q_scale=rscales,
+                       valid_tokens=self.recv_total)
+        with stage("ep_combine"):
+            self.barrier(2)
+            self._check(lib.b200moe_ep_gather(
+                output.data_ptr(), _FLOAT_CODES[output.dtype], self.ones[:T].data_ptr(),
+                row_map.data_ptr(), self.src_addr.data_ptr(), T, G, self.H, st), "ep_gather")
+        return output

@@ -210,7 +210,7 @@ class XpuFusedMoe:
 
     # ------------------------------------------------------------------
     def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
-              a1q_scale=None, row_destinations=None, shared_output=None):
+              a1q_scale=None, row_destinations=None, shared_output=None, valid_tokens=None):
         """output[T, H] = sum_j w[t, j] * Expert_{ids[t, j]}(hidden_states[t]).
 
         ``hidden_states`` is bf16/fp16 ``[T, H]``, or already quantised
@@ -225,7 +225,12 @@ class XpuFusedMoe:
 
         ``shared_output`` (not in the reference signature): ``[T, H]`` rows added to the
         routed result inside the combine, weight 1 - the output of a shared expert every
-        token passes through (see ``dense``)."""
+        token passes through (see ``dense``).
+
+        ``valid_tokens`` (not in the reference signature; used by the expert-parallel token
+        exchange): int32 ``[1]`` on the device, the number of leading rows of a worst-case
+        sized ``hidden_states`` that hold tokens.  Rows past it must carry ids of -1; their
+        output rows are then not written at all."""
         num_rows, hidden_size = hidden_states.shape
         k = topk_ids.shape[1]  # n_experts_per_token, or 1 for rows that arrive already dispatched
         R = num_rows * k
@@ -235,7 +240,8 @@ class XpuFusedMoe:
         if num_rows == 0:
             return
 
-        if (self.is_block_fp8 and row_destinations is None and self._decode_regime(num_rows * k)
+        if (self.is_block_fp8 and row_destinations is None and valid_tokens is None
+                and self._decode_regime(num_rows * k)
                 and self.activation == "silu" and not (self.gemm1_clamp_limit or 0) > 0
                 and self.inter_size % 128 == 0):
             return self._apply_decode(output, hidden_states, topk_weights, topk_ids, expert_map,
@@ -273,6 +279,9 @@ class XpuFusedMoe:
             if shared_output is not None:
                 torch.ops._moe_C.b200_moe_gather_add(output, gemm2_out, topk_weights, row_map,
                                                      shared_output)
+            elif valid_tokens is not None:
+                torch.ops._moe_C.b200_moe_gather_bounded(output, gemm2_out, topk_weights, row_map,
+                                                         valid_tokens)
             else:
                 torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map,
                                             self.num_experts)
@@ -456,6 +465,9 @@ class XpuFusedMoe:
             if shared_output is not None:
                 torch.ops._moe_C.b200_moe_gather_add(output, gemm2_out, topk_weights, row_map,
                                                      shared_output)
+            elif valid_tokens is not None:
+                torch.ops._moe_C.b200_moe_gather_bounded(output, gemm2_out, topk_weights, row_map,
+                                                         valid_tokens)
             else:
                 torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
 
