@@ -528,6 +528,13 @@ def measure(cfg, dev, rank, world, group, steps, warmup, timer, with_e2e=True, c
     res["gemm1_ms"] = sum(gemm1) / max(len(gemm1), 1)
     res["out"] = layer.out.clone()
 
+    # end to end straight after the device-timed region, under the same power state
+    if with_e2e:
+        e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, 2)
+        res["ms_e2e"] = e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, steps)
+        res["h2d"] = x_pin.numel() * 2 + logits_pin.numel() * 4
+        res["d2h"] = out_pin.numel() * 2
+
     # the same steps once more with an event pair around every stage (second pass, later in
     # the run and so under a warmer power state: the stages need not add up to ms_per_step)
     stage_ev = []
@@ -549,11 +556,6 @@ def measure(cfg, dev, rank, world, group, steps, warmup, timer, with_e2e=True, c
         res["ms_shared"] = timer.region(lambda: layer.step(x, logits), max(steps // 2, 3))
         res["out_shared"] = layer.out.clone()
         layer.use_shared = False
-    if with_e2e:
-        e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, 2)
-        res["ms_e2e"] = e2e_region(layer, timer, x_pin, logits_pin, out_pin, x, logits, steps)
-        res["h2d"] = x_pin.numel() * 2 + logits_pin.numel() * 4
-        res["d2h"] = out_pin.numel() * 2
     if sampler:
         sampler.__exit__()
         res["clocks"] = sampler.summary()

@@ -337,6 +337,14 @@ typedef struct b200moe_gemm_args {
                         addresses may be peer-mapped memory of other GPUs: this
                         is how the expert-parallel combine leaves the GEMM.      */
   int a_scale_layout; /* B200MOE_A_SCALE_*                                       */
+  int gated_act;     /* EPI_SILU_MUL only: B200MOE_ACT_SILU (0, the default), GELU,
+                        GELU_TANH, SWIGLUSTEP (act_param0 = its limit) or SITU
+                        (act_param0 = beta, act_param1 = linear beta or <= 0) applied to the
+                        gate half in the epilogue, fp32, one rounding at the store   */
+  float act_param0, act_param1;
+  float clamp_limit; /* > 0: the layer's gemm1 clamp (gate <= limit, |up| <= limit,
+                        fused_moe_interface.py:436-441 of the reference) applied to the
+                        accumulators before either gated epilogue; 0 = none          */
 } b200moe_gemm_args;
 
 /* cutlass_grouped_gemm_interface (csrc/xpu/torch_bindings.cpp:58-67,

@@ -144,10 +144,16 @@ def _layer(E, H, I, T, k, seed, w2_rows=None):
     return x, w13, w2, tw, ti.to(torch.int32)
 
 
-@pytest.mark.parametrize("activation", ["gelu", "gelu_tanh", "swiglustep", "situ", "relu2_no_mul"])
+@pytest.mark.parametrize("activation", ["silu", "gelu", "gelu_tanh", "swiglustep", "situ", "relu2_no_mul"])
 @pytest.mark.parametrize("clamp", [None, 1.0])
-def test_layer_with_each_activation(ops, activation, clamp):
+@pytest.mark.parametrize("fused", [True, False])
+def test_layer_with_each_activation(ops, activation, clamp, fused, monkeypatch):
+    """Every gated activation (and the layer's clamp) both ways: evaluated in the first GEMM's
+    epilogue, and as the stand-alone kernel between the two GEMMs (relu2_no_mul is not gated
+    and always takes the second way)."""
     from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
+    if not fused:
+        monkeypatch.setenv("B200MOE_UNFUSED_ACT", "1")
     E, H, I, T, k = 4, 256, 384, 40, 2
     x, w13, w2, tw, ti = _layer(E, H, I, T, k, 11, w2_rows=2 * I if activation == "relu2_no_mul" else None)
     kw = dict(activation_situ_beta=4.0, activation_situ_linear_beta=25.0) if activation == "situ" else {}
@@ -174,9 +180,16 @@ def test_situ_needs_beta():
         XpuFusedMoe(w13, None, None, w2, None, None, 2, "tanh", 2)
 
 
-@pytest.mark.parametrize("activation,clamp", [("silu", 0.5), ("gelu", None), ("relu2_no_mul", None)])
-def test_block_fp8_layer_with_unfused_activation(ops, activation, clamp):
+@pytest.mark.parametrize("activation,clamp", [("silu", 0.5), ("gelu", None), ("relu2_no_mul", None),
+                                              ("swiglustep", 2.0), ("situ", None), ("gelu_tanh", 1.0)])
+@pytest.mark.parametrize("fused", [True, False])
+def test_block_fp8_layer_with_each_activation(ops, activation, clamp, fused, monkeypatch):
+    """Block-FP8 layer: activation (+ clamp) and the group-128 quantisation of its result in the
+    first GEMM's epilogue, or as separate kernels on the bf16 output of that GEMM."""
     from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
+    if not fused:
+        monkeypatch.setenv("B200MOE_UNFUSED_ACT", "1")
+    kw = dict(activation_situ_beta=4.0, activation_situ_linear_beta=25.0) if activation == "situ" else {}
     E, H, I, T, k = 4, 256, 256, 48, 2
     g = torch.Generator().manual_seed(5)
     K2 = 2 * I if activation == "relu2_no_mul" else I
@@ -187,15 +200,17 @@ def test_block_fp8_layer_with_unfused_activation(ops, activation, clamp):
     tw, ti = O.topk_softmax(torch.randn(T, E, generator=g), k, True)
     ti = ti.to(torch.int32)
     moe = XpuFusedMoe(q13.to(DEV), s13.to(DEV), None, q2.to(DEV), s2.to(DEV), None, k, activation, E,
-                      gemm1_clamp_limit=clamp)
+                      gemm1_clamp_limit=clamp, **kw)
     out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
     moe.apply(out, x.to(DEV), tw.to(DEV), ti.to(DEV))
     ref = O.fused_moe("fp8block", x, q13, s13, None, q2, s2, None, tw, ti, activation,
-                      gemm1_clamp_limit=clamp, out_dtype=torch.float32)
+                      gemm1_clamp_limit=clamp, out_dtype=torch.float32,
+                      situ_beta=4.0, situ_linear_beta=25.0)
     err = (out.float().cpu() - ref).abs()
-    # The layer rounds the activation to bf16 before quantising it (as the reference does), the
-    # oracle keeps fp32: an e4m3 code flips now and then, and a flipped code of a squared value
-    # is worth more, hence the wider element bound for relu2.
-    tol = 0.15 if activation == "relu2_no_mul" else 5e-2
+    # Unfused, the layer rounds the activation to bf16 before quantising it (as the reference
+    # does), the oracle keeps fp32: an e4m3 code flips now and then, and a flipped code of a
+    # squared value is worth more, hence the wider element bound for relu2.  Fused, the
+    # activation is quantised from fp32 like the oracle's.
+    tol = 0.15 if activation == "relu2_no_mul" else (2e-2 if fused else 5e-2)
     assert (err <= tol + tol * ref.abs()).all(), f"max err {err.max():.4g}"
     assert err.mean() < 2e-2 * ref.abs().mean()

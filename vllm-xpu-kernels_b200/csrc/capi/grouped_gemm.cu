@@ -50,6 +50,11 @@ constexpr int kMaxKBlocks = 160;  // K <= 20480 for the FP8 block-scaled recipe
 
 enum : int { KIND_F16 = 0, KIND_F8 = 1 };
 
+// Internal epilogue code next to the three public ones: the split gated tile with any of the
+// gated activations and the layer's clamp, selected at run time.  It is an instantiation of
+// its own so that the SiLU epilogue of the default path keeps its registers to itself.
+constexpr int kEpiGatedAny = 3;
+
 struct GemmParams {
   const float* a_scale;
   const float* b_scale;
@@ -65,6 +70,9 @@ struct GemmParams {
   int ab_fmt;  // operand format code of the instruction descriptor
   const int64_t* d_row_ptr;  // optional per-row destination addresses (store epilogue)
   float alpha, limit;
+  int act;               // B200MOE_ACT_* of the split gated epilogue
+  float act_p0, act_p1;  // its parameters (swiglustep limit; situ betas)
+  float clamp;           // > 0: gate <= clamp and |up| <= clamp before the activation
 };
 
 struct TileCoord {
@@ -174,6 +182,27 @@ __device__ __forceinline__ float swiglu_oai_f32(float g, float u, float alpha, f
   return (u + 1.0f) * (g * fast_sigmoid(g * alpha));
 }
 
+// act(gate) * up for the activations other than SiLU, in fp32 (one rounding, at the store).
+__device__ __forceinline__ float gated_act_f32(int act, float g, float u, float p0, float p1) {
+  switch (act) {
+    case B200MOE_ACT_GELU:
+      return g * 0.5f * (1.0f + erff(g * 0.70710678118654752440f)) * u;
+    case B200MOE_ACT_GELU_TANH: {
+      const float inner = 0.79788456080286535588f * (g + 0.044715f * (g * g * g));
+      return 0.5f * g * (1.0f + tanhf(inner)) * u;
+    }
+    case B200MOE_ACT_SWIGLUSTEP:
+      return fminf(silu_f32(g), p0) * fmaxf(fminf(u, p0), -p0);
+    case B200MOE_ACT_SITU: {
+      const float ag = p0 * tanhf(g / p0) * fast_sigmoid(g);
+      const float au = p1 > 0.0f ? p1 * tanhf(u / p1) : u;
+      return ag * au;
+    }
+    default:
+      return silu_f32(g) * u;
+  }
+}
+
 __device__ __forceinline__ float load_bias(const void* bias, int dtype, int64_t i) {
   if (dtype == B200MOE_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias)[i]);
   if (dtype == B200MOE_F16) return __half2float(reinterpret_cast<const __half*>(bias)[i]);
@@ -244,7 +273,8 @@ struct Config {
   static constexpr int THREADS = 128 + EPI_WARPS * 32;   // warps 0..3: producer, MMA, 2 spare
   static constexpr int CPT = BN / 2;                     // accumulator columns per reader thread
   static constexpr int NCH = CPT / 32;                   // 32-column tcgen05.ld chunks per thread
-  static constexpr bool GATED_SPLIT = EPI == B200MOE_EPI_SILU_MUL;  // tile = [gate half | up half]
+  static constexpr bool GATED_SPLIT =
+      EPI == B200MOE_EPI_SILU_MUL || EPI == kEpiGatedAny;  // tile = [gate half | up half]
   // The fp8 128x256 tile keeps 128 fp32 accumulators per reader thread: the reader
   // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
   static constexpr bool REBALANCE_REGS = BN == 256;
@@ -393,13 +423,25 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
         store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, local_row);
       }
     }
-  } else if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
+  } else if constexpr (C::GATED_SPLIT) {
     constexpr int HALF = CPT / 2;
     const int half_n = p.N / 2;
     const int col0 = tc.n_tile * (C::BN / 2) + g * HALF;
     float o[HALF];
+    if constexpr (C::EPI == B200MOE_EPI_SILU_MUL) {
 #pragma unroll
-    for (int j = 0; j < HALF; ++j) o[j] = silu_f32(acc[j]) * acc[HALF + j];
+      for (int j = 0; j < HALF; ++j) o[j] = silu_f32(acc[j]) * acc[HALF + j];
+    } else {  // the layer's clamp and the other gated activations, same place, same pass
+#pragma unroll  // fully: the accumulators stay in registers only with static indices
+      for (int j = 0; j < HALF; ++j) {
+        float gte = acc[j], up = acc[HALF + j];
+        if (p.clamp > 0.0f) {
+          gte = fminf(gte, p.clamp);
+          up = fmaxf(fminf(up, p.clamp), -p.clamp);
+        }
+        o[j] = gated_act_f32(p.act, gte, up, p.act_p0, p.act_p1);
+      }
+    }
     if (p.d_dtype == B200MOE_E4M3) {
       // per-token-group-128 quantisation of the activation: the 128 output columns of
       // this tile are one group, held by two threads (column groups 0 and 1)
@@ -439,8 +481,14 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
     const int col0 = tc.n_tile * C::BN + g * CPT;
     float o[CPT / 2];
 #pragma unroll
-    for (int j = 0; j < CPT / 2; ++j)
-      o[j] = swiglu_oai_f32(acc[2 * j], acc[2 * j + 1], p.alpha, p.limit);
+    for (int j = 0; j < CPT / 2; ++j) {
+      float gte = acc[2 * j], up = acc[2 * j + 1];
+      if (p.clamp > 0.0f) {  // the layer's clamp on the interleaved halves
+        gte = fminf(gte, p.clamp);
+        up = fmaxf(fminf(up, p.clamp), -p.clamp);
+      }
+      o[j] = swiglu_oai_f32(gte, up, p.alpha, p.limit);
+    }
     if (col0 < p.N)
       store_rows_coalesced<CPT / 2>(wbuf, lane, p.d_dtype, col0 / 2, o, (p.N - col0) / 2, local_row);
   }
@@ -828,6 +876,10 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   p.ldd = a.epilogue == B200MOE_EPI_STORE ? a.N : a.N / 2;  // elements (bytes for e4m3)
   p.alpha = a.alpha;
   p.limit = a.limit;
+  p.act = a.gated_act;
+  p.act_p0 = a.act_param0;
+  p.act_p1 = a.act_param1;
+  p.clamp = a.clamp_limit;
   p.d_row_ptr = a.epilogue == B200MOE_EPI_STORE ? a.d_row_ptr : nullptr;
   p.ab_fmt = a.a_dtype == B200MOE_BF16 ? 1 : 0;  // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
 
@@ -1010,6 +1062,11 @@ extern "C" int b200moe_dequant_weights(int recipe, const void* B, const void* b_
   return launch_status("dequant_weights");
 }
 
+// the split gated epilogue with something other than plain SiLU
+static bool gated_any(const b200moe_gemm_args& a) {
+  return a.epilogue == B200MOE_EPI_SILU_MUL && (a.gated_act != B200MOE_ACT_SILU || a.clamp_limit > 0.0f);
+}
+
 template <int KIND, bool MN, bool PROMOTE, int BN, int STAGES, bool PAIR = false>
 static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaStream_t st) {
   switch (a.epilogue) {
@@ -1017,8 +1074,14 @@ static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cu
       return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, STAGES, PAIR>>(a, B, b_dtype, st);
     case B200MOE_EPI_SILU_MUL:
       // an MN-major split tile needs one weight box for the gate half and one for the up half
-      if constexpr (MN && !PAIR && BN * (KIND == KIND_F16 ? 2 : 1) < 256) return B200MOE_UNSUPPORTED;
-      else return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SILU_MUL, STAGES, PAIR>>(a, B, b_dtype, st);
+      if constexpr (MN && !PAIR && BN * (KIND == KIND_F16 ? 2 : 1) < 256) {
+        return B200MOE_UNSUPPORTED;
+      } else if (gated_any(a)) {
+        if constexpr (PAIR) return B200MOE_UNSUPPORTED;  // the caller does not pair these
+        else return launch_config<Config<KIND, MN, PROMOTE, BN, kEpiGatedAny, STAGES, false>>(a, B, b_dtype, st);
+      } else {
+        return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SILU_MUL, STAGES, PAIR>>(a, B, b_dtype, st);
+      }
     case B200MOE_EPI_SWIGLU_OAI:
       return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_SWIGLU_OAI, STAGES, PAIR>>(a, B, b_dtype, st);
     default:
@@ -1058,10 +1121,13 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
   if (quant_out && (a.epilogue != B200MOE_EPI_SILU_MUL || !a.d_scale || (a.N / 2) % 128 != 0))
     return B200MOE_UNSUPPORTED;
   const bool wide = want_wide_tile(a);
-  const bool pair = want_pair(a, wide);
+  const bool pair = want_pair(a, wide) && !gated_any(a);
 
-  if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR || a.a_scale_layout == B200MOE_A_SCALE_ROW_MAJOR_DECODE)
+  if (a.gated_act < B200MOE_ACT_SILU || a.gated_act > B200MOE_ACT_SITU) return B200MOE_INVALID_ARG;
+  if (a.a_scale_layout == B200MOE_A_SCALE_KBLOCK_MAJOR || a.a_scale_layout == B200MOE_A_SCALE_ROW_MAJOR_DECODE) {
+    if (gated_any(a) || a.clamp_limit > 0.0f) return B200MOE_UNSUPPORTED;  // SiLU only on that kernel
     return grouped_gemm_decode(a, st);
+  }
   if (a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3 && !a.a_scale && !a.b_scale) {
     // Unit scales: a plain e4m3 x e4m3 contraction with one accumulation phase per tile.
     // No recipe of the layer uses it; it is the same-dtype ceiling the block-scaled

@@ -606,7 +606,9 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
                          const OptTensor& D_scale = std::nullopt,
-                         const OptTensor& D_row_ptr = std::nullopt, int64_t a_scale_layout = 0) {
+                         const OptTensor& D_row_ptr = std::nullopt, int64_t a_scale_layout = 0,
+                         int64_t gated_act = 0, double act_param0 = 0.0, double act_param1 = 0.0,
+                         double clamp_limit = 0.0) {
   const char* op = "cutlass_grouped_gemm_interface";
   TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && D.is_contiguous(), op, ": A, B and D must be contiguous");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
@@ -640,6 +642,12 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
   a.E = num_experts;
   a.alpha = static_cast<float>(alpha);
   a.limit = static_cast<float>(limit);
+  TORCH_CHECK(gated_act >= B200MOE_ACT_SILU && gated_act <= B200MOE_ACT_SITU, op,
+              ": the fused gated activation is silu, gelu, gelu_tanh, swiglustep or situ");
+  a.gated_act = static_cast<int>(gated_act);
+  a.act_param0 = static_cast<float>(act_param0);
+  a.act_param1 = static_cast<float>(act_param1);
+  a.clamp_limit = static_cast<float>(clamp_limit);
   const auto bt = B.scalar_type();
   if (bt == at::kFloat8_e4m3fn && !B_scale.has_value() && !A_scale.has_value() &&
       a.a_dtype == B200MOE_E4M3) {
@@ -705,9 +713,11 @@ Tensor b200_grouped_gemm(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const Tensor& rows_per_expert, int64_t N, int64_t K, int64_t num_experts,
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
                          const OptTensor& D_scale, const OptTensor& D_row_ptr,
-                         int64_t a_scale_layout) {
+                         int64_t a_scale_layout, int64_t gated_act, double act_param0,
+                         double act_param1, double clamp_limit) {
   return grouped_gemm_impl(A, A_scale, B, B_scale, bias, D, rows_per_expert, N, K, num_experts,
-                           epilogue, b_layout, alpha, limit, D_scale, D_row_ptr, a_scale_layout);
+                           epilogue, b_layout, alpha, limit, D_scale, D_row_ptr, a_scale_layout,
+                           gated_act, act_param0, act_param1, clamp_limit);
 }
 
 Tensor b200_grouped_gemm_check(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
@@ -1016,7 +1026,8 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
       "b200_grouped_gemm(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? bias, "
       "Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, int "
       "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None, Tensor? D_row_ptr=None, int "
-      "a_scale_layout=0) -> Tensor");
+      "a_scale_layout=0, int gated_act=0, float act_param0=0.0, float act_param1=0.0, float "
+      "clamp_limit=0.0) -> Tensor");
   m.def(
       "b200_grouped_gemm_check(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? "
       "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "

@@ -324,15 +324,16 @@ class XpuFusedMoe:
             return self._run_experts_mx(rows, row_scales, rows_per_expert, out_dtype, out, oai, clamp)
         if self.is_block_fp8:
             K2 = I * self.inter_size_scale
-            if (self.activation == "silu" and not clamp and I % 128 == 0
-                    and not os.environ.get("B200MOE_UNFUSED_ACT")):
-                # SiLU*mul and the group-128 re-quantisation run in the GEMM's epilogue
+            fused = self._fused_gated(clamp)
+            if (fused is not None and I % 128 == 0 and not os.environ.get("B200MOE_UNFUSED_ACT")):
+                # activation * up (with the layer's clamp) and the group-128 re-quantisation run
+                # in the GEMM's epilogue
                 act_q = torch.empty((R, I), dtype=torch.float8_e4m3fn, device=dev)
                 act_s = torch.empty((R, I // 128), dtype=torch.float32, device=dev)
                 with self._stage("gemm1"):
                     gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
                          act_q, rows_per_expert, 2 * I, hidden_size, E, EPI_SILU_MUL, B_LAYOUT_KN,
-                         1.702, 7.0, act_s)
+                         1.702, 7.0, act_s, None, 0, *fused)
             else:
                 gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
                 with self._stage("gemm1"):
@@ -356,13 +357,16 @@ class XpuFusedMoe:
         else:
             w13, w2, layout = self._weights_16(out_dtype)
             K2 = I * self.inter_size_scale
-            fused_epi = (self.activation == "silu" or oai) and not clamp
+            fused = self._fused_gated(clamp)
+            fused_epi = (fused is not None or oai) and not os.environ.get("B200MOE_UNFUSED_ACT")
             if fused_epi:
+                lim = float(self.gemm1_clamp_limit) if clamp else 0.0
+                extra = fused if fused is not None else (0, 0.0, 0.0, lim)
                 act = torch.empty((R, I), dtype=out_dtype, device=dev)
                 with self._stage("gemm1"):
                     gemm(remapped, None, w13, None, self.w13_bias, act, rows_per_expert, 2 * I,
                          hidden_size, E, EPI_SWIGLU_OAI if oai else EPI_SILU_MUL, layout, 1.702,
-                         7.0)
+                         7.0, None, None, 0, *extra)
             else:
                 gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
                 with self._stage("gemm1"):
@@ -376,6 +380,22 @@ class XpuFusedMoe:
                 gemm(act, None, w2, None, self.w2_bias, gemm2_out, rows_per_expert, hidden_size, K2,
                      E, EPI_STORE, layout, 1.702, 7.0, None, row_ptr)
         return gemm2_out
+
+    def _fused_gated(self, clamp):
+        """(activation code, param0, param1, clamp limit) when the activation is one the first
+        GEMM's split gated epilogue evaluates (act(gate) * up on the fp32 accumulators, with
+        the layer's clamp before it), else None (swigluoai has an epilogue of its own;
+        relu2_no_mul is not gated)."""
+        if self._act_code < 0 or self.activation == "relu2_no_mul" or self.inter_size_scale != 1:
+            return None
+        p0 = p1 = 0.0
+        if self.activation == "swiglustep":
+            p0 = 7.0
+        elif self.activation == "situ":
+            p0 = self.activation_situ_beta
+            p1 = -1.0 if self.activation_situ_linear_beta is None else self.activation_situ_linear_beta
+        lim = float(self.gemm1_clamp_limit) if clamp else 0.0
+        return (self._act_code, float(p0), float(p1), lim)
 
     @staticmethod
     def _pad_mx_scales(scales, width):
@@ -465,9 +485,6 @@ class XpuFusedMoe:
             if shared_output is not None:
                 torch.ops._moe_C.b200_moe_gather_add(output, gemm2_out, topk_weights, row_map,
                                                      shared_output)
-            elif valid_tokens is not None:
-                torch.ops._moe_C.b200_moe_gather_bounded(output, gemm2_out, topk_weights, row_map,
-                                                         valid_tokens)
             else:
                 torch.ops._moe_C.moe_gather(output, gemm2_out, topk_weights, row_map, self.num_experts)
 
