@@ -278,6 +278,7 @@ struct Config {
   // The fp8 128x256 tile keeps 128 fp32 accumulators per reader thread: the reader
   // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
   static constexpr bool REBALANCE_REGS = BN == 256;
+  static constexpr int XCHG = (EPI_ == B200MOE_EPI_SILU_MUL || EPI_ == kEpiGatedAny) ? 256 : 1;
   static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES;
   static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && !PAIR_ && N_CHUNKS < 2),
                 "a split gated tile needs two weight boxes");
@@ -415,13 +416,11 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
   if constexpr (C::EPI == B200MOE_EPI_STORE) {
     const int col0 = tc.n_tile * C::BN + g * CPT;
     if (col0 < p.N) {
-      if (p.d_row_ptr) {  // the row's home may be another GPU's memory
-        store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, [&](int rr) -> void* {
-          return rr < warp_rows_valid ? reinterpret_cast<void*>(p.d_row_ptr[warp_row0 + rr]) : nullptr;
-        });
-      } else {
-        store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, local_row);
-      }
+      auto remote_row = [&](int rr) -> void* {  // the row's home may be another GPU's memory
+        return rr < warp_rows_valid ? reinterpret_cast<void*>(p.d_row_ptr[warp_row0 + rr]) : nullptr;
+      };
+      if (p.d_row_ptr) store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, remote_row);
+      else store_rows_coalesced<CPT>(wbuf, lane, p.d_dtype, col0, acc, p.N - col0, local_row);
     }
   } else if constexpr (C::GATED_SPLIT) {
     constexpr int HALF = CPT / 2;
@@ -533,9 +532,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ Barriers bars;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
-  __shared__ float xchg[2][256];  // group-amax exchange of the quantising epilogue, by tile parity
+  __shared__ float xchg[2][C::XCHG];  // group-amax exchange of the quantising epilogue, by tile parity
   __shared__ float sb_smem[2][2 * kMaxKBlocks];  // weight scales of the tile's two column blocks
-  __shared__ uint4 epi_buf[8][128];              // per reader warp: 32 rows x 64 B for coalesced stores
+  __shared__ uint4 epi_buf[C::EPI_WARPS][128];   // per reader warp: 32 rows x 64 B for coalesced stores
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -614,14 +613,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       const int kb_per_phase = C::PROMOTE ? 1 : num_kb;
       for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
         for (int ph = 0; ph < phases_per_tile && ok; ++ph) {
+          // With one accumulation phase per K block the free accumulator buffer is what this
+          // thread waits for; look at the operand stage first, so that wait is already behind
+          // it when the buffer comes back.
+          if constexpr (C::PROMOTE) {
+            ok = mbar_wait(&bars.full[stage], phase, abort_p);
+            if (!ok) break;
+          }
           ok = mbar_wait(&bars.tempty[buf], buf_phase ^ 1u, abort_p);
           if (!ok) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * C::BN;
           for (int kb = 0; kb < kb_per_phase && ok; ++kb) {
-            ok = mbar_wait(&bars.full[stage], phase, abort_p);
-            if (!ok) break;
-            tc_fence_after();
+            if constexpr (!C::PROMOTE) {
+              ok = mbar_wait(&bars.full[stage], phase, abort_p);
+              if (!ok) break;
+              tc_fence_after();
+            }
             const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
             const uint32_t b_addr = a_addr + C::A_BYTES;
 #pragma unroll
@@ -740,13 +748,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           s0 = sa * sbs[2 * ph + sel0];
           s1 = sa * sbs[2 * ph + sel1];
         }
-        int cur_buf = buf;
 #pragma unroll
         for (int q = 0; q < NCH / 2; ++q) {
           tmem_ld_wait();
           const bool last_pair = q + 1 == NCH / 2;
-          bool more = true;
-          if (last_pair) {
+          const int c0 = 2 * q, c1 = 2 * q + 1;
+          const float sc0 = c0 < NCH / 2 ? s0 : s1;
+          const float sc1 = c1 < NCH / 2 ? s0 : s1;
+          if (!last_pair) {
+            // consume a staged chunk, refill it with the chunk after next of the same buffer
+            accumulate32<C::PROMOTE>(acc + c0 * 32, ta, sc0);
+            tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, c0 + 2), ta);
+            accumulate32<C::PROMOTE>(acc + c1 * 32, tb, sc1);
+            tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, c1 + 2), tb);
+          } else {
             // every column of this buffer is in registers: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
@@ -754,25 +769,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               if constexpr (C::PAIR) mbar_arrive_cluster(&bars.tempty[buf], 0);
               else mbar_arrive(&bars.tempty[buf]);
             }
+            // The last two chunks are accumulated while the next partial is still being
+            // computed, so that the moment it is ready both staging buffers are free and its
+            // first two loads go out at once: from "accumulator complete" to "accumulator
+            // free again" is on the critical path of every K block (two buffers in flight).
+            accumulate32<C::PROMOTE>(acc + c0 * 32, ta, sc0);
+            accumulate32<C::PROMOTE>(acc + c1 * 32, tb, sc1);
             if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
-            more = ph + 1 < phases_per_tile;
-            if (more) {
+            if (ph + 1 < phases_per_tile) {
               ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
-              more = ok;
-              if (ok) tc_fence_after();
-              cur_buf = buf;
+              if (ok) {
+                tc_fence_after();
+                tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 0), ta);
+                tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 1), tb);
+              }
             }
           }
-          const int c0 = 2 * q, c1 = 2 * q + 1;
-          const int n0 = last_pair ? 0 : c0 + 2, n1 = last_pair ? 1 : c1 + 2;
-          const float sc0 = c0 < NCH / 2 ? s0 : s1;
-          const float sc1 = c1 < NCH / 2 ? s0 : s1;
-          accumulate32<C::PROMOTE>(acc + c0 * 32, ta, sc0);
-          if (more)
-            tmem_ld_32x32(tmem_base + lane_addr + cur_buf * C::BN + chunk_tmem_col<C>(g, n0), ta);
-          accumulate32<C::PROMOTE>(acc + c1 * 32, tb, sc1);
-          if (more)
-            tmem_ld_32x32(tmem_base + lane_addr + cur_buf * C::BN + chunk_tmem_col<C>(g, n1), tb);
         }
       }
       if (!ok) break;
