@@ -1106,11 +1106,18 @@ static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cu
 static bool want_pair(const b200moe_gemm_args& a, bool wide) {
   const char* force = getenv("B200MOE_PAIR");  // test hook: forces a tile shape for one call
   if (force) return atoi(force) != 0 && wide;
-  // CTA pairs schedule 256-row tiles: worth it once the experts are that tall on average.
-  // Measured on the Mixtral shapes: +3 % for 16-bit operands; nothing for the FP8 recipe,
-  // whose per-K-block accumulator hand-off gets slower across two CTAs.
+  // CTA pairs schedule 256-row tiles and halve the weight bytes each CTA stages per flop (a
+  // single CTA's 128x256 tile asks shared memory for more than it can deliver at the full MMA
+  // rate); worth it once the experts are tall enough that the 256-row tiles are not mostly
+  // padding.  Measured: +3 % for 16-bit operands on the Mixtral shapes; for the block-scaled
+  // FP8 recipe, whose per-K-block accumulator hand-off gets slower across two CTAs, +6-7 %
+  // with the store epilogue from 512 rows per expert on (second GEMM of the DeepSeek-V3 and
+  // Mixtral shapes), +2 % with the fused activation epilogue at 1024 rows per expert and
+  // -6 % at 512.
   const bool promote = a.recipe == B200MOE_RECIPE_FP8_BLOCK && a.a_dtype == B200MOE_E4M3;
-  return wide && !promote && a.R / a.E >= 1024;
+  const int64_t rows = a.R / a.E;
+  if (promote) return wide && rows >= (a.epilogue == B200MOE_EPI_STORE ? 512 : 1024);
+  return wide && rows >= 1024;
 }
 
 static bool want_wide_tile(const b200moe_gemm_args& a) {
