@@ -197,7 +197,7 @@ def score_bias(cfg):
 class Layer:
     """Routing + quantisation + XpuFusedMoe.apply, the sequence a caller runs per batch."""
 
-    def __init__(self, cfg, weights, T, dev, group=None, shared_weights=None):
+    def __init__(self, cfg, weights, T, dev, group=None, shared_weights=None, ep_backend=None):
         from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
         from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
         self.cfg, self.T, self.dev = cfg, T, dev
@@ -219,7 +219,7 @@ class Layer:
         if group is not None:
             from vllm_xpu_kernels.ep import (ExpertParallel, PeerExpertParallel, TokenExpertParallel,
                                              make_local_fn)
-            self.ep_backend = os.environ.get("B200MOE_EP", "token")
+            self.ep_backend = ep_backend or os.environ.get("B200MOE_EP", "token")
             if self.ep_backend in ("peer", "token"):
                 fp8 = cfg["recipe"] == "fp8block"
                 mx = cfg["recipe"] == "mxfp4"
@@ -504,6 +504,26 @@ def measure(cfg, dev, rank, world, group, steps, warmup, timer, with_e2e=True, c
     x, logits = x_pin.to(dev), logits_pin.to(dev)
     from vllm_xpu_kernels import capi
     lib = capi.lib()
+    if world > 1 and layer.ep_backend == "token":
+        # One step of the token-level exchange before anything is timed; if any rank fails
+        # (an exception, or a bounded device wait that gave up) all ranks fall back together to
+        # the row-level exchange, and the printed line says which one ran.
+        import torch.distributed as dist
+        ok = 1
+        try:
+            layer.step(x, logits)
+            torch.cuda.synchronize()
+            ok = int(torch.ops._xpu_C.b200_device_status() == 0)
+        except Exception as exc:  # noqa: BLE001 - any failure means "use the other exchange"
+            print(f"[rank {rank}] token-level exchange failed: {type(exc).__name__}: {exc}", file=sys.stderr)
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            del layer
+            torch.cuda.empty_cache()
+            os.environ["B200MOE_EP"] = "peer"      # workload_config() reports the exchange that ran
+            layer = Layer(cfg, weights, T, dev, group=group, shared_weights=shared_w, ep_backend="peer")
 
     for _ in range(warmup):
         layer.step(x, logits)
