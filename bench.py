@@ -115,10 +115,12 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------
-def _quant_fp8_block(w):
+def _quant_fp8_block(w, pow2=False):
     K, N = w.shape
     blk = w.view(K // 128, 128, N // 128, 128)
     s = (blk.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12)
+    if pow2:  # block scales rounded up to powers of two, as UE8M0-scaled checkpoints store them
+        s = torch.exp2(torch.ceil(torch.log2(s)))
     q = (blk / s.view(K // 128, 1, N // 128, 1)).clamp(-448, 448).view(K, N).to(torch.float8_e4m3fn)
     return q, s
 
@@ -157,7 +159,7 @@ def make_device_layer(cfg, dev, seed=0, experts=None):
             g = torch.Generator(device=dev).manual_seed(seed * 100003 + e * 7 + tag)
             w = torch.randn(K, N, generator=g, device=dev) / K ** 0.5
             if recipe == "fp8block":
-                q, s = _quant_fp8_block(w)
+                q, s = _quant_fp8_block(w, bool(cfg.get("pow2_scales")))
             elif recipe == "mxfp4":
                 q, s = _quant_mxfp4(w.t().contiguous())
             else:
@@ -201,7 +203,7 @@ class Layer:
         from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
         from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
         self.cfg, self.T, self.dev = cfg, T, dev
-        self.quant = quant_fp8_block_act
+        self.quant = lambda t: quant_fp8_block_act(t, self.moe.act_scales_pow2)
         E_loc = weights["w13"].shape[0]
         w13, w2 = weights["w13"], weights["w2"]
         if cfg["recipe"] == "mxfp4":
@@ -286,6 +288,8 @@ def flops_per_token(cfg):
 
 
 def act_format(cfg):
+    if cfg["recipe"] == "fp8block" and cfg.get("pow2_scales"):
+        return "fp8_pow2"
     return "mxfp8" if cfg["recipe"] == "mxfp4" else None
 
 
@@ -622,9 +626,9 @@ def stream_stages(cfg, stages, peaks, T):
             for name in nbytes if stages.get(name)}
 
 
-def short_config_run(key, dev, timer, peaks, steps=8, warmup=3):
+def short_config_run(key, dev, timer, peaks, steps=8, warmup=3, **over):
     """A short run of another configuration on one GPU: the figures that matter, plus parity."""
-    cfg = dict(CONFIGS[key], key=key)
+    cfg = dict(CONFIGS[key], key=key, **over)
     res = measure(cfg, dev, 0, 1, None, steps, warmup, timer, with_e2e=False)
     T = cfg["T"]
     out = {"workload": cfg["name"], "tokens": T, "steps": steps, "ms_per_step": res["ms"],
@@ -802,6 +806,13 @@ def main():
             torch.cuda.empty_cache()
             line["other_configs"] = {k: short_config_run(k, dev, timer, peaks)
                                      for k in ("c1", "c2", "c3") if k != args.config}
+            # The same DeepSeek-V3-shaped layer with its 128x128 block scales rounded up to
+            # powers of two (how UE8M0-scaled checkpoints store them): the layer then lets the
+            # tensor core apply the scales.  A variant of the workload, reported beside it.
+            v = short_config_run("c3", dev, timer, peaks, shared=False, pow2_scales=True,
+                                 name=CONFIGS["c3"]["name"] + "; block scales powers of two")
+            v["roofline"]["traffic"] = None
+            line["c3_pow2_scales"] = v
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

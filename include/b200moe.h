@@ -345,6 +345,16 @@ typedef struct b200moe_gemm_args {
   float clamp_limit; /* > 0: the layer's gemm1 clamp (gate <= limit, |up| <= limit,
                         fused_moe_interface.py:436-441 of the reference) applied to the
                         accumulators before either gated epilogue; 0 = none          */
+  int scales_pow2;   /* FP8_BLOCK recipe with E4M3 activations only.  1: every a_scale and
+                        b_scale value is an exact power of two (what
+                        per_token_group_fp8_quant(..., scale_ue8m0=True) produces, and how
+                        UE8M0-scaled checkpoints store their 128x128 block scales).  The
+                        scales are then applied by the tensor core itself (block-scaled MMA,
+                        one accumulation phase per tile) instead of once per 128 of K in
+                        registers, and the quantising epilogue writes power-of-two d_scale
+                        values, so its output can feed the next GEMM the same way.  A scale
+                        that is not a power of two leaves B200MOE_INVALID_ARG in the device
+                        status word (b200moe_device_status).  STORE and SILU_MUL epilogues. */
 } b200moe_gemm_args;
 
 /* cutlass_grouped_gemm_interface (csrc/xpu/torch_bindings.cpp:58-67,

@@ -677,10 +677,14 @@ def qdq_act(recipe, x, act_format=None):
     (moe_utils.py:190-204), nothing for bf16 and for MXFP4 weights run W4A16.
     ``act_format="mxfp8"``: e4m3 with e8m0 scales per 32 columns
     (moe_utils.py:84-109, 198-200), what the block-scaled MXFP4 path feeds its
-    tensor cores."""
+    tensor cores.  ``act_format="fp8_pow2"``: group 128 with power-of-two scales,
+    what a block-FP8 layer whose weight scales are powers of two feeds them."""
     if act_format == "mxfp8":
         q, sf = quant_mxfp8_act(x)
         return dequant_mxfp8_act(q, sf)
+    if act_format == "fp8_pow2":   # per-token-group-128 FP8 with the scale rounded up to a power of
+        q, s = per_token_group_fp8_quant(x, 128, scale_ue8m0=True)   # two (the op's scale_ue8m0 flag,
+        return dequant_fp8_group_act(q, s)                           # csrc/quantization/fp8/fp8_quant.cpp:238-252)
     if recipe == "fp8block":
         q, s = per_token_group_fp8_quant(x, 128)
         return dequant_fp8_group_act(q, s)

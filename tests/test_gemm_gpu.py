@@ -339,3 +339,79 @@ def test_large_against_cuda_core_check(ops, recipe):
         ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq, Bs, None, D, rows, N, K, E, EPI_STORE, KN)
         ops._xpu_C.b200_grouped_gemm_check(Aq.to(DEV), As.to(DEV), Bq, Bs, None, ref, rows, N, K, E, KN)
     close(D, ref)
+
+
+# ---- block-FP8 with power-of-two scales: scales applied by the tensor core -------------------
+def _pow2_case(E, rows, K, N, seed):
+    R = sum(rows)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(R + 3, K, generator=g) * torch.exp2(torch.randint(-3, 4, (R + 3, 1), generator=g).float())
+    Aq, As = O.per_token_group_fp8_quant(x.to(torch.bfloat16), 128, scale_ue8m0=True)
+    Bq, Bs = [], []
+    for _ in range(E):
+        w = torch.randn(K, N, generator=g) / K ** 0.5
+        w = w * torch.exp2(torch.randint(-2, 3, (K // 128, N // 128), generator=g).float()
+                           ).repeat_interleave(128, 0).repeat_interleave(128, 1)
+        blk = w.view(K // 128, 128, N // 128, 128)
+        sc = torch.exp2(torch.ceil(torch.log2((blk.abs().amax(dim=(1, 3)) / 448.0).clamp_min(1e-12))))
+        q = (blk / sc.view(K // 128, 1, N // 128, 1)).clamp(-448, 448).reshape(K, N).to(torch.float8_e4m3fn)
+        Bq.append(q)
+        Bs.append(sc)
+    return Aq, As, torch.stack(Bq), torch.stack(Bs), torch.tensor(rows, dtype=torch.int32), R
+
+
+@pytest.mark.parametrize("E,rows,K,N", [
+    (1, [128], 128, 256),                          # one tile, one stage
+    (1, [100], 512, 512),                          # the four stages of the ring once
+    (3, [130, 0, 257], 1024, 768),                 # ring wraps; three column tiles
+    (2, [77, 300], 2048, 7168),                    # second GEMM of the DeepSeek-V3 layer
+    (6, [500, 513, 1, 640, 390, 128], 1536, 1280), # 100 tiles... several per CTA
+])
+def test_fp8_pow2_scales_store(ops, E, rows, K, N):
+    Aq, As, Bq, Bs, rpe, R = _pow2_case(E, rows, K, N, K + N)
+    ref = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As)[:R], Bq, Bs, None, rpe, torch.float32)
+    D = torch.full((R + 3, N), 3.0, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, D, rpe.to(DEV),
+                                 N, K, E, EPI_STORE, KN, 1.702, 7.0, None, None, 0, 0, 0.0, 0.0, 0.0, True)
+    close(D[:R], ref)
+    assert (D[R:] == 3.0).all()
+    # the same problem through the promotion kernel agrees (same contract, other arithmetic order)
+    D2 = torch.empty(R + 3, N, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, D2, rpe.to(DEV),
+                                 N, K, E, EPI_STORE, KN)
+    close(D2[:R], ref)
+
+
+@pytest.mark.parametrize("E,rows,K,N", [(2, [100, 60], 256, 512), (3, [200, 129, 300], 7168, 1024)])
+def test_fp8_pow2_scales_fused_silu_quant(ops, E, rows, K, N):
+    """First GEMM of the layer on the tensor-core-scaled kernel: SiLU*mul and the group-128
+    quantisation in the epilogue, with power-of-two output scales."""
+    Aq, As, Bq, Bs, rpe, R = _pow2_case(E, rows, K, N, 7)
+    h = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As)[:R], Bq, Bs, None, rpe, torch.float32)
+    gact = O.silu_mul_fp32(h)
+    Dq = torch.zeros(R + 3, N // 2, dtype=torch.float8_e4m3fn, device=DEV)
+    Ds = torch.zeros(R + 3, N // 2 // 128, dtype=torch.float32, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, Dq, rpe.to(DEV),
+                                 N, K, E, EPI_SILU, KN, 1.702, 7.0, Ds, None, 0, 0, 0.0, 0.0, 0.0, True)
+    ds = Ds.cpu()[:R]
+    assert torch.equal(torch.exp2(torch.log2(ds).round()), ds)          # exact powers of two
+    _, rs = O.per_token_group_fp8_quant(gact, 128, scale_ue8m0=True)
+    amax = gact.view(R, -1, 128).abs().amax(-1)
+    frac = torch.log2(amax.clamp_min(1e-10) / 448)
+    clear = (frac - frac.round()).abs() > 1e-3                           # not within rounding of a power of two
+    assert torch.equal(ds[clear], rs[clear])
+    deq = Dq.cpu()[:R].float().view(R, -1, 128) * ds.unsqueeze(-1)
+    assert ((deq.view(R, -1) - gact).abs() <= 0.07 * gact.abs() + 2e-3 * ds.repeat_interleave(128, 1) * 448 / 16 + 1e-6).all()
+
+
+def test_fp8_pow2_scales_refuse_other_scales(ops):
+    """A scale that is not a power of two cannot go through the tensor core's scaling: the kernel
+    says so in the device status word instead of applying it wrongly in silence."""
+    Aq, As, Bq, Bs, rpe, R = _pow2_case(1, [64], 256, 256, 3)
+    As = As.clone()
+    As[5, 1] *= 1.5
+    D = torch.empty(R + 3, 256, dtype=torch.bfloat16, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), None, D, rpe.to(DEV),
+                                 256, 256, 1, EPI_STORE, KN, 1.702, 7.0, None, None, 0, 0, 0.0, 0.0, 0.0, True)
+    assert ops._xpu_C.b200_device_status() == -1      # B200MOE_INVALID_ARG, and the word is cleared
+    assert ops._xpu_C.b200_device_status() == 0

@@ -48,7 +48,14 @@ constexpr int kMaxExpertsSmem = 1024;
 constexpr int kSwizzleGroupM = 8;
 constexpr int kMaxKBlocks = 160;  // K <= 20480 for the FP8 block-scaled recipe
 
-enum : int { KIND_F16 = 0, KIND_F8 = 1 };
+// KIND_F8S: e4m3 x e4m3 with POWER-OF-TWO block scales (per row per 128 of K for A, per
+// 128x128 block for B), applied by the tensor core itself (kind::mxf8f6f4.block_scale, UE8M0
+// factors in tensor memory): one accumulation phase per tile, no promotion in registers.
+enum : int { KIND_F16 = 0, KIND_F8 = 1, KIND_F8S = 2 };
+constexpr int kSfaBytes = 512;    // per stage: one scale word (4 x e8m0) per row of the A tile
+constexpr int kSfbBytes = 1024;   // per stage: the same for the 256 weight columns of the tile
+constexpr int kSfaCol = 256;      // tensor-memory columns of the scale words (KIND_F8S: one
+constexpr int kSfbCol = 260;      //   256-column accumulator at column 0)
 
 // Internal epilogue code next to the three public ones: the split gated tile with any of the
 // gated activations and the layer's clamp, selected at run time.  It is an instantiation of
@@ -73,6 +80,7 @@ struct GemmParams {
   int act;               // B200MOE_ACT_* of the split gated epilogue
   float act_p0, act_p1;  // its parameters (swiglustep limit; situ betas)
   float clamp;           // > 0: gate <= clamp and |up| <= clamp before the activation
+  int pow2_scales;       // the quantising epilogue rounds its scales up to powers of two
 };
 
 struct TileCoord {
@@ -259,6 +267,7 @@ struct Config {
   static constexpr int BN = BN_;
   static constexpr int EPI = EPI_;
   static constexpr int STAGES = STAGES_;
+  static constexpr bool SCALED = KIND_ == KIND_F8S;
   static constexpr int ELT = KIND == KIND_F16 ? 2 : 1;
   static constexpr int BK = kStageRowBytes / ELT;       // elements of K per stage
   static constexpr int UMMA_K = 32 / ELT;                // K per MMA instruction
@@ -267,7 +276,10 @@ struct Config {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int CHUNK_COLS = kStageRowBytes / ELT;  // N columns per MN-major TMA box
   static constexpr int N_CHUNKS = B_COLS / CHUNK_COLS;      // boxes this CTA loads per stage
-  static constexpr int ACC_BUFS = 512 / BN;              // tensor-memory accumulator ring (all 512 columns)
+  // tensor-memory accumulator ring: all 512 columns, or one 256-column buffer next to the
+  // scale columns (the accumulator then leaves tensor memory once per tile, at its end)
+  static constexpr int ACC_BUFS = SCALED ? 1 : 512 / BN;
+  static constexpr int SF_BYTES = SCALED ? kSfaBytes + kSfbBytes : 0;   // per stage, after the operand ring
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_WARPS = 8;                    // two reader warps per TMEM lane quadrant
   static constexpr int THREADS = 128 + EPI_WARPS * 32;   // warps 0..3: producer, MMA, 2 spare
@@ -279,7 +291,10 @@ struct Config {
   // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
   static constexpr bool REBALANCE_REGS = BN == 256;
   static constexpr int XCHG = (EPI_ == B200MOE_EPI_SILU_MUL || EPI_ == kEpiGatedAny) ? 256 : 1;
-  static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES;
+  static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * (STAGE_BYTES + SF_BYTES);
+  static constexpr int SB_SMEM = PROMOTE_ ? 2 * kMaxKBlocks : 1;
+  static_assert(!SCALED || (BN_ == 256 && !PROMOTE_ && !PAIR_ && B_MN_MAJOR_),
+                "the tensor-core-scaled FP8 kernel is laid out for single CTAs and 256-column tiles");
   static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && !PAIR_ && N_CHUNKS < 2),
                 "a split gated tile needs two weight boxes");
   static_assert(!PAIR_ || BN_ == 256, "CTA pairs are laid out for 256-column tiles");
@@ -452,7 +467,11 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
       // the two warps that hold the same 32 rows (column groups 0 and 1) meet on their own barrier
       asm volatile("bar.sync %0, 64;" ::"r"(1 + ((threadIdx.x >> 5) & 3)) : "memory");
       amax = fmaxf(amax, xchg[(g ^ 1) * 128 + row]);
-      const float s = fmaxf(amax * (1.0f / 448.0f), 1.0f / (448.0f * 512.0f));
+      float s = fmaxf(amax * (1.0f / 448.0f), 1.0f / (448.0f * 512.0f));
+      if (p.pow2_scales) {  // next power of two: the consumer applies it inside the MMA
+        const uint32_t bits = __float_as_uint(s);
+        s = __uint_as_float(((bits & 0x007FFFFFu) ? bits + 0x00800000u : bits) & 0xFF800000u);
+      }
       const float inv_s = 1.0f / s;
       if (row_ok && col0 < half_n) {
         if (g == 0) p.d_scale[grow * (half_n / 128) + tc.n_tile] = s;
@@ -533,7 +552,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   __shared__ float xchg[2][C::XCHG];  // group-amax exchange of the quantising epilogue, by tile parity
-  __shared__ float sb_smem[2][2 * kMaxKBlocks];  // weight scales of the tile's two column blocks
+  __shared__ float sb_smem[2][C::SB_SMEM];  // weight scales of the tile's two column blocks
   __shared__ uint4 epi_buf[C::EPI_WARPS][128];   // per reader warp: 32 rows x 64 B for coalesced stores
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -547,7 +566,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&bars.full[s], 1);
+      mbar_init(&bars.full[s], C::SCALED ? 2 : 1);  // TMA bytes (+ the scale loader's arrival)
       mbar_init(&bars.empty[s], 1);
     }
     for (int b = 0; b < C::ACC_BUFS; ++b) {
@@ -600,10 +619,126 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
         }
       }
+    } else if (C::SCALED && warp == 1 && lane == 0) {
+      // ---------------- MMA issuer, scales applied by the tensor core ----------------
+      // Per stage: three 512-byte scale pieces (one for the 128 rows of A, two for the 256
+      // weight columns) are copied from shared to tensor memory, then four block-scaled MMAs
+      // of 32 of K each pick their byte of every scale word by its index.  One accumulation
+      // phase per tile.  The MMA issues of a stage are one straight-line block.
+      // The tensor pipe's queue is shallow and this one thread feeds it, with the 40 registers
+      // the producer warpgroup keeps: the low words of the descriptors are a base plus
+      // stage * constant, the high words are constants, and the loop is not unrolled (an
+      // unrolled version spills and measured half the speed).
+      uint8_t* sf_smem = tiles + C::STAGES * C::STAGE_BYTES;
+      const uint32_t a0 = smem_u32(tiles);
+      const uint32_t sw_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version, 128-byte swizzle
+      const uint32_t sf_hi = (128u >> 4) | (1u << 14);                // SBO 128, version, no swizzle
+      const uint32_t a_lo0 = ((a0 & 0x3FFFFu) >> 4) | ((16u >> 4) << 16);
+      const uint32_t b_lo0 = (((a0 + C::A_BYTES) & 0x3FFFFu) >> 4) | (((C::BK * kStageRowBytes) >> 4) << 16);
+      const uint32_t sf_lo0 = (smem_u32(sf_smem) & 0x3FFFFu) >> 4;
+      auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
+      const uint32_t sfa_t = tmem_base + kSfaCol, sfb_t = tmem_base + kSfbCol;
+      constexpr uint32_t kBStep = (C::UMMA_K * kStageRowBytes) >> 4;  // one 32-deep K slice of B
+      uint32_t stage = 0, phase = 0, buf_phase = 0;
+      bool ok = true;
+      for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
+        ok = mbar_wait(&bars.tempty[0], buf_phase ^ 1u, abort_p);  // the accumulator has been read out
+        if (!ok) break;
+        uint32_t accum = 0;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(&bars.full[stage], phase, abort_p);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t sf_lo = sf_lo0 + stage * (C::SF_BYTES >> 4);
+          const uint32_t a_lo = a_lo0 + stage * (C::STAGE_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + stage * (C::STAGE_BYTES >> 4);
+          tmem_cp_32x128b_x4(sfa_t, desc(sf_lo, sf_hi));
+          tmem_cp_32x128b_x4(sfb_t, desc(sf_lo + (kSfaBytes >> 4), sf_hi));
+          tmem_cp_32x128b_x4(sfb_t + 4, desc(sf_lo + ((kSfaBytes + 512) >> 4), sf_hi));
+          mma_mxf8f6f4(tmem_base, desc(a_lo, sw_hi), desc(b_lo, sw_hi),
+                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 0, 0), sfa_t, sfb_t, accum);
+          mma_mxf8f6f4(tmem_base, desc(a_lo + 2, sw_hi), desc(b_lo + kBStep, sw_hi),
+                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 1, 1), sfa_t, sfb_t, 1u);
+          mma_mxf8f6f4(tmem_base, desc(a_lo + 4, sw_hi), desc(b_lo + 2 * kBStep, sw_hi),
+                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 2, 2), sfa_t, sfb_t, 1u);
+          mma_mxf8f6f4(tmem_base, desc(a_lo + 6, sw_hi), desc(b_lo + 3 * kBStep, sw_hi),
+                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 3, 3), sfa_t, sfb_t, 1u);
+          accum = 1;
+          mma_commit(&bars.empty[stage]);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) mma_commit(&bars.tfull[0]);
+        buf_phase ^= 1u;
+      }
+    } else if (C::SCALED && warp == 2) {
+      // ---------------- scale loader (KIND_F8S) ----------------
+      // Per stage: the 128 activation scales of this K block (lane l owns rows l, 32+l, 64+l,
+      // 96+l: exactly the 16-byte piece the tensor-memory copy wants from it) and the two
+      // weight-block scales of the tile, each turned into its exponent byte and replicated
+      // over the four 32-element sub-blocks of the stage.  A scale that is not a power of two
+      // would be applied wrongly: it raises the device status word instead of passing silently.
+      uint8_t* sf_smem = tiles + C::STAGES * C::STAGE_BYTES;
+      const int nb_count = p.N / 128;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true, bad = false;
+      auto e8 = [&](float v) -> uint32_t {
+        const uint32_t bits = __float_as_uint(v);
+        if ((bits & 0x807FFFFFu) != 0u) bad = true;   // negative or mantissa bits set
+        return ((bits >> 23) & 0xFFu) * 0x01010101u;
+      };
+      for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
+        const TileCoord tc = decode_tile(sched, t);
+        int nb0 = problem_col<C>(tc.n_tile, 0, p.N) / 128;
+        int nb1 = problem_col<C>(tc.n_tile, 128, p.N) / 128;
+        nb0 = nb0 < nb_count ? nb0 : nb_count - 1;
+        nb1 = nb1 < nb_count ? nb1 : nb_count - 1;
+        const float* sb = p.b_scale + static_cast<int64_t>(tc.expert) * num_kb * nb_count;
+        // one base pointer and four small offsets (this warp runs on 40 registers)
+        const int64_t row0 = static_cast<int64_t>(tc.row_start) + lane;
+        const float* sa0 = p.a_scale + (row0 < p.R ? row0 : p.R - 1) * num_kb;
+        int off[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          int64_t row = row0 + c * 32;
+          if (row >= p.R) row = p.R - 1;  // rows past the end are never stored
+          off[c] = static_cast<int>((row - (row0 < p.R ? row0 : p.R - 1)) * num_kb);
+        }
+        float va[4], vb0, vb1;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) va[c] = sa0[off[c]];
+        vb0 = sb[nb0];
+        vb1 = sb[nb1];
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          const uint4 wa = make_uint4(e8(va[0]), e8(va[1]), e8(va[2]), e8(va[3]));
+          const uint32_t w0 = e8(vb0), w1 = e8(vb1);
+          if (kb + 1 < num_kb) {  // next stage's values are in flight while this one is handed over
+#pragma unroll
+            for (int c = 0; c < 4; ++c) va[c] = sa0[off[c] + kb + 1];
+            vb0 = sb[(kb + 1) * nb_count + nb0];
+            vb1 = sb[(kb + 1) * nb_count + nb1];
+          }
+          ok = mbar_wait(&bars.empty[stage], phase ^ 1u, abort_p);
+          if (!ok) break;
+          uint8_t* dst = sf_smem + stage * C::SF_BYTES;
+          *reinterpret_cast<uint4*>(dst + lane * 16) = wa;
+          *reinterpret_cast<uint4*>(dst + kSfaBytes + lane * 16) = make_uint4(w0, w0, w0, w0);
+          *reinterpret_cast<uint4*>(dst + kSfaBytes + 512 + lane * 16) = make_uint4(w1, w1, w1, w1);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars.full[stage]);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(&g_device_status, B200MOE_INVALID_ARG);
     } else if (warp == 1 && lane == 0 && rank == 0) {
       // ---------------- MMA issuer (the even CTA of a pair) ----------------
       const uint32_t idesc =
           make_idesc(p.ab_fmt, p.ab_fmt, 0u, C::B_MN_MAJOR ? 1u : 0u, C::TILE_M, C::BN);
+      const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version, 128-byte swizzle
+      const uint32_t a_lo0 = ((smem_u32(tiles) & 0x3FFFFu) >> 4) | ((16u >> 4) << 16);
+      const uint32_t b_lo0 = (((smem_u32(tiles) + C::A_BYTES) & 0x3FFFFu) >> 4) |
+                             (((C::B_MN_MAJOR ? C::BK * kStageRowBytes : 16) >> 4) << 16);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -630,16 +765,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
               if (!ok) break;
               tc_fence_after();
             }
-            const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
-            const uint32_t b_addr = a_addr + C::A_BYTES;
+            // descriptors: constant high words, low words = base + stage * constant (+ an
+            // immediate per K slice); this thread's scalar work between two MMAs is time the
+            // tensor pipe idles
+            const uint32_t a_lo = a_lo0 + stage * (C::STAGE_BYTES >> 4);
+            const uint32_t b_lo = b_lo0 + stage * (C::STAGE_BYTES >> 4);
 #pragma unroll
             for (int kk = 0; kk < C::BK / C::UMMA_K; ++kk) {
-              const uint64_t a_desc = make_sdesc_sw128(a_addr + kk * 32, 16, 1024);
-              const uint64_t b_desc =
-                  C::B_MN_MAJOR
-                      ? make_sdesc_sw128(b_addr + kk * C::UMMA_K * kStageRowBytes,
-                                         C::BK * kStageRowBytes, 1024)
-                      : make_sdesc_sw128(b_addr + kk * 32, 16, 1024);
+              const uint64_t a_desc = (static_cast<uint64_t>(desc_hi) << 32) | (a_lo + kk * 2);
+              const uint64_t b_desc = (static_cast<uint64_t>(desc_hi) << 32) |
+                                      (b_lo + kk * (C::B_MN_MAJOR ? ((C::UMMA_K * kStageRowBytes) >> 4) : 2));
               const uint32_t accum = (kb > 0 || kk > 0) ? 1u : 0u;
               if constexpr (C::PAIR) {
                 if (C::KIND == KIND_F16) mma_f16_pair(d_tmem, a_desc, b_desc, idesc, accum);
@@ -892,6 +1027,7 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   p.act_p0 = a.act_param0;
   p.act_p1 = a.act_param1;
   p.clamp = a.clamp_limit;
+  p.pow2_scales = a.scales_pow2;
   p.d_row_ptr = a.epilogue == B200MOE_EPI_STORE ? a.d_row_ptr : nullptr;
   p.ab_fmt = a.a_dtype == B200MOE_BF16 ? 1 : 0;  // kind::f16: 0 f16, 1 bf16; kind::f8f6f4: 0 e4m3
 
@@ -1159,6 +1295,15 @@ extern "C" int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspa
     if (!a.a_scale || !a.b_scale || a.K % 128 || a.N % 128) return B200MOE_INVALID_ARG;
     if (a.K / 128 > kMaxKBlocks) return B200MOE_UNSUPPORTED;
     if (a.epilogue == B200MOE_EPI_SILU_MUL && (a.N / 2) % 128 != 0) return B200MOE_UNSUPPORTED;
+    if (a.scales_pow2) {
+      // power-of-two scales: the tensor core applies them, one accumulation phase per tile
+      if (a.epilogue == B200MOE_EPI_SWIGLU_OAI) return B200MOE_UNSUPPORTED;
+      if (a.epilogue == B200MOE_EPI_STORE)
+        return launch_config<Config<KIND_F8S, true, false, 256, B200MOE_EPI_STORE, 4>>(a, a.B, B200MOE_E4M3, st);
+      if (gated_any(a))
+        return launch_config<Config<KIND_F8S, true, false, 256, kEpiGatedAny, 4>>(a, a.B, B200MOE_E4M3, st);
+      return launch_config<Config<KIND_F8S, true, false, 256, B200MOE_EPI_SILU_MUL, 4>>(a, a.B, B200MOE_E4M3, st);
+    }
     if (pair) return launch_epi<KIND_F8, true, true, 256, 6, true>(a, a.B, B200MOE_E4M3, st);
     if (wide || a.epilogue == B200MOE_EPI_SILU_MUL)
       return launch_epi<KIND_F8, true, true, 256, 4>(a, a.B, B200MOE_E4M3, st);

@@ -608,7 +608,7 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
                          const OptTensor& D_scale = std::nullopt,
                          const OptTensor& D_row_ptr = std::nullopt, int64_t a_scale_layout = 0,
                          int64_t gated_act = 0, double act_param0 = 0.0, double act_param1 = 0.0,
-                         double clamp_limit = 0.0) {
+                         double clamp_limit = 0.0, bool scales_pow2 = false) {
   const char* op = "cutlass_grouped_gemm_interface";
   TORCH_CHECK(A.is_contiguous() && B.is_contiguous() && D.is_contiguous(), op, ": A, B and D must be contiguous");
   TORCH_CHECK(rows_per_expert.scalar_type() == at::kInt && rows_per_expert.is_contiguous() &&
@@ -648,6 +648,7 @@ Tensor grouped_gemm_impl(const Tensor& A, const OptTensor& A_scale, const Tensor
   a.act_param0 = static_cast<float>(act_param0);
   a.act_param1 = static_cast<float>(act_param1);
   a.clamp_limit = static_cast<float>(clamp_limit);
+  a.scales_pow2 = scales_pow2 ? 1 : 0;
   const auto bt = B.scalar_type();
   if (bt == at::kFloat8_e4m3fn && !B_scale.has_value() && !A_scale.has_value() &&
       a.a_dtype == B200MOE_E4M3) {
@@ -714,10 +715,10 @@ Tensor b200_grouped_gemm(const Tensor& A, const OptTensor& A_scale, const Tensor
                          int64_t epilogue, int64_t b_layout, double alpha, double limit,
                          const OptTensor& D_scale, const OptTensor& D_row_ptr,
                          int64_t a_scale_layout, int64_t gated_act, double act_param0,
-                         double act_param1, double clamp_limit) {
+                         double act_param1, double clamp_limit, bool scales_pow2) {
   return grouped_gemm_impl(A, A_scale, B, B_scale, bias, D, rows_per_expert, N, K, num_experts,
                            epilogue, b_layout, alpha, limit, D_scale, D_row_ptr, a_scale_layout,
-                           gated_act, act_param0, act_param1, clamp_limit);
+                           gated_act, act_param0, act_param1, clamp_limit, scales_pow2);
 }
 
 Tensor b200_grouped_gemm_check(const Tensor& A, const OptTensor& A_scale, const Tensor& B,
@@ -1027,7 +1028,7 @@ TORCH_LIBRARY(B200MOE_NS_XPU_C, m) {
       "Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int epilogue, int "
       "b_layout, float alpha=1.702, float limit=7.0, Tensor? D_scale=None, Tensor? D_row_ptr=None, int "
       "a_scale_layout=0, int gated_act=0, float act_param0=0.0, float act_param1=0.0, float "
-      "clamp_limit=0.0) -> Tensor");
+      "clamp_limit=0.0, bool scales_pow2=False) -> Tensor");
   m.def(
       "b200_grouped_gemm_check(Tensor A, Tensor? A_scale, Tensor B, Tensor? B_scale, Tensor? "
       "bias, Tensor D, Tensor rows_per_expert, int N, int K, int num_experts, int b_layout) -> "

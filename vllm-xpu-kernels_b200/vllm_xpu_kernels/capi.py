@@ -25,7 +25,7 @@ class GemmArgs(Structure):
         ("d_scale", c_void_p), ("rows_per_expert", c_void_p), ("R", c_int64), ("N", c_int),
         ("K", c_int), ("E", c_int), ("alpha", c_float), ("limit", c_float), ("d_row_ptr", c_void_p),
         ("a_scale_layout", c_int), ("gated_act", c_int), ("act_param0", c_float),
-        ("act_param1", c_float), ("clamp_limit", c_float),
+        ("act_param1", c_float), ("clamp_limit", c_float), ("scales_pow2", c_int),
     ]
 
 

@@ -143,6 +143,18 @@ class XpuFusedMoe:
         self.w13, self.w2 = w13, w2
         self.gemm1_wei_scales = w13_scales if self.recipe != "bf16" else None
         self.gemm2_wei_scales = w2_scales if self.recipe != "bf16" else None
+        # Block-FP8 weights whose 128x128 scales are all exact powers of two (UE8M0-scaled
+        # checkpoints) take the kernel that lets the tensor core apply the scales; the layer then
+        # also quantises its activations with power-of-two scales.  Checked once, here (one
+        # host read).  B200MOE_FP8_PROMOTE=1 keeps the general kernel.
+        self.act_scales_pow2 = False
+        if self.is_block_fp8 and not os.environ.get("B200MOE_FP8_PROMOTE"):
+            def _pow2(t):
+                m, _ = torch.frexp(t.float())
+                return bool(((m == 0.5) & (t > 0)).all().item())
+            H_, I2_ = w13.shape[-2], w13.shape[-1]
+            self.act_scales_pow2 = (H_ % 128 == 0 and (I2_ // 2) % 128 == 0
+                                    and _pow2(w13_scales) and _pow2(w2_scales))
         # W8A16 / W4A16 recipes: widened once per activation dtype, on first use
         self._expanded = {}
         self.w13_bias, self.w2_bias = w13_bias, w2_bias
@@ -249,7 +261,7 @@ class XpuFusedMoe:
         if self.is_block_fp8 and a1q_scale is None:
             # dynamic per-token-group-128 quantisation, once per token (not per routed row)
             from .moe_utils import quant_fp8_block_act
-            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states)
+            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states, self.act_scales_pow2)
         if self._mx_native:
             if a1q_scale is None:
                 hidden_states, a1q_scale = torch.ops._xpu_C.b200_quant_mxfp8(hidden_states)
@@ -295,7 +307,7 @@ class XpuFusedMoe:
         T = hidden_states.shape[0]
         if self.is_block_fp8 and a1q_scale is None:
             from .moe_utils import quant_fp8_block_act
-            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states)
+            hidden_states, a1q_scale = quant_fp8_block_act(hidden_states, self.act_scales_pow2)
         elif self._mx_native and a1q_scale is None:
             hidden_states, a1q_scale = torch.ops._xpu_C.b200_quant_mxfp8(hidden_states)
         rows = getattr(self, "_dense_rows", None)
@@ -324,6 +336,7 @@ class XpuFusedMoe:
             return self._run_experts_mx(rows, row_scales, rows_per_expert, out_dtype, out, oai, clamp)
         if self.is_block_fp8:
             K2 = I * self.inter_size_scale
+            pow2 = self.act_scales_pow2
             fused = self._fused_gated(clamp)
             if (fused is not None and I % 128 == 0 and not os.environ.get("B200MOE_UNFUSED_ACT")):
                 # activation * up (with the layer's clamp) and the group-128 re-quantisation run
@@ -333,27 +346,28 @@ class XpuFusedMoe:
                 with self._stage("gemm1"):
                     gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
                          act_q, rows_per_expert, 2 * I, hidden_size, E, EPI_SILU_MUL, B_LAYOUT_KN,
-                         1.702, 7.0, act_s, None, 0, *fused)
+                         1.702, 7.0, act_s, None, 0, *fused, pow2)
             else:
                 gemm1_out = torch.empty((R, 2 * I), dtype=out_dtype, device=dev)
                 with self._stage("gemm1"):
                     gemm(remapped, remapped_scales, self.w13, self.gemm1_wei_scales, self.w13_bias,
-                         gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN)
+                         gemm1_out, rows_per_expert, 2 * I, hidden_size, E, EPI_STORE, B_LAYOUT_KN,
+                         1.702, 7.0, None, None, 0, 0, 0.0, 0.0, 0.0, pow2)
                 act_q = torch.empty((R, K2), dtype=torch.float8_e4m3fn, device=dev)
                 act_s = torch.empty((R, K2 // 128), dtype=torch.float32, device=dev)
                 with self._stage("act_quant"):
-                    if self.activation == "silu" and not clamp:
+                    if self.activation == "silu" and not clamp and not pow2:
                         torch.ops._C.silu_and_mul_per_block_quant(act_q, gemm1_out, act_s, 128)
                     else:
                         act = self._activate(gemm1_out)
                         torch.ops._C.per_token_group_fp8_quant(act, act_q, act_s, 128, 1e-10, -448.0,
-                                                               448.0, False, False, False)
+                                                               448.0, pow2, False, False)
             gemm2_out = out if out is not None else torch.empty(
                 (R if row_ptr is None else 1, hidden_size), dtype=out_dtype, device=dev)
             with self._stage("gemm2"):
                 gemm(act_q, act_s, self.w2, self.gemm2_wei_scales, self.w2_bias, gemm2_out,
                      rows_per_expert, hidden_size, K2, E, EPI_STORE, B_LAYOUT_KN, 1.702, 7.0, None,
-                     row_ptr)
+                     row_ptr, 0, 0, 0.0, 0.0, 0.0, pow2 and K2 % 128 == 0)
         else:
             w13, w2, layout = self._weights_16(out_dtype)
             K2 = I * self.inter_size_scale

@@ -48,12 +48,15 @@ def dequant_fp8_block_act(x_lp, x_scale):
     return (x * x_scale.unsqueeze(-1)).reshape(shape)
 
 
-def quant_fp8_block_act(x: torch.Tensor):
-    """Per-token-group-128 FP8 quantisation -> (e4m3 [M, K], f32 [M, K/128])."""
+def quant_fp8_block_act(x: torch.Tensor, pow2_scales: bool = False):
+    """Per-token-group-128 FP8 quantisation -> (e4m3 [M, K], f32 [M, K/128]).  With
+    ``pow2_scales`` every scale is rounded up to a power of two (the operator's scale_ue8m0
+    flag), which is what a layer whose weight scales are powers of two wants
+    (``XpuFusedMoe.act_scales_pow2``)."""
     x_q = torch.empty(x.shape, device=x.device, dtype=torch.float8_e4m3fn)
     x_s = torch.empty(x.shape[:-1] + (x.shape[-1] // 128,), device=x.device, dtype=torch.float32)
     torch.ops._C.per_token_group_fp8_quant(x, x_q, x_s, 128, 1e-10, FP8_E4M3_MIN, FP8_E4M3_MAX,
-                                           False, False, False)
+                                           bool(pow2_scales), False, False)
     return x_q, x_s
 
 
