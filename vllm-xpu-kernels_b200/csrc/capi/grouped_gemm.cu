@@ -52,8 +52,9 @@ constexpr int kMaxKBlocks = 160;  // K <= 20480 for the FP8 block-scaled recipe
 // 128x128 block for B), applied by the tensor core itself (kind::mxf8f6f4.block_scale, UE8M0
 // factors in tensor memory): one accumulation phase per tile, no promotion in registers.
 enum : int { KIND_F16 = 0, KIND_F8 = 1, KIND_F8S = 2 };
-constexpr int kSfaBytes = 512;    // per stage: one scale word (4 x e8m0) per row of the A tile
-constexpr int kSfbBytes = 1024;   // per stage: the same for the 256 weight columns of the tile
+constexpr int kSfaBytes = 512;    // per group of four K blocks: one scale word (4 x e8m0) per row of the A tile
+constexpr int kSfbBytes = 1024;   // ... and per weight column of the tile (256)
+constexpr int kSfGroupBytes = kSfaBytes + kSfbBytes;
 constexpr int kSfaCol = 256;      // tensor-memory columns of the scale words (KIND_F8S: one
 constexpr int kSfbCol = 260;      //   256-column accumulator at column 0)
 
@@ -279,7 +280,7 @@ struct Config {
   // tensor-memory accumulator ring: all 512 columns, or one 256-column buffer next to the
   // scale columns (the accumulator then leaves tensor memory once per tile, at its end)
   static constexpr int ACC_BUFS = SCALED ? 1 : 512 / BN;
-  static constexpr int SF_BYTES = SCALED ? kSfaBytes + kSfbBytes : 0;   // per stage, after the operand ring
+  static constexpr int SF_BYTES = SCALED ? 2 * kSfGroupBytes : 0;   // two scale groups after the operand ring
   static constexpr int TMEM_COLS = 512;
   static constexpr int EPI_WARPS = 8;                    // two reader warps per TMEM lane quadrant
   static constexpr int THREADS = 128 + EPI_WARPS * 32;   // warps 0..3: producer, MMA, 2 spare
@@ -291,7 +292,7 @@ struct Config {
   // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
   static constexpr bool REBALANCE_REGS = BN == 256;
   static constexpr int XCHG = (EPI_ == B200MOE_EPI_SILU_MUL || EPI_ == kEpiGatedAny) ? 256 : 1;
-  static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * (STAGE_BYTES + SF_BYTES);
+  static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + SF_BYTES;
   static constexpr int SB_SMEM = PROMOTE_ ? 2 * kMaxKBlocks : 1;
   static_assert(!SCALED || (BN_ == 256 && !PROMOTE_ && !PAIR_ && B_MN_MAJOR_),
                 "the tensor-core-scaled FP8 kernel is laid out for single CTAs and 256-column tiles");
@@ -308,6 +309,8 @@ struct alignas(8) Barriers {
   uint64_t tfull[4];
   uint64_t tempty[4];
   uint64_t sready;  // this tile's staged scales are in shared memory (one arrival per reader warp)
+  uint64_t sffull[2];   // KIND_F8S: a group of scale words is in shared memory / has been copied
+  uint64_t sfempty[2];  //           to tensor memory
 };
 
 // Tensor-memory column (inside one accumulator buffer) of chunk c of a reader
@@ -566,7 +569,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < C::STAGES; ++s) {
-      mbar_init(&bars.full[s], C::SCALED ? 2 : 1);  // TMA bytes (+ the scale loader's arrival)
+      mbar_init(&bars.full[s], 1);
       mbar_init(&bars.empty[s], 1);
     }
     for (int b = 0; b < C::ACC_BUFS; ++b) {
@@ -574,6 +577,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(&bars.tempty[b], C::EPI_WARPS * (C::PAIR ? 2 : 1));  // both CTAs' readers
     }
     mbar_init(&bars.sready, C::EPI_WARPS);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars.sffull[b], 1);
+      mbar_init(&bars.sfempty[b], 1);
+    }
     mbar_fence_init();
     prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -621,14 +628,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     } else if (C::SCALED && warp == 1 && lane == 0) {
       // ---------------- MMA issuer, scales applied by the tensor core ----------------
-      // Per stage: three 512-byte scale pieces (one for the 128 rows of A, two for the 256
-      // weight columns) are copied from shared to tensor memory, then four block-scaled MMAs
-      // of 32 of K each pick their byte of every scale word by its index.  One accumulation
-      // phase per tile.  The MMA issues of a stage are one straight-line block.
+      // A scale word in tensor memory holds four e8m0 bytes per row, and an MMA picks one of
+      // them by an index in its instruction descriptor.  A 128-block scale is the same for the
+      // four 32-deep MMAs of a stage, so the four bytes of a word carry FOUR K BLOCKS: the
+      // three 512-byte pieces (rows of A, the two 128-column halves of the weight tile) are
+      // copied from shared to tensor memory once per group of four stages, and the MMAs of
+      // stage j of the group all use byte j.  One accumulation phase per tile.
       // The tensor pipe's queue is shallow and this one thread feeds it, with the 40 registers
-      // the producer warpgroup keeps: the low words of the descriptors are a base plus
-      // stage * constant, the high words are constants, and the loop is not unrolled (an
-      // unrolled version spills and measured half the speed).
+      // the producer warpgroup keeps: descriptor low words are base + stage * constant, high
+      // words constants, and the loop is not unrolled (an unrolled version spills and measured
+      // half the speed).
       uint8_t* sf_smem = tiles + C::STAGES * C::STAGE_BYTES;
       const uint32_t a0 = smem_u32(tiles);
       const uint32_t sw_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version, 128-byte swizzle
@@ -639,30 +648,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       auto desc = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
       const uint32_t sfa_t = tmem_base + kSfaCol, sfb_t = tmem_base + kSfbCol;
       constexpr uint32_t kBStep = (C::UMMA_K * kStageRowBytes) >> 4;  // one 32-deep K slice of B
-      uint32_t stage = 0, phase = 0, buf_phase = 0;
+      const uint32_t idesc0 = make_idesc_mx(0u, 0u, 1u, BM, C::BN, 0, 0);
+      uint32_t stage = 0, phase = 0, buf_phase = 0, group = 0;
       bool ok = true;
       for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
         ok = mbar_wait(&bars.tempty[0], buf_phase ^ 1u, abort_p);  // the accumulator has been read out
         if (!ok) break;
         uint32_t accum = 0;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
+          const uint32_t j = static_cast<uint32_t>(kb) & 3u;
+          if (j == 0) {  // next group of scale words: shared -> tensor memory
+            const uint32_t g = group & 1u;
+            ok = mbar_wait(&bars.sffull[g], (group >> 1) & 1u, abort_p);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sf_lo = sf_lo0 + g * (kSfGroupBytes >> 4);
+            tmem_cp_32x128b_x4(sfa_t, desc(sf_lo, sf_hi));
+            tmem_cp_32x128b_x4(sfb_t, desc(sf_lo + (kSfaBytes >> 4), sf_hi));
+            tmem_cp_32x128b_x4(sfb_t + 4, desc(sf_lo + ((kSfaBytes + 512) >> 4), sf_hi));
+            mma_commit(&bars.sfempty[g]);  // the loader may refill once the copies are done
+            ++group;
+          }
           ok = mbar_wait(&bars.full[stage], phase, abort_p);
           if (!ok) break;
           tc_fence_after();
-          const uint32_t sf_lo = sf_lo0 + stage * (C::SF_BYTES >> 4);
           const uint32_t a_lo = a_lo0 + stage * (C::STAGE_BYTES >> 4);
           const uint32_t b_lo = b_lo0 + stage * (C::STAGE_BYTES >> 4);
-          tmem_cp_32x128b_x4(sfa_t, desc(sf_lo, sf_hi));
-          tmem_cp_32x128b_x4(sfb_t, desc(sf_lo + (kSfaBytes >> 4), sf_hi));
-          tmem_cp_32x128b_x4(sfb_t + 4, desc(sf_lo + ((kSfaBytes + 512) >> 4), sf_hi));
-          mma_mxf8f6f4(tmem_base, desc(a_lo, sw_hi), desc(b_lo, sw_hi),
-                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 0, 0), sfa_t, sfb_t, accum);
-          mma_mxf8f6f4(tmem_base, desc(a_lo + 2, sw_hi), desc(b_lo + kBStep, sw_hi),
-                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 1, 1), sfa_t, sfb_t, 1u);
-          mma_mxf8f6f4(tmem_base, desc(a_lo + 4, sw_hi), desc(b_lo + 2 * kBStep, sw_hi),
-                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 2, 2), sfa_t, sfb_t, 1u);
-          mma_mxf8f6f4(tmem_base, desc(a_lo + 6, sw_hi), desc(b_lo + 3 * kBStep, sw_hi),
-                       make_idesc_mx(0u, 0u, 1u, BM, C::BN, 3, 3), sfa_t, sfb_t, 1u);
+          const uint32_t idesc = idesc0 | (j << 4) | (j << 29);  // scale byte j for A and for B
+          mma_mxf8f6f4(tmem_base, desc(a_lo, sw_hi), desc(b_lo, sw_hi), idesc, sfa_t, sfb_t, accum);
+          mma_mxf8f6f4(tmem_base, desc(a_lo + 2, sw_hi), desc(b_lo + kBStep, sw_hi), idesc, sfa_t, sfb_t, 1u);
+          mma_mxf8f6f4(tmem_base, desc(a_lo + 4, sw_hi), desc(b_lo + 2 * kBStep, sw_hi), idesc, sfa_t, sfb_t, 1u);
+          mma_mxf8f6f4(tmem_base, desc(a_lo + 6, sw_hi), desc(b_lo + 3 * kBStep, sw_hi), idesc, sfa_t, sfb_t, 1u);
           accum = 1;
           mma_commit(&bars.empty[stage]);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -672,21 +688,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       }
     } else if (C::SCALED && warp == 2) {
       // ---------------- scale loader (KIND_F8S) ----------------
-      // Per stage: the 128 activation scales of this K block (lane l owns rows l, 32+l, 64+l,
-      // 96+l: exactly the 16-byte piece the tensor-memory copy wants from it) and the two
-      // weight-block scales of the tile, each turned into its exponent byte and replicated
-      // over the four 32-element sub-blocks of the stage.  A scale that is not a power of two
-      // would be applied wrongly: it raises the device status word instead of passing silently.
+      // Per group of four K blocks: the activation scales of the tile's 128 rows (lane l owns
+      // rows l, 32+l, 64+l, 96+l: exactly the 16-byte piece the tensor-memory copy wants from
+      // it; four K blocks of a row are one 16-byte load) and the weight-block scales of the
+      // tile's two column halves, each turned into its exponent byte, byte j of a word = K
+      // block j of the group.  A scale that is not a power of two would be applied wrongly:
+      // it raises the device status word instead of passing silently.
       uint8_t* sf_smem = tiles + C::STAGES * C::STAGE_BYTES;
       const int nb_count = p.N / 128;
-      int stage = 0;
-      uint32_t phase = 0;
+      const int groups = (num_kb + 3) / 4;
+      const bool vec = (num_kb & 3) == 0;
+      uint32_t group = 0;
       bool ok = true, bad = false;
       auto e8 = [&](float v) -> uint32_t {
         const uint32_t bits = __float_as_uint(v);
         if ((bits & 0x807FFFFFu) != 0u) bad = true;   // negative or mantissa bits set
-        return ((bits >> 23) & 0xFFu) * 0x01010101u;
+        return (bits >> 23) & 0xFFu;
       };
+      auto word = [&](const float4& v) { return e8(v.x) | (e8(v.y) << 8) | (e8(v.z) << 16) | (e8(v.w) << 24); };
       for (int t = sched_id; t < num_tiles && ok; t += sched_stride) {
         const TileCoord tc = decode_tile(sched, t);
         int nb0 = problem_col<C>(tc.n_tile, 0, p.N) / 128;
@@ -696,38 +715,51 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         const float* sb = p.b_scale + static_cast<int64_t>(tc.expert) * num_kb * nb_count;
         // one base pointer and four small offsets (this warp runs on 40 registers)
         const int64_t row0 = static_cast<int64_t>(tc.row_start) + lane;
-        const float* sa0 = p.a_scale + (row0 < p.R ? row0 : p.R - 1) * num_kb;
+        const int64_t base_row = row0 < p.R ? row0 : p.R - 1;
+        const float* sa0 = p.a_scale + base_row * num_kb;
         int off[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           int64_t row = row0 + c * 32;
           if (row >= p.R) row = p.R - 1;  // rows past the end are never stored
-          off[c] = static_cast<int>((row - (row0 < p.R ? row0 : p.R - 1)) * num_kb);
+          off[c] = static_cast<int>((row - base_row) * num_kb);
         }
-        float va[4], vb0, vb1;
+        for (int grp = 0; grp < groups && ok; ++grp) {
+          const int kb0 = grp * 4;
+          uint4 wa;
+          uint32_t* wp = reinterpret_cast<uint32_t*>(&wa);
 #pragma unroll
-        for (int c = 0; c < 4; ++c) va[c] = sa0[off[c]];
-        vb0 = sb[nb0];
-        vb1 = sb[nb1];
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
-          const uint4 wa = make_uint4(e8(va[0]), e8(va[1]), e8(va[2]), e8(va[3]));
-          const uint32_t w0 = e8(vb0), w1 = e8(vb1);
-          if (kb + 1 < num_kb) {  // next stage's values are in flight while this one is handed over
-#pragma unroll
-            for (int c = 0; c < 4; ++c) va[c] = sa0[off[c] + kb + 1];
-            vb0 = sb[(kb + 1) * nb_count + nb0];
-            vb1 = sb[(kb + 1) * nb_count + nb1];
+          for (int c = 0; c < 4; ++c) {
+            float4 v = make_float4(1.f, 1.f, 1.f, 1.f);
+            const float* src = sa0 + off[c] + kb0;
+            if (vec) {
+              v = *reinterpret_cast<const float4*>(src);
+            } else {
+              v.x = src[0];
+              if (kb0 + 1 < num_kb) v.y = src[1];
+              if (kb0 + 2 < num_kb) v.z = src[2];
+              if (kb0 + 3 < num_kb) v.w = src[3];
+            }
+            wp[c] = word(v);
           }
-          ok = mbar_wait(&bars.empty[stage], phase ^ 1u, abort_p);
+          float4 b0 = make_float4(1.f, 1.f, 1.f, 1.f), b1 = b0;
+          b0.x = sb[kb0 * nb_count + nb0];
+          b1.x = sb[kb0 * nb_count + nb1];
+          if (kb0 + 1 < num_kb) { b0.y = sb[(kb0 + 1) * nb_count + nb0]; b1.y = sb[(kb0 + 1) * nb_count + nb1]; }
+          if (kb0 + 2 < num_kb) { b0.z = sb[(kb0 + 2) * nb_count + nb0]; b1.z = sb[(kb0 + 2) * nb_count + nb1]; }
+          if (kb0 + 3 < num_kb) { b0.w = sb[(kb0 + 3) * nb_count + nb0]; b1.w = sb[(kb0 + 3) * nb_count + nb1]; }
+          const uint32_t w0 = word(b0), w1 = word(b1);
+          const uint32_t g = group & 1u;
+          ok = mbar_wait(&bars.sfempty[g], ((group >> 1) & 1u) ^ 1u, abort_p);
           if (!ok) break;
-          uint8_t* dst = sf_smem + stage * C::SF_BYTES;
+          uint8_t* dst = sf_smem + g * kSfGroupBytes;
           *reinterpret_cast<uint4*>(dst + lane * 16) = wa;
           *reinterpret_cast<uint4*>(dst + kSfaBytes + lane * 16) = make_uint4(w0, w0, w0, w0);
           *reinterpret_cast<uint4*>(dst + kSfaBytes + 512 + lane * 16) = make_uint4(w1, w1, w1, w1);
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&bars.full[stage]);
-          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          if (lane == 0) mbar_arrive(&bars.sffull[g]);
+          ++group;
         }
       }
       if (__any_sync(0xffffffffu, bad) && lane == 0) atomicExch(&g_device_status, B200MOE_INVALID_ARG);
