@@ -894,10 +894,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         ok = mbar_wait(&bars.sready, static_cast<uint32_t>(tile_parity), abort_p);
         if (!ok) break;
       }
-      // first two loads of the tile
       ok = mbar_wait(&bars.tfull[buf], buf_phase, abort_p);
       if (!ok) break;
       tc_fence_after();
+      if constexpr (!C::PROMOTE) {
+        // One accumulation phase per tile: the finished accumulator goes straight into the
+        // registers the epilogue works on, every chunk in flight at once, and the buffer is
+        // handed back after a single round trip.
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+          tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, c),
+                        *reinterpret_cast<float(*)[32]>(acc + c * 32));
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) tmem_ld_wait_on(*reinterpret_cast<float(*)[32]>(acc + c * 32));
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (C::PAIR) mbar_arrive_cluster(&bars.tempty[buf], 0);
+          else mbar_arrive(&bars.tempty[buf]);
+        }
+        if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
+        tile_epilogue<C>(p, tc, g, row_ok, grow, acc, xchg[tile_parity], epi_buf[ew]);
+        continue;
+      }
+      // first two loads of the tile
       tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 0), ta);
       tmem_ld_32x32(tmem_base + lane_addr + buf * C::BN + chunk_tmem_col<C>(g, 1), tb);
 
