@@ -707,6 +707,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling, sweeps)")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count (profiling)")
     ap.add_argument("--skew", action="store_true", help="Zipf-like expert load (decode sweep)")
+    ap.add_argument("--pow2-scales", action="store_true",
+                    help="block-FP8 weights with power-of-two block scales (the c3_pow2_scales variant as the main run)")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config], key=args.config)
     if args.skew:
@@ -715,6 +717,9 @@ def main():
         cfg["T"] = args.tokens
     if args.experts:
         cfg["E"] = args.experts
+    if args.pow2_scales:
+        cfg["pow2_scales"] = True
+        cfg["name"] = cfg["name"] + "; block scales powers of two"
     if args.impl == "reference":
         return run_reference(args, cfg)
 
@@ -746,7 +751,7 @@ def main():
         # experts live on all ranks; rank 0 rebuilds the ones they hit from the per-expert seeds)
         parity = parity_check(cfg, res["layer"], res["x_host"], res["logits_host"], res["out"], dev)
         peaks = load_peaks()
-        modified = bool(args.tokens or args.experts or args.skew)
+        modified = bool(args.tokens or args.experts or args.skew or args.pow2_scales)
         roof = tensor_roofline(cfg, res, peaks, T)
         if modified:
             roof["traffic"] = None
