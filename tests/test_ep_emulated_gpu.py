@@ -286,3 +286,119 @@ def test_bounded_gather_leaves_rows_past_the_count_alone(ops):
     ops._moe_C.moe_gather(ref, y, w, rm, 1)
     ops._moe_C.b200_moe_gather_bounded(out, y, w, rm, torch.tensor([25], dtype=torch.int32, device=DEV))
     assert torch.equal(out[:25], ref[:25]) and (out[25:] == 5.0).all()
+
+
+# ---- the token-level exchange end to end, ranks emulated one after the other ------------------
+@pytest.mark.parametrize("G,E_loc,T,k,recipe", [(2, 4, 40, 2, "bf16"), (4, 2, 33, 3, "bf16"),
+                                                 (2, 4, 48, 2, "fp8block"), (8, 1, 20, 4, "fp8block")])
+def test_token_level_exchange_with_emulated_ranks(ops, G, E_loc, T, k, recipe):
+    """Every step of TokenExpertParallel.apply with the ranks' launches run one after the other
+    on one GPU (none of the kernels waits on another rank): which ranks a token hits, one row
+    per (token, rank) to its owner, the owner's ordinary layer on what arrived (ids made
+    local, rows past the count masked), one partial sum per (token, rank) pulled back.  The
+    result of every rank's tokens is compared with the oracle for the whole layer."""
+    from oracle import moe_oracle as O
+    from vllm_xpu_kernels import capi
+    from vllm_xpu_kernels.fused_moe_interface import XpuFusedMoe
+    from vllm_xpu_kernels.moe_utils import quant_fp8_block_act
+    lib = capi.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    E, H, I = G * E_loc, 256, 256
+    cfg = dict(T=T, H=H, I=I, E=E, k=k, recipe=recipe, routing="softmax", activation="silu", bias=False)
+    layer = O.make_layer(cfg, seed=3)
+    fp8 = recipe == "fp8block"
+    row_bytes, scale_bytes = H * (1 if fp8 else 2), (H // 128) * 4 if fp8 else 0
+    cap, side_w = G * T, (2 * k + 3) // 4 * 4
+
+    def ok(rc):
+        assert rc == 0, (capi.status_string(rc), lib.b200moe_last_error().decode())
+
+    class R:
+        pass
+    ranks = []
+    for r in range(G):
+        rk = R()
+        rk.r = r
+        tok = O.make_layer(cfg, seed=100 + r, E_limit=1)
+        rk.x_host, rk.logits = tok["x"], tok["logits"]
+        rk.w_host, rk.ids_host = O.topk_softmax(rk.logits, k, True)
+        rk.ids = rk.ids_host.to(torch.int32).to(DEV)
+        rk.w = rk.w_host.to(DEV)
+        x = rk.x_host.to(DEV)
+        rk.x, rk.scales = quant_fp8_block_act(x) if fp8 else (x, None)
+        sl = slice(r * E_loc, (r + 1) * E_loc)
+        d = lambda t: None if t is None else t[sl].to(DEV)  # noqa: E731
+        rk.moe = XpuFusedMoe(d(layer["w13"]), d(layer["w13_scale"]), None, d(layer["w2"]), d(layer["w2_scale"]),
+                             None, k, "silu", E_loc)
+        off = 0
+        rk.off_counts = off; off = _align(off + G * G * 4)
+        rk.off_rows = off; off = _align(off + cap * row_bytes)
+        rk.off_scales = off; off = _align(off + cap * max(scale_bytes, 4))
+        rk.off_meta = off; off = _align(off + cap * 8)
+        rk.off_side = off; off = _align(off + cap * side_w * 4)
+        rk.off_out = off; off = _align(off + cap * H * 2)
+        rk.buf = torch.zeros(off, dtype=torch.uint8, device=DEV)
+        rk.buf[rk.off_side: rk.off_side + cap * side_w * 4].view(torch.int32).fill_(1)   # stale rows route to expert 1
+        i32 = dict(dtype=torch.int32, device=DEV)
+        rk.hits = torch.empty(T, G, **i32)
+        rk.send_counts = torch.zeros(G, **i32)
+        rk.row_map = torch.empty(T, G, **i32)
+        rk.side = torch.zeros(T, side_w, **i32)
+        rk.my_prefix, rk.dst_start = torch.zeros(G + 1, **i32), torch.zeros(G, **i32)
+        rk.tokens_in, rk.recv_total = torch.zeros(1, **i32), torch.zeros(1, **i32)
+        ranks.append(rk)
+    bases = (ctypes.c_int64 * G)(*[rk.buf.data_ptr() for rk in ranks])
+    ws = torch.empty(max(lib.b200moe_remap_hidden_states_workspace_bytes(T, G, G), 16), dtype=torch.uint8, device=DEV)
+    for rk in ranks:
+        ok(lib.b200moe_ep_rank_hits(rk.ids.data_ptr(), I32, T, k, E_loc, G, rk.hits.data_ptr(), st))
+        ok(lib.b200moe_remap_hidden_states(None, None, None, None, row_bytes, scale_bytes, rk.hits.data_ptr(), I32,
+                                           None, T, G, G, G, rk.send_counts.data_ptr(), rk.row_map.data_ptr(),
+                                           ws.data_ptr(), ws.numel(), st))
+        ok(lib.b200moe_ep_pack_routing(rk.ids.data_ptr(), I32, rk.w.data_ptr(), T, k, side_w, rk.side.data_ptr(), st))
+        ok(lib.b200moe_ep_put_counts(rk.send_counts.data_ptr(), G, bases, rk.off_counts, rk.r, G, st))
+    for rk in ranks:
+        counts = rk.buf[rk.off_counts: rk.off_counts + G * G * 4].view(torch.int32)
+        ok(lib.b200moe_ep_offsets(counts.data_ptr(), rk.r, G, 1, rk.my_prefix.data_ptr(), rk.dst_start.data_ptr(),
+                                  rk.tokens_in.data_ptr(), rk.recv_total.data_ptr(), st))
+        ok(lib.b200moe_ep_dispatch(rk.x.data_ptr(), rk.scales.data_ptr() if fp8 else None, row_bytes, scale_bytes,
+                                   rk.hits.data_ptr(), I32, rk.row_map.data_ptr(), T, G, rk.r, G, 1,
+                                   rk.my_prefix.data_ptr(), rk.dst_start.data_ptr(), bases, rk.off_rows,
+                                   rk.off_scales, rk.off_meta, cap, st))
+        ok(lib.b200moe_ep_dispatch(rk.side.data_ptr(), None, side_w * 4, 0, rk.hits.data_ptr(), I32,
+                                   rk.row_map.data_ptr(), T, G, rk.r, G, 1, rk.my_prefix.data_ptr(),
+                                   rk.dst_start.data_ptr(), bases, rk.off_side, 0, rk.off_meta, cap, st))
+    torch.cuda.synchronize()
+    # every rank received exactly the tokens that have an expert there, sources in rank order
+    for o, rk in enumerate(ranks):
+        want = sum(int(((s.ids_host // E_loc) == o).any(dim=1).sum()) for s in ranks)
+        assert int(rk.recv_total) == want
+    for rk in ranks:        # the owner's ordinary layer on what arrived
+        ids_local = torch.empty(cap, k, dtype=torch.int32, device=DEV)
+        w_local = torch.empty(cap, k, dtype=torch.float32, device=DEV)
+        side = rk.buf[rk.off_side: rk.off_side + cap * side_w * 4].view(torch.int32)
+        ok(lib.b200moe_ep_unpack_routing(side.data_ptr(), rk.recv_total.data_ptr(), cap, k, side_w, rk.r, E_loc,
+                                         ids_local.data_ptr(), w_local.data_ptr(), st))
+        n = int(rk.recv_total)
+        assert (ids_local[n:] == -1).all() and (ids_local[:n] < E_loc).all()
+        rows = rk.buf[rk.off_rows: rk.off_rows + cap * row_bytes].view(rk.x.dtype).view(cap, H)
+        rsc = (rk.buf[rk.off_scales: rk.off_scales + cap * scale_bytes].view(torch.float32).view(cap, -1)
+               if fp8 else None)
+        partial = rk.buf[rk.off_out: rk.off_out + cap * H * 2].view(torch.bfloat16).view(cap, H)
+        partial.fill_(9.0)
+        rk.moe.apply(partial, rows, w_local, ids_local, a1q_scale=rsc, valid_tokens=rk.recv_total)
+        assert (partial[n:] == 9.0).all()            # rows past the count are not written
+    torch.cuda.synchronize()
+    ones = torch.ones(T, G, dtype=torch.float32, device=DEV)
+    for rk in ranks:        # one partial sum per (token, rank), added in rank order
+        src = torch.zeros(T * G, dtype=torch.int64, device=DEV)
+        ok(lib.b200moe_ep_source_table(rk.my_prefix.data_ptr(), rk.dst_start.data_ptr(), T * G, G, 1, bases,
+                                       rk.off_out, H * 2, cap, src.data_ptr(), st))
+        res = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+        ok(lib.b200moe_ep_gather(res.data_ptr(), 2, ones.data_ptr(), rk.row_map.data_ptr(), src.data_ptr(),
+                                 T, G, H, st))
+        torch.cuda.synchronize()
+        ref = O.fused_moe(recipe, rk.x_host, layer["w13"], layer["w13_scale"], None, layer["w2"],
+                          layer["w2_scale"], None, rk.w_host, rk.ids_host, "silu", out_dtype=torch.float32)
+        err = (res.float().cpu() - ref).abs()
+        assert (err <= 2e-2 + 2e-2 * ref.abs()).all(), f"rank {rk.r}: max err {err.max():.4g}"
+    assert ops._xpu_C.b200_device_status() == 0
