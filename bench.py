@@ -733,6 +733,9 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
         group = dist.group.WORLD
+        # the ranks of a benchmark run in lock step: a cross-rank barrier that has not completed
+        # after 5 s never will (the library's default budget, 30 s, is for serving hosts)
+        os.environ.setdefault("B200MOE_EP_BARRIER_TIMEOUT_MS", "5000")
     import vllm_xpu_kernels._C  # noqa: F401  (registers the operators; fails loudly without the .so)
 
     T = cfg["T"]

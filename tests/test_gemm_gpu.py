@@ -363,6 +363,8 @@ def _pow2_case(E, rows, K, N, seed):
 @pytest.mark.parametrize("E,rows,K,N", [
     (1, [128], 128, 256),                          # one tile, one stage
     (1, [100], 512, 512),                          # the four stages of the ring once
+    (2, [140, 90], 640, 256),                      # five K blocks: a second scale group with one block in it
+    (2, [64, 200], 896, 512),                      # seven: the ring wraps inside the second group
     (3, [130, 0, 257], 1024, 768),                 # ring wraps; three column tiles
     (2, [77, 300], 2048, 7168),                    # second GEMM of the DeepSeek-V3 layer
     (6, [500, 513, 1, 640, 390, 128], 1536, 1280), # 100 tiles... several per CTA
