@@ -155,6 +155,25 @@ def test_c3_layer_full_size_sampled_tokens(ops, c3_weights):
     _check(bench.parity_check(cfg, layer, x, logits, out, dev, n_tokens=16))
 
 
+def test_c3_layer_with_power_of_two_scales_full_size(ops):
+    """The same layer with its 128x128 block scales rounded up to powers of two: the layer picks
+    the kernel that lets the tensor core apply the scales (and quantises activations the same
+    way); 16 sampled tokens against the oracle quantising likewise."""
+    import bench
+    dev = torch.device(DEV)
+    cfg = dict(bench.CONFIGS["c3"], key="c3", pow2_scales=True)
+    weights = bench.make_device_layer(cfg, dev)
+    layer = bench.Layer(cfg, weights, cfg["T"], dev)
+    assert layer.moe.act_scales_pow2
+    x, logits = bench.make_inputs(cfg, cfg["T"], seed=0)
+    out = layer.step(x.to(dev), logits.to(dev)).clone()
+    assert torch.ops._xpu_C.b200_device_status() == 0
+    assert torch.isfinite(out.float()).all()
+    _check(bench.parity_check(cfg, layer, x, logits, out, dev, n_tokens=16))
+    del layer, weights
+    torch.cuda.empty_cache()
+
+
 @pytest.mark.parametrize("T", [1, 8, 32, 128, 256])
 def test_c4_decode_sweep_with_zipf_routing(ops, c3_weights, T):
     """The decode regime on the same weights: few tokens and router logits offset by

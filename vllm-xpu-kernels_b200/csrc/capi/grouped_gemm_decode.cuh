@@ -222,6 +222,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
     // ---------------- MMA issuer ----------------
     // A = weights, MN-major (features contiguous); B = tokens, K-major; e4m3 x e4m3 -> fp32
     const uint32_t idesc = make_idesc(0u, 0u, 1u, 0u, kFeat, kNTok);
+    const uint32_t desc_hi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024, version, 128-byte swizzle
+    const uint32_t w_lo0 = ((smem_u32(tiles) & 0x3FFFFu) >> 4) | ((kWBytes >> 4) << 16);
+    const uint32_t tok_lo0 = (((smem_u32(tiles) + C::W_TILES * kWBytes) & 0x3FFFFu) >> 4) | ((16u >> 4) << 16);
     int stage = 0;
     uint32_t phase = 0;
     int buf = 0;
@@ -234,16 +237,20 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap map_tok,
         ok = mbar_wait(&bars.full[stage], phase, abort_p);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t w_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
-        const uint32_t tok_addr = w_addr + C::W_TILES * kWBytes;
+        // descriptors: constant high word, low words = base + stage * constant (+ an
+        // immediate per K slice): what this one thread computes between two MMAs is time
+        // the tensor pipe idles
+        const uint32_t w_lo = w_lo0 + stage * (C::STAGE_BYTES >> 4);
+        const uint32_t tok_lo = tok_lo0 + stage * (C::STAGE_BYTES >> 4);
         const uint32_t d_tmem = tmem_base + buf * C::ACC_COLS;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t b_desc = make_sdesc_sw128(tok_addr + kk * 32, 16, 1024);
-          const uint64_t a_gate = make_sdesc_sw128(w_addr + kk * 32 * 128, kWBytes, 1024);
+          const uint64_t b_desc = (static_cast<uint64_t>(desc_hi) << 32) | (tok_lo + kk * 2);
+          const uint64_t a_gate = (static_cast<uint64_t>(desc_hi) << 32) | (w_lo + kk * ((32 * 128) >> 4));
           mma_f8(d_tmem, a_gate, b_desc, idesc, kk > 0 ? 1u : 0u);
           if (GATED) {
-            const uint64_t a_up = make_sdesc_sw128(w_addr + kWBytes + kk * 32 * 128, kWBytes, 1024);
+            const uint64_t a_up = (static_cast<uint64_t>(desc_hi) << 32) |
+                                  (w_lo + (kWBytes >> 4) + kk * ((32 * 128) >> 4));
             mma_f8(d_tmem + kNTok, a_up, b_desc, idesc, kk > 0 ? 1u : 0u);
           }
         }
