@@ -220,14 +220,15 @@ class Layer:
         self.ep_backend = None
         if group is not None:
             from vllm_xpu_kernels.ep import (ExpertParallel, PeerExpertParallel, TokenExpertParallel,
-                                             make_local_fn)
+                                             WaveExpertParallel, make_local_fn)
             self.ep_backend = ep_backend or os.environ.get("B200MOE_EP", "token")
-            if self.ep_backend in ("peer", "token"):
+            if self.ep_backend in ("peer", "token", "wave"):
                 fp8 = cfg["recipe"] == "fp8block"
                 mx = cfg["recipe"] == "mxfp4"
                 row_bytes = cfg["H"] * (1 if (fp8 or mx) else 2)
                 scale_bytes = (cfg["H"] // 128) * 4 if fp8 else ((cfg["H"] + 511) // 512 * 16 if mx else 0)
-                cls = TokenExpertParallel if self.ep_backend == "token" else PeerExpertParallel
+                cls = {"token": TokenExpertParallel, "wave": WaveExpertParallel,
+                       "peer": PeerExpertParallel}[self.ep_backend]
                 self.ep = cls(group, self.moe, T, cfg["k"], cfg["H"], row_bytes, scale_bytes, E_loc, dev)
             else:
                 self.ep = ExpertParallel(group, E_loc, make_local_fn(self.moe))
@@ -378,7 +379,10 @@ def workload_config(args, cfg):
                    "the library's own kernels",
            "token": "dispatch and combine move one row per (token, rank) through peer GPU memory from "
                     "the library's own kernels; each rank runs its local layer on the tokens it got and "
-                    "returns one partial sum per token"}[os.environ.get("B200MOE_EP", "token")]
+                    "returns one partial sum per token",
+           "wave": "the token-level exchange in two waves of tokens on two streams: one wave's "
+                   "dispatch and combine run beside the other wave's grouped GEMMs (GEMM grid capped "
+                   "at 132 of 148 SMs)"}[os.environ.get("B200MOE_EP", "token")]
     par = "1 GPU" if world == 1 else (f"expert-parallel over {world} GPUs ({cfg['E'] // world} experts each), "
                                       f"tokens data-parallel, {how}")
     return {"workload": f"{cfg.get('key', args.config)}: {cfg['name']}", "parallelism": par,
@@ -508,7 +512,7 @@ def measure(cfg, dev, rank, world, group, steps, warmup, timer, with_e2e=True, c
     x, logits = x_pin.to(dev), logits_pin.to(dev)
     from vllm_xpu_kernels import capi
     lib = capi.lib()
-    if world > 1 and layer.ep_backend == "token":
+    if world > 1 and layer.ep_backend in ("token", "wave"):
         # One step of the token-level exchange before anything is timed; if any rank fails
         # (an exception, or a bounded device wait that gave up) all ranks fall back together to
         # the row-level exchange, and the printed line says which one ran.

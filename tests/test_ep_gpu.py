@@ -35,11 +35,12 @@ def _worker(rank, world, port, recipe, backend, result):
     d = lambda t: None if t is None else t[sl].to(dev)  # noqa: E731
     moe = XpuFusedMoe(d(layer["w13"]), d(layer["w13_scale"]), None, d(layer["w2"]), d(layer["w2_scale"]),
                       None, cfg["k"], "silu", per)
-    if backend == "token":
-        from vllm_xpu_kernels.ep import TokenExpertParallel
+    if backend in ("token", "wave"):
+        from vllm_xpu_kernels.ep import TokenExpertParallel, WaveExpertParallel
         fp8 = recipe == "fp8block"
-        ep = TokenExpertParallel(dist.group.WORLD, moe, cfg["T"], cfg["k"], cfg["H"],
-                                 cfg["H"] * (1 if fp8 else 2), (cfg["H"] // 128) * 4 if fp8 else 0, per, dev)
+        cls = TokenExpertParallel if backend == "token" else WaveExpertParallel
+        ep = cls(dist.group.WORLD, moe, cfg["T"], cfg["k"], cfg["H"],
+                 cfg["H"] * (1 if fp8 else 2), (cfg["H"] // 128) * 4 if fp8 else 0, per, dev)
     elif backend.startswith("peer"):
         from vllm_xpu_kernels.ep import PeerExpertParallel
         fp8 = recipe == "fp8block"
@@ -70,17 +71,18 @@ def _worker(rank, world, port, recipe, backend, result):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("backend", ["nccl", "peer-pull", "peer-push", "token"])
+@pytest.mark.parametrize("backend", ["nccl", "peer-pull", "peer-push", "token", "wave"])
 @pytest.mark.parametrize("recipe", ["bf16", "fp8block"])
 def test_expert_parallel_two_gpus(recipe, backend):
     """backend 'nccl': all-to-all-v through torch.distributed; 'peer-*': this library's kernels
     storing into the other GPU's memory for the dispatch, and for the combine either the
     token's owner reading the result rows from the peers ('pull') or the second GEMM's
     epilogue storing them into the sender's memory ('push'); 'token': one row per (token, rank)
-    out, the receiving rank's ordinary local layer, one partial sum per (token, rank) back."""
+    out, the receiving rank's ordinary local layer, one partial sum per (token, rank) back;
+    'wave': the same in two waves of tokens on two streams."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    port = 29621 + 4 * (recipe != "bf16") + ["nccl", "peer-pull", "peer-push", "token"].index(backend)
+    port = 29621 + 5 * (recipe != "bf16") + ["nccl", "peer-pull", "peer-push", "token", "wave"].index(backend)
     with mp.Manager() as m:
         result = m.dict()
         mp.spawn(_worker, args=(2, port, recipe, backend, result), nprocs=2, join=True)

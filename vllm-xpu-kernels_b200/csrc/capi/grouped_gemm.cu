@@ -1090,6 +1090,12 @@ int launch_config(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaSt
   const int64_t max_m_tiles = (a.R + C::TILE_M - 1) / C::TILE_M + a.E;
   int64_t grid = max_m_tiles * n_tiles * (C::PAIR ? 2 : 1);
   if (grid > kNumSMs) grid = kNumSMs;
+  // B200MOE_GEMM_SMS caps the persistent grid (read per call): a caller that runs the exchange
+  // kernels of one wave of tokens beside the GEMMs of another leaves them a few SMs this way
+  if (const char* cap = getenv("B200MOE_GEMM_SMS")) {
+    const int c = atoi(cap);
+    if (c >= 2 && c < grid) grid = c;
+  }
   if (grid < 1) grid = 1;
   if (C::PAIR) {
     grid = grid < 2 ? 2 : grid & ~1ll;

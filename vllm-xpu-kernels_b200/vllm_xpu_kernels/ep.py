@@ -440,11 +440,70 @@ class TokenExpertParallel(PeerExpertParallel):
         rscales = self.recv_scales.view(scales.dtype).view(self.cap, -1) if scales is not None else None
         # the ordinary local layer on the tokens that arrived; rows past recv_total carry ids of
         # -1 and their partial rows are not written
+        gate, done = getattr(self, "gemm_gate", None), getattr(self, "gemm_done", None)
+        if gate is not None:    # second wave of WaveExpertParallel: after the first wave's GEMMs
+            torch.cuda.current_stream().wait_event(gate)
         self.moe.apply(self.partial, rows, self.w_local, self.ids_local, a1q_scale=rscales,
-                       valid_tokens=self.recv_total)
+                       valid_tokens=self.recv_total, after_gemms=done)
         with stage("ep_combine"):
             self.barrier(2)
             self._check(lib.b200moe_ep_gather(
                 output.data_ptr(), _FLOAT_CODES[output.dtype], self.ones[:T].data_ptr(),
                 row_map.data_ptr(), self.src_addr.data_ptr(), T, G, self.H, st), "ep_gather")
+        return output
+
+
+class WaveExpertParallel:
+    """Two waves of tokens through two token-level exchanges on two streams, so that one
+    wave's dispatch and combine run beside the other wave's grouped GEMMs:
+
+        stream 1:  dispatch A, permute A, GEMMs A,                gather A, combine A
+        stream 2:  dispatch B, permute B,          (GEMMs A done) GEMMs B, gather B, combine B
+
+    The grouped GEMM is a persistent kernel with one CTA per SM, so the exchange kernels only
+    find room beside it when its grid is capped (``gemm_sms``, default 132 of 148;
+    B200MOE_GEMM_SMS for the duration of a call); the two waves' GEMMs are serialised by an
+    event, not left to compete for the same SMs.  Worth it only where dispatch + combine are a
+    large share of the step (many ranks); with few ranks the SMs given up cost more than the
+    transfers hidden.
+    """
+
+    def __init__(self, group, moe, tokens_per_rank: int, topk: int, hidden: int, row_bytes: int,
+                 scale_row_bytes: int, experts_per_rank: int, device, out_dtype=torch.bfloat16,
+                 gemm_sms: int = 132):
+        self.half = (tokens_per_rank + 1) // 2
+        mk = lambda: TokenExpertParallel(group, moe, self.half, topk, hidden, row_bytes, scale_row_bytes,  # noqa: E731
+                                         experts_per_rank, device, out_dtype)
+        self.waves = (mk(), mk())
+        self.streams = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+        self.gemm_sms = gemm_sms
+        self.moe = moe
+
+    def apply(self, output, hidden, topk_weights, topk_ids, scales=None):
+        T = topk_ids.shape[0]
+        cut = min(self.half, T)
+        main = torch.cuda.current_stream()
+        parts = ((0, cut), (cut, T))
+        gemms_done = torch.cuda.Event()
+        prev = os.environ.get("B200MOE_GEMM_SMS")
+        os.environ["B200MOE_GEMM_SMS"] = str(self.gemm_sms)
+        try:
+            for i, (lo, hi) in enumerate(parts):
+                if hi <= lo:
+                    continue
+                st = self.streams[i]
+                st.wait_stream(main)
+                with torch.cuda.stream(st):
+                    ep = self.waves[i]
+                    ep.gemm_gate = gemms_done if i == 1 else None      # wait for wave A's GEMMs
+                    ep.gemm_done = gemms_done if i == 0 else None      # record after wave A's GEMMs
+                    ep.apply(output[lo:hi], hidden[lo:hi], topk_weights[lo:hi], topk_ids[lo:hi],
+                             scales=None if scales is None else scales[lo:hi])
+            for st in self.streams:
+                main.wait_stream(st)
+        finally:
+            if prev is None:
+                os.environ.pop("B200MOE_GEMM_SMS", None)
+            else:
+                os.environ["B200MOE_GEMM_SMS"] = prev
         return output

@@ -222,7 +222,8 @@ class XpuFusedMoe:
 
     # ------------------------------------------------------------------
     def apply(self, output, hidden_states, topk_weights, topk_ids, expert_map=None,
-              a1q_scale=None, row_destinations=None, shared_output=None, valid_tokens=None):
+              a1q_scale=None, row_destinations=None, shared_output=None, valid_tokens=None,
+              after_gemms=None):
         """output[T, H] = sum_j w[t, j] * Expert_{ids[t, j]}(hidden_states[t]).
 
         ``hidden_states`` is bf16/fp16 ``[T, H]``, or already quantised
@@ -242,7 +243,10 @@ class XpuFusedMoe:
         ``valid_tokens`` (not in the reference signature; used by the expert-parallel token
         exchange): int32 ``[1]`` on the device, the number of leading rows of a worst-case
         sized ``hidden_states`` that hold tokens.  Rows past it must carry ids of -1; their
-        output rows are then not written at all."""
+        output rows are then not written at all.
+
+        ``after_gemms`` (not in the reference signature): a ``torch.cuda.Event`` recorded on the
+        current stream right after the second grouped GEMM, before the combine."""
         num_rows, hidden_size = hidden_states.shape
         k = topk_ids.shape[1]  # n_experts_per_token, or 1 for rows that arrive already dispatched
         R = num_rows * k
@@ -285,6 +289,8 @@ class XpuFusedMoe:
 
         row_ptr = row_destinations(row_map) if row_destinations is not None else None
         gemm2_out = self.run_experts(remapped, remapped_scales, rows_per_expert, output.dtype, row_ptr)
+        if after_gemms is not None:
+            after_gemms.record()
         if row_ptr is not None:
             return
         with self._stage("gather"):
