@@ -175,6 +175,41 @@ def test_every_tile_shape(ops, tile_n, pair, kind, monkeypatch):
     close(D, ref)
 
 
+@pytest.mark.parametrize("offload", ["0", "1"])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("E,rows_list,K,N", [(3, [130, 0, 257], 512, 768), (4, [1, 255, 256, 300], 384, 384),
+                                            (2, [700, 129], 1280, 1152)])
+def test_fp8_pair_store_through_the_spare_warps(ops, E, rows_list, K, N, out_dtype, offload, monkeypatch):
+    """Block-scaled FP8 store GEMM on CTA pairs: the finished tile leaves through a staging tile
+    in shared memory and the two spare warps (default), or through the reader warps
+    (B200MOE_STORE_OFFLOAD=0).  Ragged experts (an empty one, one row, a row more than a tile),
+    a tile that hangs over the right edge (N = 384, 1152), several tiles per CTA pair so that
+    the staging tile is reused, a bias.  Both ways give the same bits."""
+    monkeypatch.setenv("B200MOE_TILE_N", "256")
+    monkeypatch.setenv("B200MOE_PAIR", "1")
+    monkeypatch.setenv("B200MOE_STORE_OFFLOAD", offload)
+    rows = torch.tensor(rows_list, dtype=torch.int32)
+    R = int(rows.sum())
+    g = torch.Generator().manual_seed(K + N)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    Aq, As = O.per_token_group_fp8_quant(x, 128)
+    Bq, Bs = zip(*[O.quant_fp8_block_weight(torch.randn(K, N, generator=g) / K ** 0.5) for _ in range(E)])
+    Bq, Bs = torch.stack(Bq), torch.stack(Bs) * (1.0 + 0.25 * torch.rand(E, K // 128, N // 128, generator=g))
+    bias = (torch.randn(E, N, generator=g) * 0.1).to(torch.bfloat16)
+    ref = O.grouped_gemm("fp8block", O.dequant_fp8_group_act(Aq, As), Bq, Bs, bias, rows, torch.float32)
+    guard = 64  # rows after the last expert must stay untouched
+    D = torch.full((R + guard, N), 7.0, dtype=out_dtype, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), bias.to(DEV), D[:R],
+                                 rows.to(DEV), N, K, E, EPI_STORE, KN)
+    close(D[:R], ref)
+    assert bool((D[R:] == 7.0).all())
+    monkeypatch.setenv("B200MOE_STORE_OFFLOAD", "0")
+    D0 = torch.zeros(R, N, dtype=out_dtype, device=DEV)
+    ops._xpu_C.b200_grouped_gemm(Aq.to(DEV), As.to(DEV), Bq.to(DEV), Bs.to(DEV), bias.to(DEV), D0,
+                                 rows.to(DEV), N, K, E, EPI_STORE, KN)
+    assert torch.equal(D0, D[:R])
+
+
 @pytest.mark.parametrize("pair", ["0", "1"])
 @pytest.mark.parametrize("E,avg,K,N", [(2, 100, 256, 512), (8, 60, 4096, 2048), (3, 200, 512, 28672 // 8)])
 def test_fp8_fused_silu_quant_epilogue(ops, E, avg, K, N, pair, monkeypatch):

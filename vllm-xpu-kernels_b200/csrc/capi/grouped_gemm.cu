@@ -254,7 +254,7 @@ __device__ __forceinline__ void store_row16(void* D, int d_dtype, int64_t elem_o
 }
 
 template <int KIND_, bool B_MN_MAJOR_, bool PROMOTE_, int BN_, int EPI_, int STAGES_,
-          bool PAIR_ = false>
+          bool PAIR_ = false, bool OFFLOAD_ = false>
 struct Config {
   static constexpr int KIND = KIND_;
   // PAIR: two CTAs of a cluster share each MMA (cta_group::2).  The scheduled tile is
@@ -292,13 +292,22 @@ struct Config {
   // warpgroups take registers from the producer/MMA warpgroup (setmaxnreg).
   static constexpr bool REBALANCE_REGS = BN == 256;
   static constexpr int XCHG = (EPI_ == B200MOE_EPI_SILU_MUL || EPI_ == kEpiGatedAny) ? 256 : 1;
-  static constexpr size_t SMEM_BYTES = 1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + SF_BYTES;
+  // OFFLOAD: the reader warps leave the finished tile as 16-bit rows in shared memory and go
+  // straight back to the accumulators; the two spare warps of the producer warpgroup write
+  // it to global memory while the next tile is being computed.
+  static constexpr bool OFFLOAD = OFFLOAD_;
+  static constexpr int OUT_ROW_BYTES = BN_ * 2;
+  static constexpr int OUT_BYTES = OFFLOAD_ ? BM * OUT_ROW_BYTES : 0;
+  static constexpr size_t SMEM_BYTES =
+      1024 + static_cast<size_t>(STAGES) * STAGE_BYTES + SF_BYTES + OUT_BYTES;
   static constexpr int SB_SMEM = PROMOTE_ ? 2 * kMaxKBlocks : 1;
   static_assert(!SCALED || (BN_ == 256 && !PROMOTE_ && !PAIR_ && B_MN_MAJOR_),
                 "the tensor-core-scaled FP8 kernel is laid out for single CTAs and 256-column tiles");
   static_assert(!(GATED_SPLIT && B_MN_MAJOR_ && !PAIR_ && N_CHUNKS < 2),
                 "a split gated tile needs two weight boxes");
   static_assert(!PAIR_ || BN_ == 256, "CTA pairs are laid out for 256-column tiles");
+  static_assert(!OFFLOAD_ || (PROMOTE_ && EPI_ == B200MOE_EPI_STORE && BN_ == 256 && KIND_ != KIND_F8S),
+                "the offloaded store is laid out for the promoting FP8 kernel's 128 x 256 store tiles");
   static_assert(SMEM_BYTES > 116 * 1024, "one CTA per SM is assumed by the tensor-memory allocation");
   static_assert(NCH == 2 || NCH == 4, "reader pipeline alternates two 32-column buffers");
 };
@@ -311,6 +320,8 @@ struct alignas(8) Barriers {
   uint64_t sready;  // this tile's staged scales are in shared memory (one arrival per reader warp)
   uint64_t sffull[2];   // KIND_F8S: a group of scale words is in shared memory / has been copied
   uint64_t sfempty[2];  //           to tensor memory
+  uint64_t ofull;       // OFFLOAD: the staged output tile is complete (one arrival per reader warp)
+  uint64_t oempty;      //          ... has been written out (one arrival per store warp)
 };
 
 // Tensor-memory column (inside one accumulator buffer) of chunk c of a reader
@@ -406,6 +417,88 @@ __device__ __forceinline__ void store_rows_coalesced(uint4* wbuf, int lane, int 
   }
 }
 
+// acc[] += the expert's bias for the columns this reader thread holds.
+template <typename C>
+__device__ __forceinline__ void add_bias(const GemmParams& p, const TileCoord& tc, int g,
+                                         float (&acc)[C::CPT]) {
+  if (!p.bias) return;
+#pragma unroll
+  for (int c = 0; c < C::NCH; ++c) {
+    const int col0 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, c), p.N);
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col0 + j < p.N)
+        acc[c * 32 + j] += load_bias(p.bias, p.bias_dtype,
+                                     static_cast<int64_t>(tc.expert) * p.N + col0 + j);
+  }
+}
+
+// Offloaded store, reader side: row `row` of the tile (this thread's) as 16-bit values into
+// the staging tile.  A row is BN * 2 bytes = 32 pieces of 16 bytes; piece c of row r sits at
+// piece (c ^ (r & 31)) of that row, so that the 32 lanes of a reader warp (32 rows, same
+// piece) and the 32 lanes of a store warp (one row, 32 pieces) both spread over all banks.
+template <typename C>
+__device__ __forceinline__ void stage_row(uint8_t* out_stage, int row, int g, int d_dtype,
+                                          const float (&acc)[C::CPT]) {
+  uint8_t* rbase = out_stage + row * C::OUT_ROW_BYTES;
+  const int sw = row & 31;
+#pragma unroll
+  for (int i = 0; i < C::CPT / 8; ++i) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float a = acc[i * 8 + 2 * k], b = acc[i * 8 + 2 * k + 1];
+      if (d_dtype == B200MOE_BF16) {
+        const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+      } else {
+        const __half2 h = __floats2half2_rn(a, b);
+        w[k] = *reinterpret_cast<const uint32_t*>(&h);
+      }
+    }
+    const int piece = g * (C::CPT / 8) + i;
+    *reinterpret_cast<uint4*>(rbase + ((piece ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+// Offloaded store, store-warp side: rows [row_lo, row_hi) of the staged tile to D, one
+// 512-byte row per warp instruction.
+template <typename C>
+__device__ __forceinline__ void write_staged_rows(const GemmParams& p, const TileCoord& tc,
+                                                  int rank, const uint8_t* out_stage, int row_lo,
+                                                  int row_hi, int lane) {
+  const int col = tc.n_tile * C::BN + lane * 8;   // first of this lane's 8 columns
+  int valid = tc.rows_valid - rank * BM;           // rows of this CTA's 128 that exist
+  if (row_hi > valid) row_hi = valid;
+  if (col >= p.N) return;
+  uint8_t* d0 = reinterpret_cast<uint8_t*>(p.D) +
+                (static_cast<int64_t>(tc.row_start) + rank * BM) * p.ldd * 2 + static_cast<int64_t>(col) * 2;
+  const bool whole = col + 8 <= p.N;
+  // 40 registers per thread in this warpgroup: two rows in flight, one running pointer
+  const int64_t row_pitch = static_cast<int64_t>(p.ldd) * 2;
+  uint8_t* dst = d0 + row_lo * row_pitch;
+  int r = row_lo;
+  if (whole) {
+    for (; r + 2 <= row_hi; r += 2, dst += 2 * row_pitch) {
+      const uint4 v0 = *reinterpret_cast<const uint4*>(out_stage + r * C::OUT_ROW_BYTES + ((lane ^ (r & 31)) << 4));
+      const uint4 v1 = *reinterpret_cast<const uint4*>(out_stage + (r + 1) * C::OUT_ROW_BYTES +
+                                                       ((lane ^ ((r + 1) & 31)) << 4));
+      *reinterpret_cast<uint4*>(dst) = v0;
+      *reinterpret_cast<uint4*>(dst + row_pitch) = v1;
+    }
+  }
+  for (; r < row_hi; ++r, dst += row_pitch) {
+    const uint4 v = *reinterpret_cast<const uint4*>(out_stage + r * C::OUT_ROW_BYTES + ((lane ^ (r & 31)) << 4));
+    if (whole) {
+      *reinterpret_cast<uint4*>(dst) = v;
+    } else {  // ragged right edge: element by element
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+      for (int j = 0; j < 8; ++j)
+        if (col + j < p.N) reinterpret_cast<uint16_t*>(dst)[j] = e[j];
+    }
+  }
+}
+
 // acc[] -> global memory for one row of one tile.
 template <typename C>
 __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoord& tc, int g,
@@ -420,17 +513,7 @@ __device__ __forceinline__ void tile_epilogue(const GemmParams& p, const TileCoo
     if (rr >= warp_rows_valid) return nullptr;
     return reinterpret_cast<uint8_t*>(p.D) + (warp_row0 + rr) * p.ldd * 2;
   };
-  if (p.bias) {
-#pragma unroll
-    for (int c = 0; c < C::NCH; ++c) {
-      const int col0 = problem_col<C>(tc.n_tile, chunk_tmem_col<C>(g, c), p.N);
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < p.N)
-          acc[c * 32 + j] += load_bias(p.bias, p.bias_dtype,
-                                       static_cast<int64_t>(tc.expert) * p.N + col0 + j);
-    }
-  }
+  add_bias<C>(p, tc, g, acc);
   if constexpr (C::EPI == B200MOE_EPI_STORE) {
     const int col0 = tc.n_tile * C::BN + g * CPT;
     if (col0 < p.N) {
@@ -556,7 +639,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
   __shared__ int abort_flag;
   __shared__ float xchg[2][C::XCHG];  // group-amax exchange of the quantising epilogue, by tile parity
   __shared__ float sb_smem[2][C::SB_SMEM];  // weight scales of the tile's two column blocks
-  __shared__ uint4 epi_buf[C::EPI_WARPS][128];   // per reader warp: 32 rows x 64 B for coalesced stores
+  __shared__ uint4 epi_buf[C::OFFLOAD ? 1 : C::EPI_WARPS][128];   // per reader warp: 32 rows x 64 B for coalesced stores
 
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
@@ -577,6 +660,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(&bars.tempty[b], C::EPI_WARPS * (C::PAIR ? 2 : 1));  // both CTAs' readers
     }
     mbar_init(&bars.sready, C::EPI_WARPS);
+    mbar_init(&bars.ofull, C::EPI_WARPS);
+    mbar_init(&bars.oempty, 2);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&bars.sffull[b], 1);
       mbar_init(&bars.sfempty[b], 1);
@@ -827,6 +912,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
           if (++buf == C::ACC_BUFS) { buf = 0; buf_phase ^= 1u; }
         }
       }
+    } else if (C::OFFLOAD && warp >= 2) {
+      // ---------------- store warps (OFFLOAD): staged tile -> global memory ----------------
+      const uint8_t* out_stage = tiles + C::STAGES * C::STAGE_BYTES + C::SF_BYTES;
+      uint32_t out_phase = 0;
+      bool ok = true;
+      for (int t = sched_id; t < num_tiles && ok; t += sched_stride, out_phase ^= 1u) {
+        const TileCoord tc = decode_tile(sched, t);
+        ok = mbar_wait_relaxed(&bars.ofull, out_phase, abort_p);
+        if (!ok) break;
+        write_staged_rows<C>(p, tc, rank, out_stage, (warp - 2) * (BM / 2), (warp - 1) * (BM / 2), lane);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.oempty);
+      }
     }
   } else {
     // ---------------- accumulator readers / epilogue ----------------
@@ -975,7 +1073,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a,
         }
       }
       if (!ok) break;
-      tile_epilogue<C>(p, tc, g, row_ok, grow, acc, xchg[tile_parity], epi_buf[ew]);
+      if constexpr (C::OFFLOAD) {
+        // the tile leaves through shared memory; the store warps write it out while this
+        // warp is back at the accumulators of the next tile
+        add_bias<C>(p, tc, g, acc);
+        ok = mbar_wait(&bars.oempty, static_cast<uint32_t>(tile_parity) ^ 1u, abort_p);
+        if (!ok) break;
+        if (row_ok) stage_row<C>(tiles + C::STAGES * C::STAGE_BYTES + C::SF_BYTES, row_in_tile, g, p.d_dtype, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars.ofull);
+      } else {
+        tile_epilogue<C>(p, tc, g, row_ok, grow, acc, xchg[tile_parity], epi_buf[ew]);
+      }
     }
   }
 
@@ -1277,6 +1386,18 @@ template <int KIND, bool MN, bool PROMOTE, int BN, int STAGES, bool PAIR = false
 static int launch_epi(const b200moe_gemm_args& a, const void* B, int b_dtype, cudaStream_t st) {
   switch (a.epilogue) {
     case B200MOE_EPI_STORE:
+      if constexpr (KIND == KIND_F8 && PROMOTE && PAIR && BN == 256) {
+        // The tile leaves through a staging tile in shared memory and the spare warps; four
+        // operand stages instead of six make room for it.  Measured on tiles of 16 K blocks
+        // (K = 2048): +5 % with 32 experts of 1024 or 4096 rows, +2-4 % on 256 ragged experts
+        // of ~512 rows; on tiles of 112 K blocks, where the store is 2 % of a tile, -5 %.
+        // So: short tiles only.  B200MOE_STORE_OFFLOAD=0 / 1 forces the choice (tests).
+        // Rows with a home of their own (d_row_ptr) keep the reader-warp store.
+        const char* off = getenv("B200MOE_STORE_OFFLOAD");
+        const bool on = off ? off[0] != '0' : a.K <= 4096;
+        if (on && !a.d_row_ptr)
+          return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, 4, PAIR, true>>(a, B, b_dtype, st);
+      }
       return launch_config<Config<KIND, MN, PROMOTE, BN, B200MOE_EPI_STORE, STAGES, PAIR>>(a, B, b_dtype, st);
     case B200MOE_EPI_SILU_MUL:
       // an MN-major split tile needs one weight box for the gate half and one for the up half

@@ -85,6 +85,24 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+// Same contract for a wait that is off every critical path (many thousand cycles long, and a
+// microsecond late costs nothing): sleeps between polls, so the warp takes no issue slots
+// from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity,
+                                                  volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    __nanosleep(500);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitBudgetCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // Same contract, but polls without ever suspending the thread: for the waits of
 // the accumulator ring, where the time to notice a completed phase is on the
 // critical path of every K block.
