@@ -153,8 +153,15 @@ class XpuFusedMoe:
                 m, _ = torch.frexp(t.float())
                 return bool(((m == 0.5) & (t > 0)).all().item())
             H_, I2_ = w13.shape[-2], w13.shape[-1]
-            self.act_scales_pow2 = (H_ % 128 == 0 and (I2_ // 2) % 128 == 0
-                                    and _pow2(w13_scales) and _pow2(w2_scales))
+            dims_ok = H_ % 128 == 0 and (I2_ // 2) % 128 == 0
+            self.act_scales_pow2 = dims_ok and _pow2(w13_scales) and _pow2(w2_scales)
+            if dims_ok and not self.act_scales_pow2 and _is_env_enabled("B200MOE_FP8_REQUANT_POW2"):
+                # opt-in load-time step: arbitrary fp32 block scales rounded up to powers of two,
+                # the weights re-rounded against them, IN PLACE (one more e4m3 rounding per weight)
+                from .moe_utils import requant_fp8_block_weights_pow2_
+                requant_fp8_block_weights_pow2_(w13, w13_scales)
+                requant_fp8_block_weights_pow2_(w2, w2_scales)
+                self.act_scales_pow2 = True
         # W8A16 / W4A16 recipes: widened once per activation dtype, on first use
         self._expanded = {}
         self.w13_bias, self.w2_bias = w13_bias, w2_bias

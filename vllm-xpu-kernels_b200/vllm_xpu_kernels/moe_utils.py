@@ -60,6 +60,25 @@ def quant_fp8_block_act(x: torch.Tensor, pow2_scales: bool = False):
     return x_q, x_s
 
 
+def requant_fp8_block_weights_pow2_(w: torch.Tensor, scales: torch.Tensor) -> None:
+    """In place: block-FP8 weights [E, K, N] (e4m3) with 128x128 fp32 scales [E, K/128, N/128] are
+    re-expressed with every scale rounded UP to a power of two, the elements re-rounded to e4m3
+    against the new scale (value * old / new, at most a factor two smaller, so nothing
+    saturates).  A load-time step for checkpoints whose scales are arbitrary fp32 numbers: the
+    layer can then let the tensor core apply the scales.  Not exact -- each element is rounded
+    to e4m3 a second time -- which is why it is opt-in (B200MOE_FP8_REQUANT_POW2=1)."""
+    E, K, N = w.shape
+    assert K % 128 == 0 and N % 128 == 0 and scales.shape == (E, K // 128, N // 128)
+    for e in range(E):  # one expert at a time: the fp32 copy of one expert is all that is held
+        old = scales[e].float()
+        m, ex = torch.frexp(old)                      # old = m * 2^ex, m in [0.5, 1)
+        new = torch.ldexp(torch.ones_like(old), torch.where(m == 0.5, ex - 1, ex))
+        ratio = (old / new).view(K // 128, 1, N // 128, 1)
+        blk = w[e].float().view(K // 128, 128, N // 128, 128) * ratio
+        w[e].copy_(blk.view(K, N).to(torch.float8_e4m3fn))
+        scales[e].copy_(new)
+
+
 def _quant_mxfp8_act_xpu(x):
     assert x.shape[-1] % 32 == 0
     x_q = torch.empty_like(x, dtype=torch.float8_e4m3fn)
