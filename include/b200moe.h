@@ -360,6 +360,11 @@ typedef struct b200moe_gemm_args {
 /* cutlass_grouped_gemm_interface (csrc/xpu/torch_bindings.cpp:58-67,
  * csrc/xpu/grouped_gemm/grouped_gemm_interface.cpp:12-64): for expert e with
  * rows [off_e, off_e + rows_e): D = A * B_e (+ bias_e), fp32 accumulate. */
+/* Environment read per call (no effect on results): B200MOE_GEMM_SMS=n caps the persistent grid
+ * (a caller overlapping other kernels with the GEMM); B200MOE_STORE_OFFLOAD=0/1 forces where
+ * the block-FP8 store GEMM on CTA pairs writes its tiles from (reader warps / the two spare
+ * warps through a shared-memory staging tile; default: the latter for K <= 4096);
+ * B200MOE_PAIR, B200MOE_TILE_N force a tile shape (tests). */
 size_t b200moe_grouped_gemm_workspace_bytes(const b200moe_gemm_args* args);
 int b200moe_grouped_gemm(const b200moe_gemm_args* args, void* workspace,
                          size_t workspace_bytes, void* stream);
